@@ -1,0 +1,54 @@
+import os
+import sys
+
+import numpy as np
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+GOLDEN_DIR = os.path.join(ROOT, "tests", "golden")
+GOLDEN_CASES = sorted(f[:-4] for f in os.listdir(GOLDEN_DIR) if f.endswith(".npz"))
+
+
+def pytest_configure(config):
+    config.addinivalue_line("markers", "gpu: needs a CUDA device (run on a B200 box)")
+
+
+def load_golden(name):
+    return dict(np.load(os.path.join(GOLDEN_DIR, name + ".npz")))
+
+
+def golden_positions(g, oracle):
+    """Feature vectors of a golden case, rebuilt the way the op builds them."""
+    inp = g["input"]
+    sdims = list(inp.shape[:-1])
+    if "positions" in g:
+        return g["positions"]
+    if bool(g["bilateral"]):
+        ref = g["reference"]
+        return oracle.compute_positions(ref.reshape(-1, ref.shape[-1]), sdims,
+                                        float(g["theta_alpha"]), float(g["theta_beta"]))
+    return oracle.compute_positions(None, sdims, float(g["theta_gamma"]), -1.0)
+
+
+def sorted_rows(keys):
+    order = np.lexsort(keys.T[::-1])
+    return keys[order]
+
+
+def bits(a):
+    return np.ascontiguousarray(a, np.float32).view(np.uint32)
+
+
+def rel_l2(a, b):
+    a = np.asarray(a, np.float64)
+    b = np.asarray(b, np.float64)
+    return float(np.linalg.norm(a - b) / max(np.linalg.norm(b), 1e-30))
+
+
+@pytest.fixture(scope="session")
+def oracle():
+    from oracle import cpu_oracle
+    return cpu_oracle

@@ -1,0 +1,102 @@
+"""Generates the golden fixtures of this folder from the UNMODIFIED reference CPU implementation
+(oracle/_ref/libpl_ref.so, built by oracle/build.py from the reference tree, hash table pre-sized so
+it never grows).  Needs the reference tree; run from the repository root:
+
+    python tests/golden/make_golden.py
+
+Each <case>.npz holds the inputs, the call arguments and what the reference produced: forward and
+reverse outputs, the vertex count, the vertex keys (sorted rows) and each pixel's enclosing-simplex
+keys and barycentric weights.  photo_crop.npz additionally carries a 96x96 crop of the reference's
+demo photograph (Images/input.bmp) as uint8.
+"""
+import os
+import sys
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+sys.path.insert(0, ROOT)
+from oracle import cpu_oracle as O  # noqa: E402
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def sorted_rows(keys):
+    order = np.lexsort(keys.T[::-1])
+    return keys[order]
+
+
+def run_case(name, inp, ref=None, positions=None, bilateral=True, ta=1.0, tb=1.0, tg=1.0):
+    """inp [*S, C]; ref [*S, R] or None; positions [n, pd] or None (positions-in path)."""
+    sdims = list(inp.shape[:-1])
+    n = int(np.prod(sdims))
+    c = inp.shape[-1]
+    if positions is None:
+        if bilateral:
+            pos = O.compute_positions(ref.reshape(n, -1), sdims, ta, tb, impl="reference")
+        else:
+            pos = O.compute_positions(None, sdims, tg, -1.0, impl="reference")
+    else:
+        pos = positions
+    fwd = O.filter(inp.reshape(n, c), pos, reverse=False, impl="reference")
+    rev = O.filter(inp.reshape(n, c), pos, reverse=True, impl="reference", structure=False)
+    data = dict(
+        input=inp.astype(np.float32),
+        bilateral=np.array(bilateral), theta_alpha=np.float32(ta), theta_beta=np.float32(tb),
+        theta_gamma=np.float32(tg),
+        out_forward=fwd.out.reshape(inp.shape), out_reverse=rev.out.reshape(inp.shape),
+        num_vertices=np.int64(fwd.num_vertices), keys_sorted=sorted_rows(fwd.keys),
+        pixel_keys=fwd.pixel_keys(), pixel_weights=fwd.pix_weight,
+    )
+    if ref is not None:
+        data["reference"] = ref.astype(np.float32)
+    if positions is not None:
+        data["positions"] = positions.astype(np.float32)
+    np.savez_compressed(os.path.join(HERE, name + ".npz"), **data)
+    print(name, "n", n, "pd", pos.shape[1], "vd", c + 1, "M", fwd.num_vertices)
+
+
+def main():
+    rng = np.random.default_rng(20181)
+    # pd 5, vd 4: RGB filtered by itself (the reference's demo setting, theta 8 / 0.125)
+    img = rng.random((40, 48, 3), dtype=np.float32)
+    img = (0.5 * img + 0.5 * np.round(img * 3) / 3).astype(np.float32)
+    run_case("rgb_pd5_vd4", img, ref=img, ta=8.0, tb=0.125)
+    # pd 5, vd 2: grey guided by RGB, odd sizes
+    run_case("grey_pd5_vd2", rng.random((33, 29, 1), dtype=np.float32),
+             ref=rng.random((33, 29, 3), dtype=np.float32), ta=5.0, tb=0.1)
+    # pd 5, vd 22: CRF-like, 21 channels
+    logits = 3 * rng.standard_normal((32, 36, 21)).astype(np.float32)
+    e = np.exp(logits - logits.max(-1, keepdims=True))
+    ref = np.repeat(np.repeat(rng.random((4, 6, 3), dtype=np.float32), 8, 0), 6, 1)
+    ref = np.clip(ref + rng.normal(0, 0.05, ref.shape), 0, 1).astype(np.float32)
+    run_case("crf_pd5_vd22", (e / e.sum(-1, keepdims=True)).astype(np.float32), ref=ref, ta=10.0,
+             tb=0.0625)
+    # pd 4, vd 3: volume guided by one channel
+    vol = rng.random((10, 12, 9, 1), dtype=np.float32)
+    vol = np.round(vol * 4) / 4
+    run_case("volume_pd4_vd3", rng.standard_normal((10, 12, 9, 2)).astype(np.float32),
+             ref=vol.astype(np.float32), ta=5.0, tb=0.1)
+    # pd 16, vd 4: positions given
+    run_case("patch_pd16_vd4", rng.random((700, 3), dtype=np.float32),
+             positions=(rng.standard_normal((700, 16)) * 1.5).astype(np.float32))
+    # spatial-only kernels (bilateral = False): pd 2 and pd 3
+    run_case("spatial_pd2_vd4", rng.random((21, 17, 3), dtype=np.float32), bilateral=False, tg=3.0)
+    run_case("spatial_pd3_vd2", rng.random((7, 9, 8, 1), dtype=np.float32), bilateral=False, tg=2.0)
+    # 1-D signal guided by itself: pd 2, vd 2
+    sig = np.cumsum(rng.standard_normal((300, 1)), 0).astype(np.float32)
+    run_case("signal_pd2_vd2", sig, ref=sig, ta=4.0, tb=0.5)
+    # crop of the reference's demo photograph
+    from PIL import Image
+    from oracle import build as B
+    photo = np.array(Image.open(os.path.join(B.reference_root(), "Images", "input.bmp")))
+    crop = photo[500:596, 300:396]
+    x = (crop / 255.0).astype(np.float32)
+    run_case("photo_crop", x, ref=x, ta=8.0, tb=0.125)
+    d = dict(np.load(os.path.join(HERE, "photo_crop.npz")))
+    d["crop_u8"] = crop
+    np.savez_compressed(os.path.join(HERE, "photo_crop.npz"), **d)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,80 @@
+"""Pins the C restatement to the unmodified reference header (oracle/_ref/libpl_ref.so) and the
+reference's shipped golden image.  Skipped where neither the built shim nor the reference tree
+exists."""
+import os
+
+import numpy as np
+import pytest
+
+from conftest import bits
+
+from oracle import build as obuild
+from oracle import cpu_oracle as O
+
+needs_ref = pytest.mark.skipif(not O.reference_available(), reason="reference oracle not available")
+
+
+@needs_ref
+@pytest.mark.parametrize("shape,r,c,ta,tb", [
+    ((37, 41), 3, 3, 8.0, 0.125),
+    ((64, 64), 3, 21, 20.0, 0.0625),
+    ((12, 11, 10), 1, 2, 5.0, 0.1),
+    ((150, 160), 3, 1, 3.0, 0.05),     # enough vertices to make the shipped table grow
+])
+@pytest.mark.parametrize("reverse", [False, True])
+def test_port_bit_identical_to_presized_reference(shape, r, c, ta, tb, reverse):
+    rng = np.random.default_rng(7)
+    ref = rng.random((1,) + shape + (r,), dtype=np.float32)
+    inp = rng.standard_normal((1,) + shape + (c,)).astype(np.float32)
+    o1, s1 = O.lattice_filter(inp, ref, True, ta, tb, 1.0, reverse, impl="port", structure=True)
+    o2, s2 = O.lattice_filter(inp, ref, True, ta, tb, 1.0, reverse, impl="reference", structure=True)
+    assert s1[0].num_vertices == s2[0].num_vertices
+    assert np.array_equal(s1[0].keys, s2[0].keys)
+    assert np.array_equal(s1[0].pix_vertex, s2[0].pix_vertex)
+    assert np.array_equal(bits(s1[0].pix_weight), bits(s2[0].pix_weight))
+    assert np.array_equal(bits(o1), bits(o2))
+
+
+@needs_ref
+def test_port_matches_reference_positions_in_pd16():
+    rng = np.random.default_rng(3)
+    pos = (rng.standard_normal((2000, 16)) * 2).astype(np.float32)
+    inp = rng.random((2000, 3), dtype=np.float32)
+    a = O.filter(inp, pos, impl="port")
+    b = O.filter(inp, pos, impl="reference")
+    assert a.num_vertices == b.num_vertices
+    assert np.array_equal(a.keys, b.keys)
+    assert np.array_equal(bits(a.out), bits(b.out))
+
+
+@needs_ref
+def test_batch_entry_points_agree():
+    rng = np.random.default_rng(5)
+    ref = rng.random((3, 20, 24, 3), dtype=np.float32)
+    inp = rng.random((3, 20, 24, 4), dtype=np.float32)
+    a, _ = O.filter_batch_timed(inp, ref, True, 6.0, 0.2, impl="port", threads=2)
+    b, _ = O.filter_batch_timed(inp, ref, True, 6.0, 0.2, impl="reference", threads=2,
+                                min_vertices=20 * 24 * 6)
+    c = O.lattice_filter(inp, ref, True, 6.0, 0.2, impl="port")
+    assert np.array_equal(bits(a), bits(b))
+    assert np.array_equal(bits(a), bits(c))
+
+
+@pytest.mark.skipif(obuild.reference_root() is None, reason="reference tree absent")
+def test_shipped_golden_image():
+    """Images/input.bmp -> Images/bilateral_out_1.bmp (Tests/bilateral_filter.py: theta 8 / 0.125,
+    np.round(out * 255)).  The reference as shipped reproduces the file exactly; the duplicate-free
+    result (pre-sized reference == C restatement) differs by one grey level in a few hundred bytes."""
+    from PIL import Image
+    root = obuild.reference_root()
+    im = np.array(Image.open(os.path.join(root, "Images", "input.bmp")))
+    gold = np.array(Image.open(os.path.join(root, "Images", "bilateral_out_1.bmp")))
+    x = (im / 255.0).astype(np.float32).reshape(-1, 3)
+    pos = O.compute_positions(x, list(im.shape[:2]), 8.0, 0.125, impl="reference")
+    shipped = O.filter(x, pos, impl="reference", as_shipped=True, structure=False)
+    assert np.array_equal(np.round(shipped.out.reshape(im.shape) * 255).astype(np.uint8), gold)
+    port = O.filter(x, pos, impl="port", structure=False)
+    d = np.abs(np.round(port.out.reshape(im.shape) * 255).astype(np.int32) - gold.astype(np.int32))
+    assert d.max() <= 1
+    assert (d != 0).mean() <= 5e-4
+    assert port.num_vertices == 155703
