@@ -1,0 +1,123 @@
+/* C ABI of the B200 permutohedral-lattice filter library (libpl_lattice.so).
+ *
+ * Plain pointers and sizes only.  Every pointer named "device" is a CUDA device pointer of the
+ * current device; everything runs stream-ordered on `stream` (a cudaStream_t passed as void*).
+ * Unless a comment says otherwise no call synchronises with the host, allocates, or keeps state
+ * between calls: the caller owns inputs, outputs and the workspace.  All calls return a pl_status.
+ *
+ * Each entry point names the reference interface it replaces (paths inside
+ * MiguelMonteiro/permutohedral_lattice).
+ */
+#ifndef PL_LATTICE_H
+#define PL_LATTICE_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum pl_status {
+    PL_OK = 0,
+    PL_INVALID_ARGUMENT = 1,    /* null pointer, negative size, size beyond 32-bit indexing */
+    PL_UNSUPPORTED_DIMS = 2,    /* (pd, vd) without a compiled instantiation; see pl_supported */
+    PL_WORKSPACE_TOO_SMALL = 3, /* workspace_bytes below pl_workspace_bytes for these sizes */
+    PL_CAPACITY_EXCEEDED = 4,   /* more lattice entries than max_entries allowed (device-side) */
+    PL_CUDA_ERROR = 5,          /* a CUDA runtime call failed; see pl_last_cuda_error */
+    PL_INTERNAL_ERROR = 6       /* a bounded device loop gave up (should not happen) */
+} pl_status;
+
+/* Accumulation order of the splat stage. */
+typedef enum pl_mode {
+    PL_MODE_ATOMIC = 0,        /* floating-point atomics; sums differ run to run in the last bits */
+    PL_MODE_DETERMINISTIC = 1  /* sorted, segmented reduction; bitwise reproducible */
+} pl_mode;
+
+/* Counters read back from a workspace after a call (pl_lattice_stats). */
+typedef struct pl_stats {
+    int64_t num_vertices;  /* distinct lattice vertices over the whole batch */
+    int64_t num_entries;   /* tile-local vertex entries (>= num_vertices) */
+    int64_t table_slots;   /* hash table capacity chosen on the device for this call */
+    int32_t device_status; /* pl_status recorded by the kernels (PL_OK, PL_CAPACITY_EXCEEDED, ...) */
+    int32_t reserved;
+} pl_stats;
+
+/* 1 if position dimension pd and value dimension vd (= input channels + 1) can be filtered.
+ * Replaces the build-time SPATIAL_DIMS / INPUT_CHANNELS / REFERENCE_CHANNELS selection of
+ * src/LatticeFilterKernel.cu:30-38,87-100 (one compiled pair, LOG(FATAL) otherwise). */
+int pl_supported(int pd, int vd);
+
+const char* pl_strerror(int status);
+
+/* Text of the last CUDA error seen by this thread inside the library ("" if none). */
+const char* pl_last_cuda_error(void);
+
+/* Bytes of device workspace for `batch` items of `n` points each.  spatial_dims (HOST array, product
+ * n) must be the one later given to pl_lattice_filter_f32; pass NULL for pl_filter_f32 (points are
+ * then tiled in index order).  max_entries bounds the lattice entries the call may create over the
+ * whole batch; 0 means the worst case batch*n*(pd+1), which can never overflow.  Replaces the
+ * scratch allocations of PermutohedralLatticeGPU's constructor
+ * (src/PermutohedralLatticeGPU.cuh:434-451) and src/DeviceMemoryAllocator.h:47-120. */
+int pl_workspace_bytes(int batch, int n, int pd, int vd, int n_spatial_dims, const int* spatial_dims,
+                       int64_t max_entries, size_t* bytes);
+
+/* positions[n*pd] (device) <- feature vectors: for each spatial dimension s (row-major pixel order,
+ * last dimension fastest) coordinate / spatial_std, then reference[c] / feature_std.
+ * spatial_dims is a HOST array.  reference may be NULL when n_reference_channels == 0.
+ * Replaces ComputeKernel<GPUDevice,T>::operator() (src/LatticeFilterKernel.h:40-54,
+ * src/LatticeFilterKernel.cu:44-68) and compute_bilateral_kernel_gpu / compute_spatial_kernel_gpu
+ * (Tests/bilateral_filter_gpu.h:8-19, Tests/PermutohedralLatticeGPU.cu:19-42). */
+int pl_compute_positions_f32(const float* reference, float* positions, int n,
+                             int n_reference_channels, int n_spatial_dims, const int* spatial_dims,
+                             float spatial_std, float feature_std, void* stream);
+
+/* output[batch*n*(vd-1)] <- lattice filter of input[batch*n*(vd-1)] at positions[batch*n*pd]
+ * (all device, item-major, channels last).  Each batch item is an independent lattice.
+ * reverse != 0 runs the blur axes pd..0 (the reference's gradient definition).
+ * Replaces LatticeFilter<GPUDevice,T>::operator() (src/LatticeFilterKernel.h:28-38,
+ * src/LatticeFilterKernel.cu:75-101), PermutohedralLatticeGPU::filter
+ * (src/PermutohedralLatticeGPU.cuh:454-479) and lattice_filter_gpu (Tests/PermutohedralLatticeGPU.cu:6-16),
+ * one call per batch instead of one per item. */
+int pl_filter_f32(float* output, const float* input, const float* positions, int batch, int n,
+                  int pd, int vd, int reverse, void* workspace, size_t workspace_bytes,
+                  int64_t max_entries, int mode, void* stream);
+
+/* The whole op on device tensors input[batch, *spatial_dims, n_input_channels] and
+ * reference[batch, *spatial_dims, n_reference_channels]: features are built on the fly (never
+ * written to memory).  bilateral != 0: pd = n_spatial_dims + n_reference_channels, coordinates
+ * divided by theta_alpha, reference channels by theta_beta.  bilateral == 0: pd = n_spatial_dims,
+ * coordinates divided by theta_gamma, reference unused (may be NULL).  spatial_dims is a HOST array.
+ * Replaces LatticeFilterOp<GPUDevice,T>::Compute (src/LatticeFilterKernel.cpp:98-181) for the
+ * op registered at src/LatticeFilterKernel.cpp:30-43. */
+int pl_lattice_filter_f32(float* output, const float* input, const float* reference, int batch,
+                          int n_spatial_dims, const int* spatial_dims, int n_input_channels,
+                          int n_reference_channels, int bilateral, float theta_alpha,
+                          float theta_beta, float theta_gamma, int reverse, void* workspace,
+                          size_t workspace_bytes, int64_t max_entries, int mode, void* stream);
+
+/* Copies the counters of the last call that used `workspace` to the host.  SYNCHRONISES `stream`.
+ * Returns PL_OK when read; the call's own outcome is stats->device_status.
+ * No counterpart in the reference (it prints or exits: src/PermutohedralLatticeGPU.cuh:49-55,442-445). */
+int pl_lattice_stats(const void* workspace, pl_stats* stats, void* stream);
+
+/* Lattice structure of the last call that used `workspace`, for verification (all outputs device,
+ * any may be NULL): vertex_keys[num_vertices*pd] int16 and vertex_item[num_vertices] (batch item of
+ * each vertex), pixel_vertex[batch*n*(pd+1)] (vertex index of each point's simplex corners,
+ * remainder ascending) and pixel_weight[batch*n*(pd+1)] (barycentric weights).  The positions /
+ * reference arguments must be the ones given to that call (pass positions for pl_filter_f32,
+ * reference + geometry for pl_lattice_filter_f32; the unused one NULL).  vertex arrays must hold
+ * max_vertices rows; rows beyond num_vertices are left untouched.
+ * Corresponds to HashTableCPU::getKeys and the MatrixEntry records
+ * (src/PermutohedralLatticeCPU.h:153-154,187-191). */
+int pl_export_lattice(const void* workspace, const float* positions, const float* reference,
+                      int batch, int n, int pd, int vd, int n_spatial_dims, const int* spatial_dims,
+                      int n_reference_channels, float spatial_std, float feature_std,
+                      int64_t max_entries, int64_t max_vertices, int16_t* vertex_keys,
+                      int32_t* vertex_item, int32_t* pixel_vertex, float* pixel_weight,
+                      void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PL_LATTICE_H */

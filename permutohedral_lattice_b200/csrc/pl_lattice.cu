@@ -1,0 +1,1009 @@
+// B200 (sm_100a) permutohedral-lattice filter: kernels and the C ABI of include/pl_lattice.h.
+//
+// Pipeline of one call (whole batch in every launch, nothing synchronises with the host):
+//
+//   build_tiles     one CTA per tile of TP points: features -> enclosing simplex -> pd+1 vertex keys
+//                   per point; the tile's keys are de-duplicated in a shared-memory hash; the
+//                   distinct keys become a contiguous run of "entries" in a global list and every
+//                   splat records the 16-bit index of its entry inside the tile.
+//   clear_table     sizes the global hash table from the entry count (on the device) and clears it.
+//   insert_entries  one CAS per entry into the table; the first entry of a key owns a new vertex.
+//   link_vertices   entry -> vertex index; the +-1 neighbours of every vertex along each of the
+//                   pd+1 axes; zeroes the value rows.
+//   splat_tiles     one CTA per tile: barycentric weights recomputed, values accumulated per entry
+//                   in shared memory, one row of global atomics per entry.
+//   blur_axis       pd+1 launches: V'[v] = (V[n1] + 2 V[v] + V[n2]) / 4, Jacobi, ping-pong buffers.
+//   slice_tiles     one CTA per tile: the tile's vertex rows staged in shared memory, each point
+//                   interpolates, divides by the homogeneous channel and writes its output row.
+//
+// A table slot is one 64-bit word (32-bit hash tag | index of the owning entry); full keys are
+// compared through the entry list, which a previous launch has completely written, so there are no
+// locks, no waiting and no duplicate vertices.  All device loops are bounded.
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <string.h>
+
+#include "../../include/pl_lattice.h"
+#include "simplex.cuh"
+
+namespace pl {
+
+typedef unsigned long long u64;
+typedef unsigned int u32;
+typedef unsigned short u16;
+
+constexpr u64 EMPTY_SLOT = ~0ull;
+constexpr int MAX_SDIMS = 8;
+constexpr int MAX_PD = 16;
+
+// ---------------------------------------------------------------------------------------------
+// Geometry of a call: how points map to tiles and how features are produced.
+// ---------------------------------------------------------------------------------------------
+struct Geom {
+    int batch, n;           // items, points per item
+    int W, H, outer;        // n = outer * H * W (W fastest)
+    int TX, TY;             // tile = TY rows of TX points, TX * TY = TP
+    int tiles_x, tiles_y, tiles_per_item, num_tiles;
+    int n_sdims, R;         // op path: spatial dims and reference channels (pd = n_sdims + R)
+    int sdims[MAX_SDIMS];
+    float spatial_std, feature_std;
+    int from_positions;     // 1: features are read from a positions array
+    float scale[MAX_PD];    // host-computed scale factors (double arithmetic rounded to float)
+};
+
+struct Header {   // first 256 bytes of the workspace
+    u32 num_entries;
+    u32 num_vertices;
+    u32 status;
+    u32 table_log2;
+    u32 pad[60];
+};
+
+struct Layout {   // byte offsets into the workspace
+    size_t tile_info, rec, list_keys, list_ref, vid, vowner, table, nbr, v0, v1, total;
+    u64 max_entries;   // capacity of entry- and vertex-indexed arrays
+    u64 table_slots;   // allocated slots (power of two)
+};
+
+template <int KW>
+struct alignas((KW % 2 == 0) ? 16 : 8) Key {
+    u64 w[KW];
+};
+
+template <int PD>
+struct Cfg {
+    static constexpr int KW = (PD + 1 + 3) / 4;          // 16-bit fields: PD coordinates + item
+    static constexpr int TP = (PD <= 8) ? 256 : 128;     // points per tile = threads per CTA
+    static constexpr int SPLATS = TP * (PD + 1);
+    static constexpr int LS = (2 * SPLATS <= 1024)   ? 1024
+                              : (2 * SPLATS <= 2048) ? 2048
+                              : (2 * SPLATS <= 4096) ? 4096
+                              : (2 * SPLATS <= 8192) ? 8192
+                                                     : 16384;   // shared hash slots (>= 2 * SPLATS)
+    static constexpr size_t BUILD_SMEM = sizeof(Key<KW>) * SPLATS + sizeof(int) * LS + sizeof(u16) * SPLATS;
+};
+
+template <int KW>
+__device__ __forceinline__ u64 hash_key(const Key<KW>& k) {
+    u64 h = 0x9E3779B97F4A7C15ull;
+#pragma unroll
+    for (int j = 0; j < KW; j++) {
+        h ^= k.w[j];
+        h *= 0xFF51AFD7ED558CCDull;
+        h ^= h >> 32;
+    }
+    h *= 0xC4CEB9FE1A85EC53ull;
+    h ^= h >> 29;
+    return h;
+}
+
+template <int KW>
+__device__ __forceinline__ bool key_equal(const Key<KW>& a, const Key<KW>& b) {
+    bool eq = true;
+#pragma unroll
+    for (int j = 0; j < KW; j++) eq = eq && (a.w[j] == b.w[j]);
+    return eq;
+}
+
+// 16-bit field f of a key (fields 0..PD-1: coordinates, field PD: batch item).
+template <int KW>
+__device__ __forceinline__ void key_set(Key<KW>& k, int f, u16 v) {
+    k.w[f >> 2] |= (u64)v << (16 * (f & 3));
+}
+template <int KW>
+__device__ __forceinline__ u16 key_get(const Key<KW>& k, int f) {
+    return (u16)(k.w[f >> 2] >> (16 * (f & 3)));
+}
+
+// Point handled by thread `tid` of tile `tile`: item, point index inside the item, validity.
+__device__ __forceinline__ bool tile_point(const Geom& g, int tile, int tid, int& item, int& pix) {
+    item = tile / g.tiles_per_item;
+    int t = tile - item * g.tiles_per_item;
+    int per_plane = g.tiles_x * g.tiles_y;
+    int o = t / per_plane;
+    t -= o * per_plane;
+    int ty = t / g.tiles_x, tx = t - ty * g.tiles_x;
+    int ly = tid / g.TX, lx = tid - ly * g.TX;
+    int y = ty * g.TY + ly, x = tx * g.TX + lx;
+    pix = (o * g.H + y) * g.W + x;
+    return (y < g.H) && (x < g.W);
+}
+
+// Feature vector of a point.  Op path: src/PermutohedralLatticeCPU.h:464-473 (coordinate of each
+// spatial dimension as float divided by spatial_std, reference channel divided by feature_std; IEEE
+// divisions, not reciprocal multiplies).  Positions path: a row of the positions array.
+template <int PD>
+__device__ __forceinline__ void load_features(const Geom& g, const float* __restrict__ positions,
+                                              const float* __restrict__ reference, int item, int pix,
+                                              float* f) {
+    if (g.from_positions) {
+        const float* p = positions + ((size_t)item * g.n + pix) * PD;
+#pragma unroll
+        for (int i = 0; i < PD; i++) f[i] = __ldg(p + i);
+    } else {
+        int divisor = 1;
+#pragma unroll
+        for (int i = PD - 1; i >= 0; i--) {
+            if (i < g.n_sdims) {
+                int c = (pix / divisor) % g.sdims[i];
+                f[i] = PL_FDIV((float)c, g.spatial_std);
+                divisor *= g.sdims[i];
+            } else {
+                f[i] = PL_FDIV(__ldg(reference + ((size_t)item * g.n + pix) * g.R + (i - g.n_sdims)),
+                               g.feature_std);
+            }
+        }
+    }
+}
+
+// Status word of the call, read once per CTA so that every thread takes the same branch even while
+// other CTAs of the same launch are setting error bits.
+__device__ __forceinline__ bool call_failed(const Header* hdr) {
+    __shared__ u32 status_s;
+    if (threadIdx.x == 0) status_s = hdr->status;
+    __syncthreads();
+    return status_s != 0;
+}
+
+// ---------------------------------------------------------------------------------------------
+// build_tiles
+// ---------------------------------------------------------------------------------------------
+template <int PD>
+__global__ void __launch_bounds__(Cfg<PD>::TP)
+build_tiles(Geom g, const float* __restrict__ positions, const float* __restrict__ reference,
+            Header* hdr, int2* __restrict__ tile_info, u16* __restrict__ rec,
+            Key<Cfg<PD>::KW>* __restrict__ list_keys, u32 max_entries) {
+    constexpr int KW = Cfg<PD>::KW, TP = Cfg<PD>::TP, SPLATS = Cfg<PD>::SPLATS, LS = Cfg<PD>::LS;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    Key<KW>* keys_s = reinterpret_cast<Key<KW>*>(smem_raw);
+    int* hslots = reinterpret_cast<int*>(smem_raw + sizeof(Key<KW>) * SPLATS);
+    u16* lidx_s = reinterpret_cast<u16*>(smem_raw + sizeof(Key<KW>) * SPLATS + sizeof(int) * LS);
+    __shared__ int nloc_s, base_s;
+
+    const int tid = threadIdx.x, tile = blockIdx.x;
+    for (int i = tid; i < LS; i += TP) hslots[i] = -1;
+    if (tid == 0) nloc_s = 0;
+
+    int item, pix;
+    const bool valid = tile_point(g, tile, tid, item, pix);
+    if (valid) {
+        float f[PD];
+        load_features<PD>(g, positions, reference, item, pix, f);
+        Simplex<PD> s;
+        find_simplex<PD>(f, g.scale, s);
+#pragma unroll
+        for (int r = 0; r <= PD; r++) {
+            Key<KW> k;
+#pragma unroll
+            for (int j = 0; j < KW; j++) k.w[j] = 0;
+#pragma unroll
+            for (int i = 0; i < PD; i++) key_set<KW>(k, i, (u16)vertex_coord<PD>(s, i, r));
+            key_set<KW>(k, PD, (u16)item);
+            keys_s[r * TP + tid] = k;
+        }
+    }
+    __syncthreads();
+
+    // de-duplicate: the first splat to claim a slot for a key represents it
+    int rep[PD + 1];
+#pragma unroll
+    for (int r = 0; r <= PD; r++) {
+        rep[r] = -1;
+        if (valid) {
+            const int me = r * TP + tid;
+            const Key<KW> k = keys_s[me];
+            u32 s = (u32)hash_key<KW>(k) & (LS - 1);
+            for (int it = 0; it < LS; it++) {
+                int o = hslots[s];
+                if (o < 0) {
+                    o = atomicCAS(&hslots[s], -1, me);
+                    if (o < 0) { rep[r] = me; break; }
+                }
+                if (key_equal<KW>(keys_s[o], k)) { rep[r] = o; break; }
+                s = (s + 1) & (LS - 1);
+            }
+        }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int r = 0; r <= PD; r++) {
+        if (valid && rep[r] == r * TP + tid) lidx_s[r * TP + tid] = (u16)atomicAdd(&nloc_s, 1);
+    }
+    __syncthreads();
+    if (tid == 0) {
+        int cnt = nloc_s;
+        u32 base = atomicAdd(&hdr->num_entries, (u32)cnt);
+        if ((u64)base + (u64)cnt > (u64)max_entries) {
+            atomicOr(&hdr->status, 1u << PL_CAPACITY_EXCEEDED);
+            base_s = -1;
+            tile_info[tile] = make_int2(0, 0);
+        } else {
+            base_s = (int)base;
+            tile_info[tile] = make_int2((int)base, cnt);
+        }
+    }
+    __syncthreads();
+    const int base = base_s;
+    u16* rec_tile = rec + (size_t)tile * SPLATS;
+#pragma unroll
+    for (int r = 0; r <= PD; r++) {
+        const int me = r * TP + tid;
+        u16 l = 0;
+        if (valid && rep[r] >= 0) {
+            l = lidx_s[rep[r]];
+            if (rep[r] == me && base >= 0) list_keys[(size_t)base + l] = keys_s[me];
+        }
+        rec_tile[me] = l;
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// clear_table: table capacity = power of two >= 2 * entries (at least 1024), chosen on the device.
+// ---------------------------------------------------------------------------------------------
+__global__ void clear_table(Header* hdr, u64* __restrict__ table, u32 max_log2) {
+    if (hdr->status != 0) return;
+    u32 need = 2u * hdr->num_entries;
+    u32 lg = 10;
+    while (lg < max_log2 && (1ull << lg) < (u64)need) lg++;
+    if (blockIdx.x == 0 && threadIdx.x == 0) hdr->table_log2 = lg;
+    const u64 cap = 1ull << lg;
+    for (u64 i = (u64)blockIdx.x * blockDim.x + threadIdx.x; i < cap; i += (u64)gridDim.x * blockDim.x)
+        table[i] = EMPTY_SLOT;
+}
+
+// ---------------------------------------------------------------------------------------------
+// insert_entries
+// ---------------------------------------------------------------------------------------------
+// Returns the index of the entry owning `k` in the table, or -1 if absent.
+template <int KW>
+__device__ __forceinline__ int table_find(const u64* __restrict__ table, u64 mask,
+                                          const Key<KW>* __restrict__ list_keys, const Key<KW>& k) {
+    const u64 h = hash_key<KW>(k);
+    const u32 tag = (u32)(h >> 32);
+    u64 s = h & mask;
+    for (u64 it = 0; it <= mask; it++) {
+        const u64 cur = table[s];
+        if (cur == EMPTY_SLOT) return -1;
+        if ((u32)(cur >> 32) == tag) {
+            const u32 o = (u32)cur;
+            if (key_equal<KW>(list_keys[o], k)) return (int)o;
+        }
+        s = (s + 1) & mask;
+    }
+    return -1;
+}
+
+template <int KW>
+__global__ void __launch_bounds__(256)
+insert_entries(Header* hdr, u64* __restrict__ table, const Key<KW>* __restrict__ list_keys,
+               u32* __restrict__ list_ref, u32* __restrict__ vid, u32* __restrict__ vowner) {
+    if (call_failed(hdr)) return;
+    const u32 T = hdr->num_entries;
+    const u64 mask = (1ull << hdr->table_log2) - 1;
+    __shared__ u32 warp_cnt[8];
+    __shared__ u32 block_base;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (u32 start = blockIdx.x * 256u; start < T; start += gridDim.x * 256u) {
+        const u32 t = start + threadIdx.x;
+        bool winner = false;
+        if (t < T) {
+            const Key<KW> k = list_keys[t];
+            const u64 h = hash_key<KW>(k);
+            const u32 tag = (u32)(h >> 32);
+            const u64 mine = ((u64)tag << 32) | (u64)t;
+            u64 s = h & mask;
+            u32 owner = 0xFFFFFFFFu;
+            for (u64 it = 0; it <= mask; it++) {
+                u64 cur = table[s];
+                if (cur == EMPTY_SLOT) {
+                    cur = atomicCAS(&table[s], EMPTY_SLOT, mine);
+                    if (cur == EMPTY_SLOT) { owner = t; winner = true; break; }
+                }
+                if ((u32)(cur >> 32) == tag) {
+                    const u32 o = (u32)cur;
+                    if (key_equal<KW>(list_keys[o], k)) { owner = o; break; }
+                }
+                s = (s + 1) & mask;
+            }
+            if (owner == 0xFFFFFFFFu) {
+                atomicOr(&hdr->status, 1u << PL_INTERNAL_ERROR);
+                owner = t;
+            }
+            list_ref[t] = owner;
+        }
+        // vertex indices: one atomic per CTA and chunk
+        const u32 ballot = __ballot_sync(0xFFFFFFFFu, winner);
+        if (lane == 0) warp_cnt[warp] = __popc(ballot);
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            u32 tot = 0;
+#pragma unroll
+            for (int w = 0; w < 8; w++) { u32 c = warp_cnt[w]; warp_cnt[w] = tot; tot += c; }
+            block_base = tot ? atomicAdd(&hdr->num_vertices, tot) : 0u;
+        }
+        __syncthreads();
+        if (winner) {
+            const u32 v = block_base + warp_cnt[warp] + __popc(ballot & ((1u << lane) - 1u));
+            vid[t] = v;
+            vowner[v] = t;
+        }
+        __syncthreads();
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// link_vertices: entry -> vertex, neighbour table, zeroed value rows
+// ---------------------------------------------------------------------------------------------
+template <int PD>
+__global__ void __launch_bounds__(256)
+link_vertices(Header* hdr, const u64* __restrict__ table,
+              const Key<Cfg<PD>::KW>* __restrict__ list_keys, u32* __restrict__ list_ref,
+              const u32* __restrict__ vid, const u32* __restrict__ vowner, int* __restrict__ nbr,
+              float* __restrict__ v0, u64 max_entries, int vd) {
+    constexpr int KW = Cfg<PD>::KW;
+    if (hdr->status != 0) return;
+    const u32 T = hdr->num_entries, M = hdr->num_vertices;
+    const u64 mask = (1ull << hdr->table_log2) - 1;
+    const u64 gtid = (u64)blockIdx.x * blockDim.x + threadIdx.x;
+    const u64 gsz = (u64)gridDim.x * blockDim.x;
+
+    for (u64 t = gtid; t < T; t += gsz) list_ref[t] = vid[list_ref[t]];
+
+    // neighbours: item (v, axis a, direction d).  Along axis a < PD the neighbour key is every
+    // stored coordinate +1 (d = 0) or -1 (d = 1), except coordinate a which moves by -PD / +PD;
+    // along axis PD no stored coordinate is special (src/PermutohedralLatticeCPU.h:381-388).
+    const u64 items = (u64)M * (PD + 1) * 2;
+    for (u64 e = gtid; e < items; e += gsz) {
+        const u32 v = (u32)(e / (2 * (PD + 1)));
+        const int rem = (int)(e - (u64)v * (2 * (PD + 1)));
+        const int a = rem >> 1, d = rem & 1;
+        const Key<KW> k = list_keys[vowner[v]];
+        Key<KW> nk;
+#pragma unroll
+        for (int j = 0; j < KW; j++) nk.w[j] = 0;
+#pragma unroll
+        for (int i = 0; i < PD; i++) {
+            int c = (int16_t)key_get<KW>(k, i);
+            int step = (i == a) ? -PD : 1;
+            c += d ? -step : step;
+            key_set<KW>(nk, i, (u16)(int16_t)c);
+        }
+        key_set<KW>(nk, PD, key_get<KW>(k, PD));
+        const int o = table_find<KW>(table, mask, list_keys, nk);
+        nbr[((u64)a * max_entries + v) * 2 + d] = (o < 0) ? -1 : (int)vid[o];
+    }
+
+    const u64 cells = (u64)M * vd;
+    for (u64 e = gtid; e < cells; e += gsz) v0[e] = 0.f;
+}
+
+// ---------------------------------------------------------------------------------------------
+// splat_tiles
+// ---------------------------------------------------------------------------------------------
+template <int PD>
+__global__ void __launch_bounds__(Cfg<PD>::TP)
+splat_tiles(Geom g, const float* __restrict__ positions, const float* __restrict__ reference,
+            const float* __restrict__ input, const Header* hdr, const int2* __restrict__ tile_info,
+            const u16* __restrict__ rec, const u32* __restrict__ list_ref, float* __restrict__ v0,
+            int vd, int rows_cap) {
+    constexpr int TP = Cfg<PD>::TP, SPLATS = Cfg<PD>::SPLATS;
+    extern __shared__ __align__(16) float rows[];   // [rows_cap][vd]
+    if (call_failed(hdr)) return;
+    const int tid = threadIdx.x, tile = blockIdx.x;
+    const int2 info = tile_info[tile];
+    const int base = info.x, cnt = info.y;
+    const int nrows = min(cnt, rows_cap);
+    for (int i = tid; i < nrows * vd; i += TP) rows[i] = 0.f;
+    __syncthreads();
+
+    int item, pix;
+    const bool valid = tile_point(g, tile, tid, item, pix);
+    if (valid) {
+        float f[PD];
+        load_features<PD>(g, positions, reference, item, pix, f);
+        Simplex<PD> s;
+        find_simplex<PD>(f, g.scale, s);
+        float w[PD + 1];
+        barycentric<PD>(s, w);
+        int l[PD + 1];
+        const u16* rec_tile = rec + (size_t)tile * SPLATS;
+#pragma unroll
+        for (int r = 0; r <= PD; r++) l[r] = rec_tile[r * TP + tid];
+        const int C = vd - 1;
+        const float* in_row = input + ((size_t)item * g.n + pix) * C;
+        for (int j = 0; j < vd; j++) {
+            const float x = (j < C) ? __ldg(in_row + j) : 1.f;
+#pragma unroll
+            for (int r = 0; r <= PD; r++) {
+                const float c = (j < C) ? PL_FMUL(w[r], x) : w[r];
+                if (l[r] < nrows)
+                    atomicAdd(&rows[l[r] * vd + j], c);
+                else
+                    atomicAdd(&v0[(size_t)list_ref[base + l[r]] * vd + j], c);
+            }
+        }
+    }
+    __syncthreads();
+    for (int i = tid; i < nrows * vd; i += TP) {
+        const int l = i / vd, j = i - l * vd;
+        atomicAdd(&v0[(size_t)list_ref[base + l] * vd + j], rows[i]);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// blur_axis: one [1 2 1]/4 pass along lattice axis `axis` (src/PermutohedralLatticeCPU.h:403-405:
+// the three products and their sum in double, one rounding to float).  VW floats per thread.
+// ---------------------------------------------------------------------------------------------
+template <int VW>
+struct VecT;
+template <> struct VecT<1> { typedef float type; };
+template <> struct VecT<2> { typedef float2 type; };
+template <> struct VecT<4> { typedef float4 type; };
+
+__device__ __forceinline__ float mix3(float a, float b, float c) {
+    return (float)PL_DADD(PL_DADD(PL_DMUL(0.25, (double)a), PL_DMUL(0.5, (double)b)),
+                          PL_DMUL(0.25, (double)c));
+}
+
+template <int VW>
+__global__ void __launch_bounds__(256)
+blur_axis(const Header* hdr, const int* __restrict__ nbr_axis, const float* __restrict__ src,
+          float* __restrict__ dst, int vd) {
+    typedef typename VecT<VW>::type V;
+    if (hdr->status != 0) return;
+    const u32 M = hdr->num_vertices;
+    const int per_row = vd / VW;
+    const u64 items = (u64)M * per_row;
+    const V* __restrict__ s = reinterpret_cast<const V*>(src);
+    V* __restrict__ d = reinterpret_cast<V*>(dst);
+    const int2* __restrict__ nb = reinterpret_cast<const int2*>(nbr_axis);
+    for (u64 e = (u64)blockIdx.x * blockDim.x + threadIdx.x; e < items;
+         e += (u64)gridDim.x * blockDim.x) {
+        const u32 v = (u32)(e / per_row);
+        const int j = (int)(e - (u64)v * per_row);
+        const int2 n = __ldg(nb + v);
+        const V b = s[e];
+        V a, c;
+        if constexpr (VW == 1) {
+            a = (n.x >= 0) ? s[(u64)n.x * per_row + j] : 0.f;
+            c = (n.y >= 0) ? s[(u64)n.y * per_row + j] : 0.f;
+            d[e] = mix3(a, b, c);
+        } else if constexpr (VW == 2) {
+            a = (n.x >= 0) ? s[(u64)n.x * per_row + j] : make_float2(0.f, 0.f);
+            c = (n.y >= 0) ? s[(u64)n.y * per_row + j] : make_float2(0.f, 0.f);
+            d[e] = make_float2(mix3(a.x, b.x, c.x), mix3(a.y, b.y, c.y));
+        } else {
+            a = (n.x >= 0) ? s[(u64)n.x * per_row + j] : make_float4(0.f, 0.f, 0.f, 0.f);
+            c = (n.y >= 0) ? s[(u64)n.y * per_row + j] : make_float4(0.f, 0.f, 0.f, 0.f);
+            d[e] = make_float4(mix3(a.x, b.x, c.x), mix3(a.y, b.y, c.y), mix3(a.z, b.z, c.z),
+                               mix3(a.w, b.w, c.w));
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// slice_tiles (src/PermutohedralLatticeCPU.h:333-352: float multiply-then-add per remainder in
+// ascending order, reciprocal of the homogeneous channel in double, one multiply per channel)
+// ---------------------------------------------------------------------------------------------
+template <int PD>
+__global__ void __launch_bounds__(Cfg<PD>::TP)
+slice_tiles(Geom g, const float* __restrict__ positions, const float* __restrict__ reference,
+            float* __restrict__ output, const Header* hdr, const int2* __restrict__ tile_info,
+            const u16* __restrict__ rec, const u32* __restrict__ list_ref,
+            const float* __restrict__ vsrc, int vd, int rows_cap) {
+    constexpr int TP = Cfg<PD>::TP, SPLATS = Cfg<PD>::SPLATS;
+    extern __shared__ __align__(16) float rows[];   // [rows_cap][vd]
+    if (call_failed(hdr)) return;
+    const int tid = threadIdx.x, tile = blockIdx.x;
+    const int2 info = tile_info[tile];
+    const int base = info.x, cnt = info.y;
+    const int nrows = min(cnt, rows_cap);
+    for (int i = tid; i < nrows * vd; i += TP) {
+        const int l = i / vd, j = i - l * vd;
+        rows[i] = vsrc[(size_t)list_ref[base + l] * vd + j];
+    }
+    __syncthreads();
+
+    int item, pix;
+    const bool valid = tile_point(g, tile, tid, item, pix);
+    if (!valid) return;
+    float f[PD];
+    load_features<PD>(g, positions, reference, item, pix, f);
+    Simplex<PD> s;
+    find_simplex<PD>(f, g.scale, s);
+    float w[PD + 1];
+    barycentric<PD>(s, w);
+    const u16* rec_tile = rec + (size_t)tile * SPLATS;
+    const float* rp[PD + 1];
+#pragma unroll
+    for (int r = 0; r <= PD; r++) {
+        const int l = rec_tile[r * TP + tid];
+        rp[r] = (l < nrows) ? (rows + l * vd) : (vsrc + (size_t)list_ref[base + l] * vd);
+    }
+    const int C = vd - 1;
+    float norm = 0.f;
+#pragma unroll
+    for (int r = 0; r <= PD; r++) norm = PL_FADD(norm, PL_FMUL(w[r], rp[r][C]));
+    const float inv = (float)(1.0 / (double)norm);
+    float* out_row = output + ((size_t)item * g.n + pix) * C;
+    for (int j = 0; j < C; j++) {
+        float acc = 0.f;
+#pragma unroll
+        for (int r = 0; r <= PD; r++) acc = PL_FADD(acc, PL_FMUL(w[r], rp[r][j]));
+        out_row[j] = PL_FMUL(acc, inv);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// positions kernel (the standalone ComputeKernel functor) and lattice export
+// ---------------------------------------------------------------------------------------------
+__global__ void positions_kernel(const float* __restrict__ reference, float* __restrict__ positions,
+                                 int n, int R, int n_sdims, Geom g) {
+    const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= n) return;
+    const int pd = n_sdims + R;
+    int divisor = 1;
+    for (int s = n_sdims - 1; s >= 0; s--) {
+        positions[(size_t)pd * idx + s] = PL_FDIV((float)((idx / divisor) % g.sdims[s]), g.spatial_std);
+        divisor *= g.sdims[s];
+    }
+    for (int c = 0; c < R; c++)
+        positions[(size_t)pd * idx + n_sdims + c] = PL_FDIV(reference[(size_t)idx * R + c], g.feature_std);
+}
+
+template <int PD>
+__global__ void __launch_bounds__(Cfg<PD>::TP)
+export_points(Geom g, const float* __restrict__ positions, const float* __restrict__ reference,
+              const Header* hdr, const int2* __restrict__ tile_info, const u16* __restrict__ rec,
+              const u32* __restrict__ list_ref, int32_t* __restrict__ pixel_vertex,
+              float* __restrict__ pixel_weight) {
+    constexpr int TP = Cfg<PD>::TP, SPLATS = Cfg<PD>::SPLATS;
+    if (hdr->status != 0) return;
+    const int tid = threadIdx.x, tile = blockIdx.x;
+    int item, pix;
+    if (!tile_point(g, tile, tid, item, pix)) return;
+    const int base = tile_info[tile].x;
+    float f[PD];
+    load_features<PD>(g, positions, reference, item, pix, f);
+    Simplex<PD> s;
+    find_simplex<PD>(f, g.scale, s);
+    float w[PD + 1];
+    barycentric<PD>(s, w);
+    const u16* rec_tile = rec + (size_t)tile * SPLATS;
+    const size_t o = ((size_t)item * g.n + pix) * (PD + 1);
+#pragma unroll
+    for (int r = 0; r <= PD; r++) {
+        if (pixel_vertex) pixel_vertex[o + r] = (int32_t)list_ref[base + rec_tile[r * TP + tid]];
+        if (pixel_weight) pixel_weight[o + r] = w[r];
+    }
+}
+
+template <int PD>
+__global__ void export_vertices(const Header* hdr, const Key<Cfg<PD>::KW>* __restrict__ list_keys,
+                                const u32* __restrict__ vowner, long long max_vertices,
+                                int16_t* __restrict__ vertex_keys, int32_t* __restrict__ vertex_item) {
+    constexpr int KW = Cfg<PD>::KW;
+    if (hdr->status != 0) return;
+    const u32 M = hdr->num_vertices;
+    for (u64 v = (u64)blockIdx.x * blockDim.x + threadIdx.x; v < M && v < (u64)max_vertices;
+         v += (u64)gridDim.x * blockDim.x) {
+        const Key<KW> k = list_keys[vowner[v]];
+        if (vertex_keys) {
+#pragma unroll
+            for (int i = 0; i < PD; i++) vertex_keys[v * PD + i] = (int16_t)key_get<KW>(k, i);
+        }
+        if (vertex_item) vertex_item[v] = (int32_t)key_get<KW>(k, PD);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------------------
+static thread_local char g_cuda_error[256] = "";
+
+static int cuda_fail(cudaError_t e, const char* where) {
+    snprintf(g_cuda_error, sizeof(g_cuda_error), "%s: %s", where, cudaGetErrorString(e));
+    return PL_CUDA_ERROR;
+}
+#define PL_CUDA(call)                                   \
+    do {                                                \
+        cudaError_t e_ = (call);                        \
+        if (e_ != cudaSuccess) return cuda_fail(e_, #call); \
+    } while (0)
+
+static size_t align_up(size_t x) { return (x + 255) & ~(size_t)255; }
+
+static int tp_of(int pd) { return pd <= 8 ? 256 : 128; }
+static int kw_of(int pd) { return (pd + 1 + 3) / 4; }
+
+static bool pd_supported(int pd) {
+    return pd == 1 || pd == 2 || pd == 3 || pd == 4 || pd == 5 || pd == 6 || pd == 7 || pd == 8 ||
+           pd == 16;
+}
+
+// src/PermutohedralLatticeCPU.h:194-217, T = float: double arithmetic rounded to float.
+static void scale_factors(int pd, float* out) {
+    float inv_std_dev = (float)((pd + 1) * sqrt(2.0 / 3));
+    for (int i = 0; i < pd; i++)
+        out[i] = (float)(1.0 / sqrt((double)((i + 1) * (i + 2))) * (double)inv_std_dev);
+}
+
+static int make_geom(Geom& g, int batch, int n, int pd, int n_sdims, const int* sdims, int R,
+                     float spatial_std, float feature_std, bool from_positions) {
+    memset(&g, 0, sizeof(g));
+    g.batch = batch;
+    g.n = n;
+    g.from_positions = from_positions ? 1 : 0;
+    g.n_sdims = n_sdims;
+    g.R = R;
+    g.spatial_std = spatial_std;
+    g.feature_std = feature_std;
+    const int tp = tp_of(pd);
+    if (from_positions || n_sdims < 2) {
+        g.W = n; g.H = 1; g.outer = 1;
+        g.TX = tp; g.TY = 1;
+    } else {
+        g.W = sdims[n_sdims - 1];
+        g.H = sdims[n_sdims - 2];
+        g.outer = 1;
+        for (int i = 0; i < n_sdims - 2; i++) g.outer *= sdims[i];
+        g.TX = 16;
+        while (g.TX > 1 && g.TX / 2 >= g.W) g.TX /= 2;   // narrow images: narrower, taller tiles
+        g.TY = tp / g.TX;
+    }
+    for (int i = 0; i < n_sdims; i++) g.sdims[i] = sdims[i];
+    g.tiles_x = (g.W + g.TX - 1) / g.TX;
+    g.tiles_y = (g.H + g.TY - 1) / g.TY;
+    long long per_item = (long long)g.tiles_x * g.tiles_y * g.outer;
+    long long total = per_item * batch;
+    if (total > 0x7FFFFFFFll) return PL_INVALID_ARGUMENT;
+    g.tiles_per_item = (int)per_item;
+    g.num_tiles = (int)total;
+    scale_factors(pd, g.scale);
+    return PL_OK;
+}
+
+static int make_layout(Layout& L, const Geom& g, int pd, int vd, int64_t max_entries_arg) {
+    const u64 S = (u64)g.batch * (u64)g.n * (u64)(pd + 1);
+    if (S >= 0x7FFFFFF0ull) return PL_INVALID_ARGUMENT;
+    u64 E = (max_entries_arg <= 0 || (u64)max_entries_arg > S) ? S : (u64)max_entries_arg;
+    if (E < 1) E = 1;
+    L.max_entries = E;
+    u64 slots = 1024;
+    while (slots < 2 * E) slots <<= 1;
+    L.table_slots = slots;
+    const size_t tile_splats = (size_t)tp_of(pd) * (pd + 1);
+    size_t off = align_up(sizeof(Header));
+    L.tile_info = off; off += align_up(sizeof(int2) * (size_t)g.num_tiles);
+    L.rec = off;       off += align_up(sizeof(u16) * tile_splats * (size_t)g.num_tiles);
+    L.list_keys = off; off += align_up(sizeof(u64) * kw_of(pd) * E);
+    L.list_ref = off;  off += align_up(sizeof(u32) * E);
+    L.vid = off;       off += align_up(sizeof(u32) * E);
+    L.vowner = off;    off += align_up(sizeof(u32) * E);
+    L.table = off;     off += align_up(sizeof(u64) * slots);
+    L.nbr = off;       off += align_up(sizeof(int) * 2 * (size_t)(pd + 1) * E);
+    L.v0 = off;        off += align_up(sizeof(float) * (size_t)vd * E);
+    L.v1 = off;        off += align_up(sizeof(float) * (size_t)vd * E);
+    L.total = off;
+    return PL_OK;
+}
+
+static int g_num_sms = 0;
+static int num_sms() {
+    if (g_num_sms == 0) {
+        int dev = 0, sms = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess ||
+            cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
+            sms = 148;
+        g_num_sms = sms;
+    }
+    return g_num_sms;
+}
+
+// Rows of the per-tile shared-memory value cache used by splat_tiles / slice_tiles.
+static int rows_cap_for(int pd, int vd) {
+    const int splats = tp_of(pd) * (pd + 1);
+    int cap = (48 * 1024) / (vd * (int)sizeof(float));
+    if (cap > splats) cap = splats;
+    if (cap < 1) cap = 1;
+    return cap;
+}
+
+template <int PD>
+static int run_filter(const Geom& g, float* output, const float* input, const float* positions,
+                      const float* reference, int vd, int reverse, void* workspace,
+                      const Layout& L, cudaStream_t st) {
+    constexpr int KW = Cfg<PD>::KW, TP = Cfg<PD>::TP;
+    unsigned char* ws = static_cast<unsigned char*>(workspace);
+    Header* hdr = reinterpret_cast<Header*>(ws);
+    int2* tile_info = reinterpret_cast<int2*>(ws + L.tile_info);
+    u16* rec = reinterpret_cast<u16*>(ws + L.rec);
+    Key<KW>* list_keys = reinterpret_cast<Key<KW>*>(ws + L.list_keys);
+    u32* list_ref = reinterpret_cast<u32*>(ws + L.list_ref);
+    u32* vid = reinterpret_cast<u32*>(ws + L.vid);
+    u32* vowner = reinterpret_cast<u32*>(ws + L.vowner);
+    u64* table = reinterpret_cast<u64*>(ws + L.table);
+    int* nbr = reinterpret_cast<int*>(ws + L.nbr);
+    float* v0 = reinterpret_cast<float*>(ws + L.v0);
+    float* v1 = reinterpret_cast<float*>(ws + L.v1);
+
+    PL_CUDA(cudaMemsetAsync(hdr, 0, sizeof(Header), st));
+    if (g.num_tiles == 0) return PL_OK;
+
+    // per device and cheap, so set on every call rather than cached
+    PL_CUDA(cudaFuncSetAttribute(build_tiles<PD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)Cfg<PD>::BUILD_SMEM));
+    const int sms = num_sms();
+    const int wide = sms * 8;
+    int table_log2 = 0;
+    while ((1ull << table_log2) < L.table_slots) table_log2++;
+
+    build_tiles<PD><<<g.num_tiles, TP, Cfg<PD>::BUILD_SMEM, st>>>(
+        g, positions, reference, hdr, tile_info, rec, list_keys, (u32)L.max_entries);
+    clear_table<<<wide, 256, 0, st>>>(hdr, table, (u32)table_log2);
+    insert_entries<KW><<<wide, 256, 0, st>>>(hdr, table, list_keys, list_ref, vid, vowner);
+    link_vertices<PD><<<wide, 256, 0, st>>>(hdr, table, list_keys, list_ref, vid, vowner, nbr, v0,
+                                            L.max_entries, vd);
+    const int rows_cap = rows_cap_for(PD, vd);
+    const size_t rows_smem = (size_t)rows_cap * vd * sizeof(float);
+    splat_tiles<PD><<<g.num_tiles, TP, rows_smem, st>>>(g, positions, reference, input, hdr,
+                                                        tile_info, rec, list_ref, v0, vd, rows_cap);
+    float* src = v0;
+    float* dst = v1;
+    for (int step = 0; step <= PD; step++) {
+        const int axis = reverse ? PD - step : step;
+        const int* nb = nbr + (size_t)axis * L.max_entries * 2;
+        if (vd % 4 == 0)
+            blur_axis<4><<<wide, 256, 0, st>>>(hdr, nb, src, dst, vd);
+        else if (vd % 2 == 0)
+            blur_axis<2><<<wide, 256, 0, st>>>(hdr, nb, src, dst, vd);
+        else
+            blur_axis<1><<<wide, 256, 0, st>>>(hdr, nb, src, dst, vd);
+        float* tmp = src; src = dst; dst = tmp;
+    }
+    slice_tiles<PD><<<g.num_tiles, TP, rows_smem, st>>>(g, positions, reference, output, hdr,
+                                                        tile_info, rec, list_ref, src, vd, rows_cap);
+    PL_CUDA(cudaGetLastError());
+    return PL_OK;
+}
+
+template <int PD>
+static int run_export(const Geom& g, const float* positions, const float* reference, const void* workspace,
+                      const Layout& L, long long max_vertices, int16_t* vertex_keys,
+                      int32_t* vertex_item, int32_t* pixel_vertex, float* pixel_weight,
+                      cudaStream_t st) {
+    constexpr int KW = Cfg<PD>::KW, TP = Cfg<PD>::TP;
+    const unsigned char* ws = static_cast<const unsigned char*>(workspace);
+    const Header* hdr = reinterpret_cast<const Header*>(ws);
+    if (g.num_tiles == 0) return PL_OK;
+    if (pixel_vertex || pixel_weight)
+        export_points<PD><<<g.num_tiles, TP, 0, st>>>(
+            g, positions, reference, hdr, reinterpret_cast<const int2*>(ws + L.tile_info),
+            reinterpret_cast<const u16*>(ws + L.rec), reinterpret_cast<const u32*>(ws + L.list_ref),
+            pixel_vertex, pixel_weight);
+    if (vertex_keys || vertex_item)
+        export_vertices<PD><<<num_sms() * 4, 256, 0, st>>>(
+            hdr, reinterpret_cast<const Key<KW>*>(ws + L.list_keys),
+            reinterpret_cast<const u32*>(ws + L.vowner), max_vertices, vertex_keys, vertex_item);
+    PL_CUDA(cudaGetLastError());
+    return PL_OK;
+}
+
+#define PL_DISPATCH_PD(pd, CALL)            \
+    switch (pd) {                           \
+        case 1: return CALL(1);             \
+        case 2: return CALL(2);             \
+        case 3: return CALL(3);             \
+        case 4: return CALL(4);             \
+        case 5: return CALL(5);             \
+        case 6: return CALL(6);             \
+        case 7: return CALL(7);             \
+        case 8: return CALL(8);             \
+        case 16: return CALL(16);           \
+        default: return PL_UNSUPPORTED_DIMS; \
+    }
+
+static int filter_common(const Geom& g, float* output, const float* input, const float* positions,
+                         const float* reference, int pd, int vd, int reverse, void* workspace,
+                         size_t workspace_bytes, int64_t max_entries, int mode, cudaStream_t st) {
+    if (mode != PL_MODE_ATOMIC) return PL_INVALID_ARGUMENT;
+    Layout L;
+    int rc = make_layout(L, g, pd, vd, max_entries);
+    if (rc != PL_OK) return rc;
+    if (workspace_bytes < L.total) return PL_WORKSPACE_TOO_SMALL;
+#define CALL(P) run_filter<P>(g, output, input, positions, reference, vd, reverse, workspace, L, st)
+    PL_DISPATCH_PD(pd, CALL)
+#undef CALL
+}
+
+}  // namespace pl
+
+using namespace pl;
+
+extern "C" {
+
+int pl_supported(int pd, int vd) { return pd_supported(pd) && vd >= 2 && vd <= 4096 ? 1 : 0; }
+
+const char* pl_strerror(int status) {
+    switch (status) {
+        case PL_OK: return "ok";
+        case PL_INVALID_ARGUMENT: return "invalid argument";
+        case PL_UNSUPPORTED_DIMS: return "unsupported (pd, vd)";
+        case PL_WORKSPACE_TOO_SMALL: return "workspace too small";
+        case PL_CAPACITY_EXCEEDED: return "lattice entries exceed max_entries";
+        case PL_CUDA_ERROR: return "CUDA error";
+        case PL_INTERNAL_ERROR: return "internal error (bounded device loop gave up)";
+    }
+    return "unknown status";
+}
+
+const char* pl_last_cuda_error(void) { return g_cuda_error; }
+
+int pl_workspace_bytes(int batch, int n, int pd, int vd, int n_spatial_dims, const int* spatial_dims,
+                       int64_t max_entries, size_t* bytes) {
+    if (!bytes || batch < 0 || n < 0 || batch > 65535) return PL_INVALID_ARGUMENT;
+    if (!pl_supported(pd, vd)) return PL_UNSUPPORTED_DIMS;
+    Geom g;
+    int rc;
+    if (spatial_dims) {
+        if (n_spatial_dims < 1 || n_spatial_dims > MAX_SDIMS || n_spatial_dims > pd) return PL_INVALID_ARGUMENT;
+        long long prod = 1;
+        for (int i = 0; i < n_spatial_dims; i++) prod *= spatial_dims[i];
+        if (prod != n) return PL_INVALID_ARGUMENT;
+        rc = make_geom(g, batch, n, pd, n_spatial_dims, spatial_dims, pd - n_spatial_dims, 1.f, 1.f, false);
+    } else {
+        int one = n;
+        rc = make_geom(g, batch, n, pd, 1, &one, pd - 1, 1.f, 1.f, true);
+    }
+    if (rc != PL_OK) return rc;
+    Layout L;
+    rc = make_layout(L, g, pd, vd, max_entries);
+    if (rc != PL_OK) return rc;
+    *bytes = L.total;
+    return PL_OK;
+}
+
+int pl_compute_positions_f32(const float* reference, float* positions, int n,
+                             int n_reference_channels, int n_spatial_dims, const int* spatial_dims,
+                             float spatial_std, float feature_std, void* stream) {
+    if (!positions || n < 0 || n_spatial_dims < 0 || n_spatial_dims > MAX_SDIMS ||
+        n_reference_channels < 0 || (n_reference_channels > 0 && !reference) ||
+        (n_spatial_dims > 0 && !spatial_dims))
+        return PL_INVALID_ARGUMENT;
+    if (n == 0) return PL_OK;
+    Geom g;
+    memset(&g, 0, sizeof(g));
+    for (int i = 0; i < n_spatial_dims; i++) g.sdims[i] = spatial_dims[i];
+    g.spatial_std = spatial_std;
+    g.feature_std = feature_std;
+    positions_kernel<<<(n + 255) / 256, 256, 0, (cudaStream_t)stream>>>(
+        reference, positions, n, n_reference_channels, n_spatial_dims, g);
+    PL_CUDA(cudaGetLastError());
+    return PL_OK;
+}
+
+int pl_filter_f32(float* output, const float* input, const float* positions, int batch, int n,
+                  int pd, int vd, int reverse, void* workspace, size_t workspace_bytes,
+                  int64_t max_entries, int mode, void* stream) {
+    if (batch < 0 || n < 0 || batch > 65535) return PL_INVALID_ARGUMENT;
+    if (!pl_supported(pd, vd)) return PL_UNSUPPORTED_DIMS;
+    if (batch == 0 || n == 0) return PL_OK;
+    if (!output || !input || !positions || !workspace) return PL_INVALID_ARGUMENT;
+    Geom g;
+    int one = n;
+    int rc = make_geom(g, batch, n, pd, 1, &one, pd - 1, 1.f, 1.f, true);
+    if (rc != PL_OK) return rc;
+    return filter_common(g, output, input, positions, nullptr, pd, vd, reverse, workspace,
+                         workspace_bytes, max_entries, mode, (cudaStream_t)stream);
+}
+
+static int op_geom(Geom& g, int batch, int n_spatial_dims, const int* spatial_dims,
+                   int n_reference_channels, int bilateral, float theta_alpha, float theta_beta,
+                   float theta_gamma, int* pd_out, int* n_out) {
+    if (batch < 0 || batch > 65535 || n_spatial_dims < 1 || n_spatial_dims > MAX_SDIMS || !spatial_dims ||
+        n_reference_channels < 0)
+        return PL_INVALID_ARGUMENT;
+    long long n = 1;
+    for (int i = 0; i < n_spatial_dims; i++) {
+        if (spatial_dims[i] < 0) return PL_INVALID_ARGUMENT;
+        n *= spatial_dims[i];
+        if (n > 0x7FFFFFFFll) return PL_INVALID_ARGUMENT;
+    }
+    // src/LatticeFilterKernel.cpp:131-142
+    const int R = bilateral ? n_reference_channels : 0;
+    const int pd = n_spatial_dims + R;
+    const float spatial_std = bilateral ? theta_alpha : theta_gamma;
+    const float feature_std = bilateral ? theta_beta : -1.f;
+    *pd_out = pd;
+    *n_out = (int)n;
+    if (!pd_supported(pd)) return PL_UNSUPPORTED_DIMS;
+    return make_geom(g, batch, (int)n, pd, n_spatial_dims, spatial_dims, R, spatial_std, feature_std, false);
+}
+
+int pl_lattice_filter_f32(float* output, const float* input, const float* reference, int batch,
+                          int n_spatial_dims, const int* spatial_dims, int n_input_channels,
+                          int n_reference_channels, int bilateral, float theta_alpha,
+                          float theta_beta, float theta_gamma, int reverse, void* workspace,
+                          size_t workspace_bytes, int64_t max_entries, int mode, void* stream) {
+    if (n_input_channels < 1) return PL_INVALID_ARGUMENT;
+    Geom g;
+    int pd = 0, n = 0;
+    int rc = op_geom(g, batch, n_spatial_dims, spatial_dims, n_reference_channels, bilateral,
+                     theta_alpha, theta_beta, theta_gamma, &pd, &n);
+    if (rc != PL_OK) return rc;
+    const int vd = n_input_channels + 1;
+    if (!pl_supported(pd, vd)) return PL_UNSUPPORTED_DIMS;
+    if (batch == 0 || n == 0) return PL_OK;
+    if (!output || !input || !workspace || (g.R > 0 && !reference)) return PL_INVALID_ARGUMENT;
+    return filter_common(g, output, input, nullptr, reference, pd, vd, reverse, workspace,
+                         workspace_bytes, max_entries, mode, (cudaStream_t)stream);
+}
+
+int pl_lattice_stats(const void* workspace, pl_stats* stats, void* stream) {
+    if (!workspace || !stats) return PL_INVALID_ARGUMENT;
+    Header h;
+    PL_CUDA(cudaMemcpyAsync(&h, workspace, sizeof(Header), cudaMemcpyDeviceToHost, (cudaStream_t)stream));
+    PL_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
+    stats->num_vertices = h.num_vertices;
+    stats->num_entries = h.num_entries;
+    stats->table_slots = (int64_t)1 << h.table_log2;
+    stats->device_status = PL_OK;
+    for (int code = PL_INVALID_ARGUMENT; code <= PL_INTERNAL_ERROR; code++)
+        if (h.status & (1u << code)) stats->device_status = code;
+    stats->reserved = 0;
+    return PL_OK;
+}
+
+int pl_export_lattice(const void* workspace, const float* positions, const float* reference,
+                      int batch, int n, int pd, int vd, int n_spatial_dims, const int* spatial_dims,
+                      int n_reference_channels, float spatial_std, float feature_std,
+                      int64_t max_entries, int64_t max_vertices, int16_t* vertex_keys,
+                      int32_t* vertex_item, int32_t* pixel_vertex, float* pixel_weight,
+                      void* stream) {
+    if (!workspace || batch < 0 || n < 0 || batch > 65535) return PL_INVALID_ARGUMENT;
+    if (!pl_supported(pd, vd)) return PL_UNSUPPORTED_DIMS;
+    if (batch == 0 || n == 0) return PL_OK;
+    Geom g;
+    int rc;
+    if (positions) {
+        int one = n;
+        rc = make_geom(g, batch, n, pd, 1, &one, pd - 1, 1.f, 1.f, true);
+    } else {
+        if (n_spatial_dims < 1 || n_spatial_dims > MAX_SDIMS || !spatial_dims ||
+            n_spatial_dims + n_reference_channels != pd || (n_reference_channels > 0 && !reference))
+            return PL_INVALID_ARGUMENT;
+        rc = make_geom(g, batch, n, pd, n_spatial_dims, spatial_dims, n_reference_channels,
+                       spatial_std, feature_std, false);
+    }
+    if (rc != PL_OK) return rc;
+    Layout L;
+    rc = make_layout(L, g, pd, vd, max_entries);
+    if (rc != PL_OK) return rc;
+#define CALL(P) run_export<P>(g, positions, reference, workspace, L, (long long)max_vertices, vertex_keys, \
+                              vertex_item, pixel_vertex, pixel_weight, (cudaStream_t)stream)
+    PL_DISPATCH_PD(pd, CALL)
+#undef CALL
+}
+
+}  // extern "C"

@@ -1,0 +1,239 @@
+"""Host-side mirror of the reference operator on torch CUDA tensors.
+
+`lattice_filter(input_image, reference_image, bilateral, theta_alpha, theta_beta, theta_gamma,
+reverse)` has the arguments, defaults, shapes and gradient of the `LatticeFilter` op
+(src/LatticeFilterKernel.cpp:30-43, gradient lattice_filter_op_loader.py:32-54); torch supplies
+device memory and streams only, every computation happens in libpl_lattice.so through its C ABI.
+"""
+import ctypes
+
+import torch
+
+from . import capi
+
+_workspaces = {}   # (device index, stream handle) -> uint8 tensor, grown on demand
+
+
+def _workspace(device, stream_handle, nbytes):
+    key = (device.index, stream_handle)
+    ws = _workspaces.get(key)
+    if ws is None or ws.numel() < nbytes:
+        ws = torch.empty(int(nbytes), dtype=torch.uint8, device=device)
+        _workspaces[key] = ws
+    return ws
+
+
+def release_workspaces():
+    _workspaces.clear()
+
+
+def _stream_handle(device):
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def _check_tensor(t, name):
+    if not t.is_cuda:
+        raise ValueError("%s must be a CUDA tensor (there is no CPU path in this package)" % name)
+    if t.dtype != torch.float32:
+        raise TypeError("%s must be float32" % name)
+
+
+class FilterCall:
+    """Geometry of one op call; keeps what pl_export_lattice needs to be given again."""
+
+    def __init__(self, input_shape, reference_shape, bilateral, theta_alpha, theta_beta,
+                 theta_gamma):
+        if len(input_shape) < 3:
+            raise ValueError("input_image must be [batch, *spatial, channels]")
+        self.batch = int(input_shape[0])
+        self.sdims = [int(s) for s in input_shape[1:-1]]
+        self.n = 1
+        for s in self.sdims:
+            self.n *= s
+        self.c = int(input_shape[-1])
+        self.bilateral = bool(bilateral)
+        if self.bilateral:
+            if reference_shape is None or list(reference_shape[:-1]) != list(input_shape[:-1]):
+                raise ValueError("reference_image must match input_image in batch and spatial dims")
+            self.r = int(reference_shape[-1])
+            self.spatial_std, self.feature_std = float(theta_alpha), float(theta_beta)
+        else:
+            self.r = 0
+            self.spatial_std, self.feature_std = float(theta_gamma), -1.0
+        self.pd = len(self.sdims) + self.r
+        self.vd = self.c + 1
+        self.theta = (float(theta_alpha), float(theta_beta), float(theta_gamma))
+
+    def workspace_bytes(self, max_entries=0):
+        nbytes = ctypes.c_size_t(0)
+        capi.check(capi.lib().pl_workspace_bytes(self.batch, self.n, self.pd, self.vd,
+                                                 len(self.sdims), capi.int_array(self.sdims),
+                                                 int(max_entries), ctypes.byref(nbytes)),
+                   "pl_workspace_bytes")
+        return nbytes.value
+
+
+def lattice_filter_raw(input_image, reference_image, bilateral=True, theta_alpha=1.0,
+                       theta_beta=1.0, theta_gamma=1.0, reverse=False, mode="atomic",
+                       max_entries=0, check=None, workspace=None, out=None):
+    """One call of pl_lattice_filter_f32 on the current stream.  Returns (output, workspace, call)."""
+    _check_tensor(input_image, "input_image")
+    x = input_image.contiguous()
+    ref = None
+    if bilateral:
+        _check_tensor(reference_image, "reference_image")
+        ref = reference_image.contiguous()
+    call = FilterCall(tuple(x.shape), None if ref is None else tuple(ref.shape), bilateral,
+                      theta_alpha, theta_beta, theta_gamma)
+    if not capi.lib().pl_supported(call.pd, call.vd):
+        raise capi.PlError(capi.PL_UNSUPPORTED_DIMS, "lattice_filter(pd=%d, vd=%d)" % (call.pd, call.vd))
+    if out is None:
+        out = torch.empty_like(x)
+    if call.batch == 0 or call.n == 0:
+        return out, None, call
+    stream = _stream_handle(x.device)
+    with torch.cuda.device(x.device):
+        nbytes = call.workspace_bytes(max_entries)
+        ws = workspace if workspace is not None else _workspace(x.device, stream, nbytes)
+        rc = capi.lib().pl_lattice_filter_f32(
+            out.data_ptr(), x.data_ptr(), 0 if ref is None else ref.data_ptr(), call.batch,
+            len(call.sdims), capi.int_array(call.sdims), call.c, call.r, int(call.bilateral),
+            call.theta[0], call.theta[1], call.theta[2], int(bool(reverse)), ws.data_ptr(),
+            ws.numel(), int(max_entries), capi.MODES[mode], stream)
+        capi.check(rc, "pl_lattice_filter_f32")
+        if check is None:
+            check = max_entries > 0
+        if check:
+            st = lattice_stats(ws, stream)
+            if st.device_status != capi.PL_OK:
+                raise capi.PlError(st.device_status, "lattice_filter (device)")
+    return out, ws, call
+
+
+def lattice_stats(workspace, stream=None):
+    """Counters of the last call that used `workspace` (synchronises the stream)."""
+    st = capi.PlStats()
+    if stream is None:
+        stream = _stream_handle(workspace.device)
+    with torch.cuda.device(workspace.device):
+        capi.check(capi.lib().pl_lattice_stats(workspace.data_ptr(), ctypes.byref(st), stream),
+                   "pl_lattice_stats")
+    return st
+
+
+class _LatticeFilterFunction(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, input_image, reference_image, bilateral, theta_alpha, theta_beta, theta_gamma,
+                reverse, mode):
+        ctx.args = (bilateral, theta_alpha, theta_beta, theta_gamma, mode)
+        ctx.save_for_backward(reference_image)
+        out, _, _ = lattice_filter_raw(input_image, reference_image, bilateral, theta_alpha,
+                                       theta_beta, theta_gamma, reverse, mode)
+        return out
+
+    @staticmethod
+    def backward(ctx, grad):
+        # lattice_filter_op_loader.py:32-54: the gradient w.r.t. the input is the same filter applied
+        # to the upstream gradient with reverse=True; the reference image gets zeros.
+        (reference_image,) = ctx.saved_tensors
+        bilateral, theta_alpha, theta_beta, theta_gamma, mode = ctx.args
+        g, _, _ = lattice_filter_raw(grad, reference_image, bilateral, theta_alpha, theta_beta,
+                                     theta_gamma, True, mode)
+        ref_grad = torch.zeros_like(reference_image) if reference_image is not None else None
+        return g, ref_grad, None, None, None, None, None, None
+
+
+def lattice_filter(input_image, reference_image, bilateral=True, theta_alpha=1.0, theta_beta=1.0,
+                   theta_gamma=1.0, reverse=False, mode="atomic"):
+    """output[B, *S, C] = permutohedral-lattice filter of input_image[B, *S, C] guided by
+    reference_image[B, *S, R] (bilateral) or by position only (bilateral=False, theta_gamma)."""
+    return _LatticeFilterFunction.apply(input_image, reference_image, bool(bilateral),
+                                        float(theta_alpha), float(theta_beta), float(theta_gamma),
+                                        bool(reverse), mode)
+
+
+def compute_positions(reference_image, spatial_dims, spatial_std, feature_std):
+    """positions[n, n_sdims + R] for one item: the ComputeKernel functor
+    (src/LatticeFilterKernel.h:40-54).  reference_image [n, R] or None."""
+    sdims = [int(s) for s in spatial_dims]
+    n = 1
+    for s in sdims:
+        n *= s
+    if reference_image is not None:
+        _check_tensor(reference_image, "reference_image")
+        ref = reference_image.contiguous().view(n, -1)
+        r, device = ref.shape[1], ref.device
+    else:
+        ref, r, device = None, 0, torch.device("cuda", torch.cuda.current_device())
+    pos = torch.empty((n, len(sdims) + r), dtype=torch.float32, device=device)
+    with torch.cuda.device(device):
+        capi.check(capi.lib().pl_compute_positions_f32(
+            0 if ref is None else ref.data_ptr(), pos.data_ptr(), n, r, len(sdims),
+            capi.int_array(sdims), float(spatial_std), float(feature_std), _stream_handle(device)),
+            "pl_compute_positions_f32")
+    return pos
+
+
+def filter_positions(input_values, positions, reverse=False, mode="atomic", max_entries=0,
+                     check=None, workspace=None):
+    """The LatticeFilter functor (src/LatticeFilterKernel.h:28-38) on [batch, n, C] values at
+    [batch, n, pd] positions (2-D tensors are taken as batch 1).  Returns (output, workspace)."""
+    _check_tensor(input_values, "input_values")
+    _check_tensor(positions, "positions")
+    squeeze = input_values.dim() == 2
+    x = input_values.contiguous().view((1,) + tuple(input_values.shape)) if squeeze else input_values.contiguous()
+    p = positions.contiguous().view((1,) + tuple(positions.shape)) if squeeze else positions.contiguous()
+    batch, n, c = x.shape
+    pd = p.shape[-1]
+    if tuple(p.shape[:2]) != (batch, n):
+        raise ValueError("positions must be [batch, n, pd] matching input_values")
+    vd = c + 1
+    out = torch.empty_like(x)
+    ws = None
+    if batch and n:
+        stream = _stream_handle(x.device)
+        with torch.cuda.device(x.device):
+            nbytes = ctypes.c_size_t(0)
+            capi.check(capi.lib().pl_workspace_bytes(batch, n, pd, vd, 0, None, int(max_entries),
+                                                     ctypes.byref(nbytes)), "pl_workspace_bytes")
+            ws = workspace if workspace is not None else _workspace(x.device, stream, nbytes.value)
+            capi.check(capi.lib().pl_filter_f32(out.data_ptr(), x.data_ptr(), p.data_ptr(), batch, n,
+                                                pd, vd, int(bool(reverse)), ws.data_ptr(), ws.numel(),
+                                                int(max_entries), capi.MODES[mode], stream),
+                       "pl_filter_f32")
+            if check is None:
+                check = max_entries > 0
+            if check:
+                st = lattice_stats(ws, stream)
+                if st.device_status != capi.PL_OK:
+                    raise capi.PlError(st.device_status, "filter_positions (device)")
+    return (out[0] if squeeze else out), ws
+
+
+def export_lattice(workspace, stats, batch, n, pd, vd, positions=None, reference=None, sdims=None,
+                   spatial_std=1.0, feature_std=1.0, max_entries=0):
+    """Lattice structure of the last call on `workspace` as torch tensors:
+    (vertex_keys [M, pd] int16, vertex_item [M] int32, pixel_vertex [batch, n, pd+1] int32,
+    pixel_weight [batch, n, pd+1] float32)."""
+    device = workspace.device
+    m = int(stats.num_vertices)
+    vkeys = torch.zeros((m, pd), dtype=torch.int16, device=device)
+    vitem = torch.zeros((m,), dtype=torch.int32, device=device)
+    pv = torch.zeros((batch, n, pd + 1), dtype=torch.int32, device=device)
+    pw = torch.zeros((batch, n, pd + 1), dtype=torch.float32, device=device)
+    with torch.cuda.device(device):
+        if positions is not None:
+            rc = capi.lib().pl_export_lattice(workspace.data_ptr(), positions.contiguous().data_ptr(), 0,
+                                              batch, n, pd, vd, 0, None, 0, 1.0, 1.0, int(max_entries),
+                                              m, vkeys.data_ptr(), vitem.data_ptr(), pv.data_ptr(),
+                                              pw.data_ptr(), _stream_handle(device))
+        else:
+            r = pd - len(sdims)
+            rc = capi.lib().pl_export_lattice(workspace.data_ptr(), 0,
+                                              0 if reference is None else reference.contiguous().data_ptr(),
+                                              batch, n, pd, vd, len(sdims), capi.int_array(sdims), r,
+                                              float(spatial_std), float(feature_std), int(max_entries),
+                                              m, vkeys.data_ptr(), vitem.data_ptr(), pv.data_ptr(),
+                                              pw.data_ptr(), _stream_handle(device))
+        capi.check(rc, "pl_export_lattice")
+    return vkeys, vitem, pv, pw

@@ -1,0 +1,202 @@
+"""Parity of the CUDA path (through the C ABI) with the CPU oracle and the reference-made golden
+fixtures: lattice structure bit-exact, fp32 outputs within rel-L2 1e-5 / max-abs 1e-4."""
+import numpy as np
+import pytest
+
+from conftest import GOLDEN_CASES, load_golden
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def gpu():
+    import torch
+    if not torch.cuda.is_available():
+        pytest.fail("GPU tests need a CUDA device")
+    import gpu_helpers
+    return gpu_helpers
+
+
+@pytest.mark.parametrize("case", GOLDEN_CASES)
+def test_golden_fixture(case, gpu, oracle):
+    import torch
+    import permutohedral_lattice_b200 as plb
+    g = load_golden(case)
+    inp = g["input"]
+    c = inp.shape[-1]
+    n = int(np.prod(inp.shape[:-1]))
+    if "positions" in g:
+        pos = torch.from_numpy(g["positions"]).cuda()
+        x = torch.from_numpy(inp.reshape(n, c)).cuda()
+        out_f, ws = plb.filter_positions(x, pos, reverse=False)
+        st = plb.lattice_stats(ws)
+        vk, vi, pv, pw = plb.export_lattice(ws, st, 1, n, pos.shape[1], c + 1, positions=pos)
+        out_r, _ = plb.filter_positions(x, pos, reverse=True)
+    else:
+        ref = g["reference"][None] if "reference" in g else None
+        args = (bool(g["bilateral"]), float(g["theta_alpha"]), float(g["theta_beta"]),
+                float(g["theta_gamma"]))
+        out_f, ws, call, x, r = gpu.run_op(inp[None], ref, *args, False)
+        st, (vk, vi, pv, pw) = gpu.export_op(ws, call, r)
+        out_r = gpu.run_op(inp[None], ref, *args, True)[0]
+    assert st.device_status == 0
+    assert st.num_vertices == int(g["num_vertices"])
+    vk_n, pv_n = vk.cpu().numpy(), pv.cpu().numpy()
+    from conftest import bits, sorted_rows
+    assert np.array_equal(sorted_rows(vk_n), g["keys_sorted"])
+    assert np.array_equal(vk_n[pv_n[0]], g["pixel_keys"])
+    assert np.array_equal(bits(pw.cpu().numpy()[0]), bits(g["pixel_weights"]))
+    gpu.assert_outputs_close(out_f.cpu().numpy().reshape(inp.shape), g["out_forward"], case + " fwd")
+    gpu.assert_outputs_close(out_r.cpu().numpy().reshape(inp.shape), g["out_reverse"], case + " rev")
+
+
+@pytest.mark.parametrize("config", [0, 1, 2, 3])
+def test_small_workload_op_path(config, gpu, oracle):
+    from permutohedral_lattice_b200 import workloads
+    w = workloads.small(config)
+    want, items = oracle.lattice_filter(w.input, w.reference, True, w.theta_alpha, w.theta_beta,
+                                        1.0, False, structure=True)
+    out, ws, call, x, r = gpu.run_op(w.input, w.reference, True, w.theta_alpha, w.theta_beta, 1.0, False)
+    st, (vk, vi, pv, pw) = gpu.export_op(ws, call, r)
+    gpu.assert_structure_equal(vk, vi, pv, pw, items, w.name)
+    gpu.assert_outputs_close(out.cpu().numpy(), want, w.name + " fwd")
+    if w.backward:
+        want_b = oracle.lattice_filter(w.grad, w.reference, True, w.theta_alpha, w.theta_beta, 1.0, True)
+        got_b = gpu.run_op(w.grad, w.reference, True, w.theta_alpha, w.theta_beta, 1.0, True)[0]
+        gpu.assert_outputs_close(got_b.cpu().numpy(), want_b, w.name + " bwd")
+
+
+def test_small_workload_positions_pd16(gpu, oracle):
+    import torch
+    import permutohedral_lattice_b200 as plb
+    from permutohedral_lattice_b200 import workloads
+    w = workloads.small(4)
+    b, n, c = w.batch, w.pixels_per_item, w.input.shape[-1]
+    x = torch.from_numpy(w.input.reshape(b, n, c)).cuda()
+    p = torch.from_numpy(w.positions).cuda()
+    out, ws = plb.filter_positions(x, p)
+    st = plb.lattice_stats(ws)
+    vk, vi, pv, pw = plb.export_lattice(ws, st, b, n, 16, c + 1, positions=p)
+    items = [oracle.filter(w.input[i].reshape(n, c), w.positions[i]) for i in range(b)]
+    gpu.assert_structure_equal(vk, vi, pv, pw, items, w.name)
+    want = np.stack([o.out for o in items])
+    gpu.assert_outputs_close(out.cpu().numpy(), want, w.name)
+
+
+@pytest.mark.parametrize("shape,r,c", [
+    ((1, 1), 3, 3),          # a single point
+    ((1, 37), 3, 2),         # one row
+    ((53, 1), 3, 2),         # one column (narrow tiles)
+    ((17, 33), 1, 1),        # one past the tile edge in both directions
+    ((3, 5, 7), 2, 4),       # tiny volume, pd 5
+    ((300,), 1, 1),          # 1-D signal
+])
+def test_ragged_shapes(shape, r, c, gpu, oracle):
+    rng = np.random.default_rng(11)
+    ref = rng.random((2,) + shape + (r,), dtype=np.float32)
+    inp = rng.standard_normal((2,) + shape + (c,)).astype(np.float32)
+    for reverse in (False, True):
+        want, items = oracle.lattice_filter(inp, ref, True, 3.0, 0.25, 1.0, reverse, structure=True)
+        out, ws, call, x, rt = gpu.run_op(inp, ref, True, 3.0, 0.25, 1.0, reverse)
+        st, (vk, vi, pv, pw) = gpu.export_op(ws, call, rt)
+        gpu.assert_structure_equal(vk, vi, pv, pw, items, str(shape))
+        gpu.assert_outputs_close(out.cpu().numpy(), want, str(shape))
+
+
+def test_empty_inputs(gpu):
+    import torch
+    import permutohedral_lattice_b200 as plb
+    out = plb.lattice_filter(torch.zeros((0, 8, 8, 3), device="cuda"), torch.zeros((0, 8, 8, 3), device="cuda"))
+    assert out.shape == (0, 8, 8, 3)
+    out = plb.lattice_filter(torch.zeros((2, 0, 8, 3), device="cuda"), torch.zeros((2, 0, 8, 3), device="cuda"))
+    assert out.shape == (2, 0, 8, 3)
+
+
+def test_identical_points_collide_into_one_simplex(gpu, oracle):
+    # every point has the same features: pd+1 vertices in total, output = mean of the inputs
+    import torch
+    import permutohedral_lattice_b200 as plb
+    rng = np.random.default_rng(2)
+    x = rng.random((1, 1000, 3), dtype=np.float32)
+    p = np.tile(np.array([[0.3, -1.2, 4.0, 0.01, 2.5]], np.float32), (1, 1000, 1))
+    out, ws = plb.filter_positions(torch.from_numpy(x).cuda(), torch.from_numpy(p).cuda())
+    st = plb.lattice_stats(ws)
+    assert st.num_vertices == 6
+    want = oracle.filter(x[0], p[0]).out
+    gpu.assert_outputs_close(out.cpu().numpy()[0], want, "collide")
+    assert np.allclose(out.cpu().numpy()[0], x[0].mean(0, keepdims=True), atol=1e-5)
+
+
+def test_batch_items_are_independent(gpu):
+    import torch
+    import permutohedral_lattice_b200 as plb
+    rng = np.random.default_rng(4)
+    ref = torch.from_numpy(rng.random((3, 20, 24, 3), dtype=np.float32)).cuda()
+    inp = torch.from_numpy(rng.random((3, 20, 24, 5), dtype=np.float32)).cuda()
+    whole = plb.lattice_filter(inp, ref, True, 4.0, 0.2)
+    for b in range(3):
+        one = plb.lattice_filter(inp[b:b + 1], ref[b:b + 1], True, 4.0, 0.2)
+        gpu.assert_outputs_close(one.cpu().numpy(), whole[b:b + 1].cpu().numpy(), "item %d" % b)
+
+
+def test_capacity_exceeded_is_reported_not_fatal(gpu):
+    import torch
+    import permutohedral_lattice_b200 as plb
+    from permutohedral_lattice_b200 import capi
+    rng = np.random.default_rng(5)
+    ref = torch.from_numpy(rng.random((1, 64, 64, 3), dtype=np.float32)).cuda()
+    inp = torch.from_numpy(rng.random((1, 64, 64, 3), dtype=np.float32)).cuda()
+    with pytest.raises(capi.PlError) as e:
+        plb.lattice_filter_raw(inp, ref, True, 1.0, 0.01, max_entries=100)
+    assert e.value.status == capi.PL_CAPACITY_EXCEEDED
+    # the context is still usable and a properly sized call succeeds
+    out = plb.lattice_filter(inp, ref, True, 1.0, 0.01)
+    assert torch.isfinite(out).all()
+
+
+def test_unsupported_dims_and_bad_arguments(gpu):
+    import torch
+    import permutohedral_lattice_b200 as plb
+    from permutohedral_lattice_b200 import capi
+    with pytest.raises(capi.PlError) as e:   # pd = 2 + 9 = 11 has no instantiation
+        plb.lattice_filter(torch.zeros((1, 4, 4, 2), device="cuda"), torch.zeros((1, 4, 4, 9), device="cuda"))
+    assert e.value.status == capi.PL_UNSUPPORTED_DIMS
+    with pytest.raises(ValueError):
+        plb.lattice_filter(torch.zeros((1, 4, 4, 2), device="cuda"), torch.zeros((1, 4, 5, 3), device="cuda"))
+    with pytest.raises(ValueError):
+        plb.lattice_filter(torch.zeros((1, 4, 4, 2)), torch.zeros((1, 4, 4, 3)))
+    ws = torch.empty(1024, dtype=torch.uint8, device="cuda")
+    with pytest.raises(capi.PlError) as e:
+        plb.lattice_filter_raw(torch.zeros((1, 8, 8, 2), device="cuda"), torch.zeros((1, 8, 8, 3), device="cuda"),
+                               workspace=ws)
+    assert e.value.status == capi.PL_WORKSPACE_TOO_SMALL
+
+
+def test_autograd_matches_reverse_filter(gpu, oracle):
+    import torch
+    import permutohedral_lattice_b200 as plb
+    rng = np.random.default_rng(6)
+    ref_n = rng.random((1, 24, 20, 3), dtype=np.float32)
+    inp_n = rng.random((1, 24, 20, 4), dtype=np.float32)
+    grad_n = rng.standard_normal((1, 24, 20, 4)).astype(np.float32)
+    ref = torch.from_numpy(ref_n).cuda().requires_grad_(True)
+    inp = torch.from_numpy(inp_n).cuda().requires_grad_(True)
+    out = plb.lattice_filter(inp, ref, True, 5.0, 0.2)
+    out.backward(torch.from_numpy(grad_n).cuda())
+    want = oracle.lattice_filter(grad_n, ref_n, True, 5.0, 0.2, 1.0, True)
+    gpu.assert_outputs_close(inp.grad.cpu().numpy(), want, "autograd")
+    assert torch.count_nonzero(ref.grad) == 0
+
+
+def test_compute_positions_matches_oracle(gpu, oracle):
+    import torch
+    import permutohedral_lattice_b200 as plb
+    from conftest import bits
+    rng = np.random.default_rng(8)
+    ref = rng.random((6 * 7 * 5, 2), dtype=np.float32)
+    got = plb.compute_positions(torch.from_numpy(ref).cuda(), [6, 7, 5], 80.0, 0.0625).cpu().numpy()
+    want = oracle.compute_positions(ref, [6, 7, 5], 80.0, 0.0625)
+    assert np.array_equal(bits(got), bits(want))
+    got = plb.compute_positions(None, [9, 4], 3.0, 1.0).cpu().numpy()
+    want = oracle.compute_positions(None, [9, 4], 3.0, -1.0)
+    assert np.array_equal(bits(got), bits(want))
