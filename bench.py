@@ -1,0 +1,423 @@
+"""Benchmark of the lattice-filter hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--config 2] [--impl ours|reference]
+
+One step = one forward + one backward (reverse=True on an upstream gradient) lattice filter over the
+whole batch of the configuration (forward only for configurations 0 and 4).  Default workload:
+configuration 2, dense-CRF message passing, 16 x 512x512, 21 channels guided by RGB + xy
+(pd 5, vd 22).  Metric: Mpixels/s.  Under torchrun every rank filters its own batch on its own GPU
+(weak scaling, no collective in the data path); time is the maximum over ranks.
+
+The line also carries: `roofline` for the slowest kernel (algorithmic bytes / CUDA-event time, against
+the measured HBM copy bandwidth in MEASURED_PEAKS.json), `roofline_call` for the whole step,
+`stages_ms` (per-call stage times from events recorded inside the timed steps), `e2e` (the same
+step through the public API from pinned host buffers, copies included) and `cpu_baseline` (the CPU
+oracle on this box's host cores, bounded sample).  `--impl reference` times the reference CPU
+implementation alone.
+"""
+import argparse
+import ctypes
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "Mpixels/s fwd+bwd (pd=5, vd=22 CRF)"
+FALLBACK_HBM_GBS = 6650.0
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--config", type=int, default=2)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--e2e-steps", type=int, default=3)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--cpu-threads", type=int, default=0)
+    return ap.parse_args()
+
+
+def metric_name(cfg, w):
+    if cfg == 2:
+        return METRIC
+    return "Mpixels/s %s (pd=%d, vd=%d)" % ("fwd+bwd" if w.backward else "fwd", w.pd, w.vd)
+
+
+def make_workload(cfg, rank):
+    from permutohedral_lattice_b200 import workloads
+    w = workloads.CONFIGS[cfg]()
+    if rank:   # another rank's batch: same distributions, other content
+        rng = np.random.default_rng(1000 + rank)
+        perm = rng.permutation(w.batch)
+        w.input = np.ascontiguousarray(np.roll(w.input[perm], rank * 7, axis=1))
+        if w.reference is not None:
+            w.reference = np.ascontiguousarray(np.roll(w.reference[perm], rank * 7, axis=1))
+        if w.positions is not None:
+            w.positions = np.ascontiguousarray(w.positions[perm])
+        if w.grad is not None:
+            w.grad = np.ascontiguousarray(w.grad[perm])
+    return w
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        try:
+            with open(path) as f:
+                return float(json.load(f)["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return FALLBACK_HBM_GBS, "fallback"
+
+
+class ClockSampler:
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.proc = None
+        self.gpu = gpu_index
+        self.path = "/tmp/pl_bench_clocks_%d_%d.csv" % (os.getpid(), gpu_index)
+
+    def start(self):
+        try:
+            self.out = open(self.path, "w")
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.gpu), "--query-gpu=" + self.QUERY,
+                 "--format=csv,noheader,nounits", "-lms", "100"], stdout=self.out,
+                stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        self.out.close()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        with open(self.path) as f:
+            for line in f:
+                parts = [p.strip() for p in line.split(",")]
+                if len(parts) < 9:
+                    continue
+                try:
+                    sm.append(float(parts[1]))
+                    mx.append(float(parts[2]))
+                except ValueError:
+                    continue
+                for name, val in zip(names, parts[5:9]):
+                    if val.lower().startswith("active"):
+                        reasons.add(name)
+        try:
+            os.remove(self.path)
+        except OSError:
+            pass
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def algorithmic_bytes(w, num_vertices):
+    """Per call (one direction), whole batch: 4N(F + 2C) + 4M vd (2(pd+1) + 2), split per stage:
+    build reads the features, splat reads the input and writes the M rows, each blur pass reads and
+    writes the M rows, slice reads the M rows and writes the output."""
+    npx = w.batch * w.pixels_per_item
+    c = w.vd - 1
+    f = w.pd if w.positions is not None else (w.reference.shape[-1] if w.bilateral else 0)
+    rows = 4 * num_vertices * w.vd
+    stage = {"build": 4 * npx * f, "splat": 4 * npx * c + rows, "blur": 2 * rows * (w.pd + 1),
+             "slice": rows + 4 * npx * c, "index": 0}
+    return stage, sum(stage.values()), 4 * npx * (f + 2 * c)
+
+
+def cpu_baseline(w, threads, prefer_reference=True):
+    """The CPU oracle on a bounded sample: the full batch (all items, fwd [+ bwd]) on `threads`
+    host threads, one lattice per item.  Returns the cpu_baseline object."""
+    from oracle import cpu_oracle as O
+    if w.positions is not None:   # positions path: per-item filter calls, single thread
+        items = min(w.batch, 1)
+        t0 = time.perf_counter()
+        for b in range(items):
+            O.filter(w.input[b].reshape(w.pixels_per_item, -1), w.positions[b], structure=False)
+        secs = time.perf_counter() - t0
+        return {"value": items * w.pixels_per_item / secs / 1e6, "unit": "Mpixels/s", "cores": 1,
+                "kind": "port", "sample": "%d item(s) of %s, forward, 1 thread" % (items, w.name)}
+    kind = "port"
+    kwargs = {}
+    if prefer_reference and O.reference_available():
+        try:
+            O._load_reference()
+            kind = "reference"
+            kwargs = {"min_vertices": w.pixels_per_item * (w.pd + 1) // 4}
+        except Exception:
+            kind = "port"
+    impl = "reference" if kind == "reference" else "port"
+    args = (w.reference, w.bilateral, w.theta_alpha, w.theta_beta, w.theta_gamma)
+    try:
+        _, secs = O.filter_batch_timed(w.input, *args, reverse=False, impl=impl, threads=threads, **kwargs)
+        if w.backward:
+            _, s2 = O.filter_batch_timed(w.grad, *args, reverse=True, impl=impl, threads=threads, **kwargs)
+            secs += s2
+    except RuntimeError:
+        # pre-sized reference table too small for this data: worst-case size
+        kwargs = {"min_vertices": w.pixels_per_item * (w.pd + 1)} if kind == "reference" else {}
+        _, secs = O.filter_batch_timed(w.input, *args, reverse=False, impl=impl, threads=threads, **kwargs)
+        if w.backward:
+            _, s2 = O.filter_batch_timed(w.grad, *args, reverse=True, impl=impl, threads=threads, **kwargs)
+            secs += s2
+    return {"value": w.batch * w.pixels_per_item / secs / 1e6, "unit": "Mpixels/s", "cores": threads,
+            "kind": kind,
+            "sample": "full batch of %s (%d items, %s) once, %d host threads, one lattice per item%s"
+                      % (w.name, w.batch, "fwd+bwd" if w.backward else "fwd", threads,
+                         ", hash table pre-sized (never grows)" if kind == "reference" else ""),
+            "seconds": secs}
+
+
+def host_threads(requested, batch):
+    n = requested if requested > 0 else (os.cpu_count() or 1)
+    return max(1, min(n, batch))
+
+
+def run_reference(args, rank, world):
+    """--impl reference: the reference's own CPU implementation of the path on the host cores."""
+    if rank != 0:
+        return
+    w = make_workload(args.config, 0)
+    threads = host_threads(args.cpu_threads, w.batch)
+    times = []
+    info = None
+    for i in range(args.warmup + args.steps):
+        info = cpu_baseline(w, threads)
+        if i >= args.warmup:
+            times.append(info["seconds"])
+        if sum(times) > 240 and len(times) >= 1:   # keep the whole run within a few minutes
+            break
+    secs = sum(times) / len(times)
+    value = w.batch * w.pixels_per_item / secs / 1e6
+    line = {
+        "impl": "reference", "metric": metric_name(args.config, w), "value": value,
+        "unit": "Mpixels/s", "n_gpus": args.gpus, "steps": len(times), "warmup": args.warmup,
+        "ms_per_step": secs * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic",
+        "config": {"workload": w.name, "batch": w.batch, "pixels_per_item": w.pixels_per_item,
+                   "pd": w.pd, "vd": w.vd, "direction": "fwd+bwd" if w.backward else "fwd"},
+        "cpu_baseline": {"value": value, "unit": "Mpixels/s", "cores": info["cores"],
+                         "kind": info["kind"], "sample": info["sample"]},
+        "e2e": {"value": value, "unit": "Mpixels/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    args = parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+
+    import torch
+    import torch.distributed as dist
+    import permutohedral_lattice_b200 as plb
+    from permutohedral_lattice_b200 import capi
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the product has no CPU path")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    w = make_workload(args.config, rank)
+    b, n, c = w.batch, w.pixels_per_item, w.vd - 1
+    use_positions = w.positions is not None
+
+    x = torch.from_numpy(w.input).to(dev)
+    ref = None if w.reference is None else torch.from_numpy(w.reference).to(dev)
+    pos = None if not use_positions else torch.from_numpy(w.positions).to(dev)
+    grad = None if w.grad is None else torch.from_numpy(w.grad).to(dev)
+    out_f = torch.empty_like(x)
+    out_b = torch.empty_like(x)
+    xf = x.view(b, n, c)
+
+    def one_call(inp, out, reverse, events=None):
+        if events is not None:
+            arr = (ctypes.c_void_p * capi.NUM_STAGE_EVENTS)(*[e.cuda_event for e in events])
+            capi.lib().pl_profile_next_call(arr)
+        if use_positions:
+            o, ws = plb.filter_positions(inp.view(b, n, c), pos, reverse=reverse)
+            return o, ws
+        o, ws, _ = plb.lattice_filter_raw(inp, ref, w.bilateral, w.theta_alpha, w.theta_beta,
+                                          w.theta_gamma, reverse, out=out)
+        return o, ws
+
+    def step(events_f=None, events_b=None):
+        _, ws = one_call(x, out_f, False, events_f)
+        if w.backward:
+            one_call(grad, out_b, True, events_b)
+        return ws
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # warm-up (also creates the workspace and every stage event before the timed region)
+    for _ in range(max(args.warmup, 3)):
+        ws = step()
+    torch.cuda.synchronize()
+    st = plb.lattice_stats(ws)
+    if st.device_status != 0:
+        raise SystemExit("device status %d" % st.device_status)
+    calls_per_step = 2 if w.backward else 1
+    ev = [[[torch.cuda.Event(enable_timing=True) for _ in range(capi.NUM_STAGE_EVENTS)]
+           for _ in range(calls_per_step)] for _ in range(args.steps)]
+    for s in ev:
+        for call in s:
+            for e in call:
+                e.record()
+    t_begin = torch.cuda.Event(enable_timing=True)
+    t_end = torch.cuda.Event(enable_timing=True)
+
+    sampler = ClockSampler(local_rank)
+    barrier()
+    sampler.start()
+    t_begin.record()
+    for k in range(args.steps):
+        step(ev[k][0], ev[k][1] if w.backward else None)
+    t_end.record()
+    barrier()
+    clocks = sampler.stop()
+    elapsed_ms = t_begin.elapsed_time(t_end)
+    if world > 1:
+        t = torch.tensor([elapsed_ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        elapsed_ms = float(t.item())
+    ms_per_step = elapsed_ms / args.steps
+    total_pixels = b * n * world
+    value = total_pixels / (ms_per_step * 1e-3) / 1e6
+
+    # per-stage times of a call, averaged over all timed calls
+    stage_ms = {name: 0.0 for name in capi.STAGE_NAMES}
+    ncalls = 0
+    for s in ev:
+        for call in s:
+            for i, name in enumerate(capi.STAGE_NAMES):
+                stage_ms[name] += call[i].elapsed_time(call[i + 1])
+            ncalls += 1
+    stage_ms = {k: v / ncalls for k, v in stage_ms.items()}
+
+    # roofline
+    hbm_gbs, peak_kind = peaks()
+    stage_bytes, call_bytes, io_bytes = algorithmic_bytes(w, int(st.num_vertices))
+    kernel_ms = dict(stage_ms)
+    kernel_ms["blur"] = stage_ms["blur"] / (w.pd + 1)          # one blur_axis launch
+    kernel_bytes = dict(stage_bytes)
+    kernel_bytes["blur"] = stage_bytes["blur"] / (w.pd + 1)
+    kernel_names = {"build": "build_tiles", "splat": "splat_tiles", "blur": "blur_axis",
+                    "slice": "slice_tiles"}
+    dominant = max(kernel_names, key=lambda k: stage_ms[k])
+    achieved = kernel_bytes[dominant] / (kernel_ms[dominant] * 1e-3) / 1e9
+    roofline = {"bound": "hbm", "kernel": kernel_names[dominant], "achieved": achieved,
+                "peak": hbm_gbs, "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / hbm_gbs,
+                "traffic": None, "algorithmic_bytes_per_launch": kernel_bytes[dominant],
+                "ms_per_launch": kernel_ms[dominant]}
+    call_ms = ms_per_step / calls_per_step
+    call_gbs = call_bytes / (call_ms * 1e-3) / 1e9
+    roofline_call = {"algorithmic_bytes_per_call": call_bytes, "io_floor_bytes_per_call": io_bytes,
+                     "achieved": call_gbs, "peak": hbm_gbs, "unit": "GB/s", "frac": call_gbs / hbm_gbs,
+                     "ms_per_call": call_ms}
+
+    # end to end through the public API from pinned host buffers
+    hx = torch.from_numpy(w.input).pin_memory()
+    href = None if w.reference is None else torch.from_numpy(w.reference).pin_memory()
+    hpos = None if not use_positions else torch.from_numpy(w.positions).pin_memory()
+    hgrad = None if w.grad is None else torch.from_numpy(w.grad).pin_memory()
+    hout_f = torch.empty_like(hx).pin_memory()
+    hout_b = torch.empty_like(hx).pin_memory()
+    h2d = hx.numel() * 4 + (href.numel() * 4 if href is not None else 0) + \
+        (hpos.numel() * 4 if hpos is not None else 0) + (hgrad.numel() * 4 if w.backward else 0)
+    d2h = hx.numel() * 4 * calls_per_step
+
+    def e2e_step():
+        dx = hx.to(dev, non_blocking=True)
+        if use_positions:
+            dp = hpos.to(dev, non_blocking=True)
+            o, _ = plb.filter_positions(dx.view(b, n, c), dp)
+            hout_f.copy_(o.view_as(hout_f), non_blocking=True)
+        else:
+            dr = None if href is None else href.to(dev, non_blocking=True)
+            o = plb.lattice_filter(dx, dr, w.bilateral, w.theta_alpha, w.theta_beta, w.theta_gamma)
+            hout_f.copy_(o, non_blocking=True)
+            if w.backward:
+                dg = hgrad.to(dev, non_blocking=True)
+                g = plb.lattice_filter(dg, dr, w.bilateral, w.theta_alpha, w.theta_beta,
+                                       w.theta_gamma, reverse=True)
+                hout_b.copy_(g, non_blocking=True)
+
+    e2e_step()
+    barrier()
+    e0 = torch.cuda.Event(enable_timing=True)
+    e1 = torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.e2e_steps):
+        e2e_step()
+    e1.record()
+    barrier()
+    e2e_ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([e2e_ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item())
+    e2e_value = total_pixels / (e2e_ms / args.e2e_steps * 1e-3) / 1e6
+
+    kernels_per_call = 6 + (w.pd + 1)   # build, clear, insert, link, splat, slice + blur passes
+    line = {
+        "metric": metric_name(args.config, w), "value": value, "unit": "Mpixels/s", "n_gpus": world,
+        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic",
+        "config": {"workload": w.name, "batch_per_gpu": b, "global_batch": b * world,
+                   "pixels_per_item": n, "pd": w.pd, "vd": w.vd,
+                   "direction": "fwd+bwd" if w.backward else "fwd", "parallelism": "batch-sharded x%d" % world,
+                   "mode": "atomic", "l2_policy": "inputs larger than L2 (%.0f MB read per call)"
+                   % ((x.numel() + (ref.numel() if ref is not None else 0)) * 4 / 1e6),
+                   "num_vertices": int(st.num_vertices), "num_entries": int(st.num_entries)},
+        "clocks": clocks,
+        "e2e": {"value": e2e_value, "unit": "Mpixels/s", "h2d_bytes_per_step": h2d,
+                "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms / args.e2e_steps},
+        "gpu_launches": kernels_per_call * calls_per_step * args.steps,
+        "roofline": roofline, "roofline_call": roofline_call,
+        "stages_ms": stage_ms,
+    }
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        info = cpu_baseline(w, host_threads(args.cpu_threads, w.batch))
+        info.pop("seconds", None)
+        line["cpu_baseline"] = info
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -96,6 +96,14 @@ int pl_lattice_filter_f32(float* output, const float* input, const float* refere
                           float theta_beta, float theta_gamma, int reverse, void* workspace,
                           size_t workspace_bytes, int64_t max_entries, int mode, void* stream);
 
+/* Profiling aid: the next pl_filter_f32 / pl_lattice_filter_f32 call made by this host thread records
+ * the PL_NUM_STAGE_EVENTS cudaEvent_t handles of stage_events[] on its stream at the stage
+ * boundaries (start, after build, after index, after splat, after blur, after slice), then forgets
+ * them.  The array must stay valid until that call returns.  NULL cancels.
+ * The reference only times whole calls with std::clock (Tests/test_bilateral_gpu.cpp:32-36). */
+#define PL_NUM_STAGE_EVENTS 6
+int pl_profile_next_call(void** stage_events);
+
 /* Copies the counters of the last call that used `workspace` to the host.  SYNCHRONISES `stream`.
  * Returns PL_OK when read; the call's own outcome is stats->device_status.
  * No counterpart in the reference (it prints or exits: src/PermutohedralLatticeGPU.cuh:49-55,442-445). */

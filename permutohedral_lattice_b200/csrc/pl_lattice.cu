@@ -621,6 +621,8 @@ __global__ void export_vertices(const Header* hdr, const Key<Cfg<PD>::KW>* __res
 // host side
 // ---------------------------------------------------------------------------------------------
 static thread_local char g_cuda_error[256] = "";
+// Stage-boundary events for the next filter call of this thread (pl_profile_next_call); consumed by it.
+static thread_local cudaEvent_t* g_stage_events = nullptr;
 
 static int cuda_fail(cudaError_t e, const char* where) {
     snprintf(g_cuda_error, sizeof(g_cuda_error), "%s: %s", where, cudaGetErrorString(e));
@@ -748,6 +750,9 @@ static int run_filter(const Geom& g, float* output, const float* input, const fl
     float* v0 = reinterpret_cast<float*>(ws + L.v0);
     float* v1 = reinterpret_cast<float*>(ws + L.v1);
 
+    cudaEvent_t* ev = g_stage_events;
+    g_stage_events = nullptr;
+    if (ev) PL_CUDA(cudaEventRecord(ev[0], st));
     PL_CUDA(cudaMemsetAsync(hdr, 0, sizeof(Header), st));
     if (g.num_tiles == 0) return PL_OK;
 
@@ -761,14 +766,17 @@ static int run_filter(const Geom& g, float* output, const float* input, const fl
 
     build_tiles<PD><<<g.num_tiles, TP, Cfg<PD>::BUILD_SMEM, st>>>(
         g, positions, reference, hdr, tile_info, rec, list_keys, (u32)L.max_entries);
+    if (ev) PL_CUDA(cudaEventRecord(ev[1], st));
     clear_table<<<wide, 256, 0, st>>>(hdr, table, (u32)table_log2);
     insert_entries<KW><<<wide, 256, 0, st>>>(hdr, table, list_keys, list_ref, vid, vowner);
     link_vertices<PD><<<wide, 256, 0, st>>>(hdr, table, list_keys, list_ref, vid, vowner, nbr, v0,
                                             L.max_entries, vd);
+    if (ev) PL_CUDA(cudaEventRecord(ev[2], st));
     const int rows_cap = rows_cap_for(PD, vd);
     const size_t rows_smem = (size_t)rows_cap * vd * sizeof(float);
     splat_tiles<PD><<<g.num_tiles, TP, rows_smem, st>>>(g, positions, reference, input, hdr,
                                                         tile_info, rec, list_ref, v0, vd, rows_cap);
+    if (ev) PL_CUDA(cudaEventRecord(ev[3], st));
     float* src = v0;
     float* dst = v1;
     for (int step = 0; step <= PD; step++) {
@@ -782,8 +790,10 @@ static int run_filter(const Geom& g, float* output, const float* input, const fl
             blur_axis<1><<<wide, 256, 0, st>>>(hdr, nb, src, dst, vd);
         float* tmp = src; src = dst; dst = tmp;
     }
+    if (ev) PL_CUDA(cudaEventRecord(ev[4], st));
     slice_tiles<PD><<<g.num_tiles, TP, rows_smem, st>>>(g, positions, reference, output, hdr,
                                                         tile_info, rec, list_ref, src, vd, rows_cap);
+    if (ev) PL_CUDA(cudaEventRecord(ev[5], st));
     PL_CUDA(cudaGetLastError());
     return PL_OK;
 }
@@ -958,6 +968,11 @@ int pl_lattice_filter_f32(float* output, const float* input, const float* refere
     if (!output || !input || !workspace || (g.R > 0 && !reference)) return PL_INVALID_ARGUMENT;
     return filter_common(g, output, input, nullptr, reference, pd, vd, reverse, workspace,
                          workspace_bytes, max_entries, mode, (cudaStream_t)stream);
+}
+
+int pl_profile_next_call(void** stage_events) {
+    g_stage_events = reinterpret_cast<cudaEvent_t*>(stage_events);
+    return PL_OK;
 }
 
 int pl_lattice_stats(const void* workspace, pl_stats* stats, void* stream) {
