@@ -80,7 +80,7 @@ def peaks():
 
 
 class ClockSampler:
-    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+    QUERY = ("timestamp,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
@@ -94,10 +94,20 @@ class ClockSampler:
             self.out = open(self.path, "w")
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", str(self.gpu), "--query-gpu=" + self.QUERY,
-                 "--format=csv,noheader,nounits", "-lms", "100"], stdout=self.out,
+                 "--format=csv,noheader,nounits", "-lms", "20"], stdout=self.out,
                 stderr=subprocess.DEVNULL)
+            deadline = time.time() + 5.0      # wait for the first sample so the region is covered
+            while time.time() < deadline and os.path.getsize(self.path) == 0:
+                time.sleep(0.05)
+                self.out.flush()
         except Exception:
             self.proc = None
+
+    def mark_begin(self):
+        self.t0 = time.time()
+
+    def mark_end(self):
+        self.t1 = time.time()
 
     def stop(self):
         if self.proc is None:
@@ -108,21 +118,32 @@ class ClockSampler:
         except Exception:
             self.proc.kill()
         self.out.close()
-        sm, mx, reasons = [], [], set()
+        import datetime
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        rows = []
         with open(self.path) as f:
             for line in f:
                 parts = [p.strip() for p in line.split(",")]
                 if len(parts) < 9:
                     continue
                 try:
-                    sm.append(float(parts[1]))
-                    mx.append(float(parts[2]))
+                    ts = datetime.datetime.strptime(parts[0], "%Y/%m/%d %H:%M:%S.%f").timestamp()
+                    rows.append((ts, float(parts[1]), float(parts[2]), parts[5:9]))
                 except ValueError:
                     continue
-                for name, val in zip(names, parts[5:9]):
-                    if val.lower().startswith("active"):
-                        reasons.add(name)
+        # samples taken inside the timed region (one sampling period of slack); if the region was
+        # shorter than a period, the nearest sample
+        inside = [r for r in rows if self.t0 - 0.02 <= r[0] <= self.t1 + 0.02]
+        if not inside and rows:
+            mid = 0.5 * (self.t0 + self.t1)
+            inside = [min(rows, key=lambda r: abs(r[0] - mid))]
+        sm = [r[1] for r in inside]
+        mx = [r[2] for r in inside]
+        reasons = set()
+        for r in inside:
+            for name, val in zip(names, r[3]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
         try:
             os.remove(self.path)
         except OSError:
@@ -299,13 +320,15 @@ def main():
     t_end = torch.cuda.Event(enable_timing=True)
 
     sampler = ClockSampler(local_rank)
-    barrier()
     sampler.start()
+    barrier()
+    sampler.mark_begin()
     t_begin.record()
     for k in range(args.steps):
         step(ev[k][0], ev[k][1] if w.backward else None)
     t_end.record()
     barrier()
+    sampler.mark_end()
     clocks = sampler.stop()
     elapsed_ms = t_begin.elapsed_time(t_end)
     if world > 1:

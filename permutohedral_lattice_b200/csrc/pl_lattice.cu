@@ -157,6 +157,9 @@ __device__ __forceinline__ void load_features(const Geom& g, const float* __rest
     }
 }
 
+// Floats of a vertex row: vd padded to a multiple of 4 (16-byte rows).
+__host__ __device__ __forceinline__ int padded_vd(int vd) { return (vd + 3) & ~3; }
+
 // Status word of the call, read once per CTA so that every thread takes the same branch even while
 // other CTAs of the same launch are setting error bits.
 __device__ __forceinline__ bool call_failed(const Header* hdr) {
@@ -394,164 +397,331 @@ link_vertices(Header* hdr, const u64* __restrict__ table,
         nbr[((u64)a * max_entries + v) * 2 + d] = (o < 0) ? -1 : (int)vid[o];
     }
 
-    const u64 cells = (u64)M * vd;
+    const u64 cells = (u64)M * padded_vd(vd);
     for (u64 e = gtid; e < cells; e += gsz) v0[e] = 0.f;
 }
 
 // ---------------------------------------------------------------------------------------------
-// splat_tiles
+// Value rows.  A vertex row holds vd floats padded to VP = a multiple of 4, so that rows are 16-byte
+// aligned: every row access below is a float4, and a row of 22 channels covers exactly three
+// 32-byte sectors.  Pad channels stay zero through splat and blur and are never sliced.
 // ---------------------------------------------------------------------------------------------
-template <int PD>
+// Vector reduction into global memory (sm_90+): one L2 operation per 16 bytes.
+__device__ __forceinline__ void red_add_v4(float* addr, float4 v) {
+    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(v.x), "f"(v.y), "f"(v.z),
+                 "f"(v.w)
+                 : "memory");
+}
+__device__ __forceinline__ void cp_async4(void* smem, const void* gmem) {
+    const unsigned sa = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(sa), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
+    const unsigned sa = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(sa), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() {
+    asm volatile("cp.async.commit_group;\n\tcp.async.wait_group 0;" ::: "memory");
+}
+
+// How a warp's lanes are spread over value rows: GS lanes (one float4 each) per row, PPW rows per
+// warp instruction.  Rows wider than 32 quads are walked in chunks of 32 quads.
+struct LaneMap {
+    int gs, ppw, g, q0;
+    bool active;
+    __device__ __forceinline__ LaneMap(int qpr, int lane) {
+        gs = qpr < 32 ? qpr : 32;
+        ppw = 32 / gs;
+        g = lane / gs;
+        q0 = lane - g * gs;
+        active = g < ppw;
+    }
+};
+
+// ---------------------------------------------------------------------------------------------
+// splat_tiles: V[vertex] += sum over the tile's splats of weight * [input channels, 1].
+// The splats of a tile are counting-sorted by entry in shared memory, then each entry's run is
+// summed in registers by a group of lanes (one float4 of channels per lane) reading the tile's
+// input rows from shared memory, and leaves the CTA as one vector reduction per 16 bytes.
+// No floating-point atomics in shared memory, no per-entry row cache.
+// VD > 0: value dimension known at compile time; VD == 0: taken from vd_rt.
+// ---------------------------------------------------------------------------------------------
+template <int PD, int VD>
+struct SplatSmem {
+    static constexpr int TP = Cfg<PD>::TP, SPLATS = Cfg<PD>::SPLATS;
+    static size_t bytes(int vd) {
+        return sizeof(float) * (size_t)TP * padded_vd(vd) + sizeof(uint2) * SPLATS + 2 * sizeof(int) * SPLATS +
+               sizeof(int) * TP;
+    }
+};
+
+template <int PD, int VD>
 __global__ void __launch_bounds__(Cfg<PD>::TP)
 splat_tiles(Geom g, const float* __restrict__ positions, const float* __restrict__ reference,
             const float* __restrict__ input, const Header* hdr, const int2* __restrict__ tile_info,
             const u16* __restrict__ rec, const u32* __restrict__ list_ref, float* __restrict__ v0,
-            int vd, int rows_cap) {
-    constexpr int TP = Cfg<PD>::TP, SPLATS = Cfg<PD>::SPLATS;
-    extern __shared__ __align__(16) float rows[];   // [rows_cap][vd]
+            int vd_rt) {
+    constexpr int TP = Cfg<PD>::TP, SPLATS = Cfg<PD>::SPLATS, NW = TP / 32;
+    const int vd = VD ? VD : vd_rt;
+    const int C = vd - 1, VP = padded_vd(vd), QPR = VP >> 2;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    float* in_s = reinterpret_cast<float*>(smem_raw);                       // [TP][VP]
+    uint2* sorted_s = reinterpret_cast<uint2*>(in_s + (size_t)TP * VP);     // [SPLATS] (point, weight)
+    int* cur_s = reinterpret_cast<int*>(sorted_s + SPLATS);                 // [SPLATS] count, then cursor
+    int* off_s = cur_s + SPLATS;                                            // [SPLATS] run start
+    int* prow_s = off_s + SPLATS;                                           // [TP] global row of each point
+    __shared__ int wsum_s[32];
     if (call_failed(hdr)) return;
-    const int tid = threadIdx.x, tile = blockIdx.x;
+    const int tid = threadIdx.x, tile = blockIdx.x, lane = tid & 31, warp = tid >> 5;
     const int2 info = tile_info[tile];
-    const int base = info.x, cnt = info.y;
-    const int nrows = min(cnt, rows_cap);
-    for (int i = tid; i < nrows * vd; i += TP) rows[i] = 0.f;
-    __syncthreads();
+    const int base = info.x, nloc = info.y;
 
     int item, pix;
     const bool valid = tile_point(g, tile, tid, item, pix);
+    prow_s[tid] = valid ? item * g.n + pix : -1;
+    for (int i = tid; i < nloc; i += TP) cur_s[i] = 0;
+    // homogeneous channel and padding of this point's staged row
+    in_s[tid * VP + C] = 1.f;
+    for (int j = C + 1; j < VP; j++) in_s[tid * VP + j] = 0.f;
+    __syncthreads();
+
+    // stage the tile's input rows: consecutive threads copy consecutive floats of global memory
+    for (int k = tid; k < TP * C; k += TP) {
+        const int p = k / C, j = k - p * C;
+        const int row = prow_s[p];
+        if (row >= 0) cp_async4(in_s + p * VP + j, input + (size_t)row * C + j);
+    }
+
+    float w[PD + 1];
+    int l[PD + 1];
     if (valid) {
         float f[PD];
         load_features<PD>(g, positions, reference, item, pix, f);
         Simplex<PD> s;
         find_simplex<PD>(f, g.scale, s);
-        float w[PD + 1];
         barycentric<PD>(s, w);
-        int l[PD + 1];
         const u16* rec_tile = rec + (size_t)tile * SPLATS;
 #pragma unroll
-        for (int r = 0; r <= PD; r++) l[r] = rec_tile[r * TP + tid];
-        const int C = vd - 1;
-        const float* in_row = input + ((size_t)item * g.n + pix) * C;
-        for (int j = 0; j < vd; j++) {
-            const float x = (j < C) ? __ldg(in_row + j) : 1.f;
+        for (int r = 0; r <= PD; r++) {
+            l[r] = rec_tile[r * TP + tid];
+            atomicAdd(&cur_s[l[r]], 1);
+        }
+    }
+    __syncthreads();
+
+    // exclusive scan of the per-entry counts
+    {
+        int local[PD + 1];
+        int sum = 0;
 #pragma unroll
-            for (int r = 0; r <= PD; r++) {
-                const float c = (j < C) ? PL_FMUL(w[r], x) : w[r];
-                if (l[r] < nrows)
-                    atomicAdd(&rows[l[r] * vd + j], c);
-                else
-                    atomicAdd(&v0[(size_t)list_ref[base + l[r]] * vd + j], c);
+        for (int r = 0; r <= PD; r++) {
+            const int i = tid * (PD + 1) + r;
+            local[r] = sum;
+            sum += (i < nloc) ? cur_s[i] : 0;
+        }
+        int incl = sum;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const int t = __shfl_up_sync(0xFFFFFFFFu, incl, d);
+            if (lane >= d) incl += t;
+        }
+        if (lane == 31) wsum_s[warp] = incl;
+        __syncthreads();
+        if (warp == 0) {
+            const int v = (lane < NW) ? wsum_s[lane] : 0;
+            int vi = v;
+#pragma unroll
+            for (int d = 1; d < 32; d <<= 1) {
+                const int t = __shfl_up_sync(0xFFFFFFFFu, vi, d);
+                if (lane >= d) vi += t;
+            }
+            wsum_s[lane] = vi - v;
+        }
+        __syncthreads();
+        const int excl = incl - sum + wsum_s[warp];
+#pragma unroll
+        for (int r = 0; r <= PD; r++) {
+            const int i = tid * (PD + 1) + r;
+            if (i < nloc) {
+                off_s[i] = excl + local[r];
+                cur_s[i] = excl + local[r];
             }
         }
     }
     __syncthreads();
-    for (int i = tid; i < nrows * vd; i += TP) {
-        const int l = i / vd, j = i - l * vd;
-        atomicAdd(&v0[(size_t)list_ref[base + l] * vd + j], rows[i]);
+    if (valid) {
+#pragma unroll
+        for (int r = 0; r <= PD; r++) {
+            const int pos = atomicAdd(&cur_s[l[r]], 1);
+            sorted_s[pos] = make_uint2((unsigned)tid, __float_as_uint(w[r]));
+        }
+    }
+    cp_async_wait_all();
+    __syncthreads();
+
+    const LaneMap lm(QPR, lane);
+    if (!lm.active) return;
+    const float4* in4 = reinterpret_cast<const float4*>(in_s);
+    for (int e = warp * lm.ppw + lm.g; e < nloc; e += NW * lm.ppw) {
+        const int beg = off_s[e], end = cur_s[e];
+        float* vrow = v0 + (size_t)list_ref[base + e] * VP;
+        for (int q = lm.q0; q < QPR; q += lm.gs) {
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int sidx = beg; sidx < end; sidx++) {
+                const uint2 pw = sorted_s[sidx];
+                const float wt = __uint_as_float(pw.y);
+                const float4 x = in4[pw.x * QPR + q];
+                acc.x = PL_FADD(acc.x, PL_FMUL(wt, x.x));
+                acc.y = PL_FADD(acc.y, PL_FMUL(wt, x.y));
+                acc.z = PL_FADD(acc.z, PL_FMUL(wt, x.z));
+                acc.w = PL_FADD(acc.w, PL_FMUL(wt, x.w));
+            }
+            red_add_v4(vrow + 4 * q, acc);
+        }
     }
 }
 
 // ---------------------------------------------------------------------------------------------
 // blur_axis: one [1 2 1]/4 pass along lattice axis `axis` (src/PermutohedralLatticeCPU.h:403-405:
-// the three products and their sum in double, one rounding to float).  VW floats per thread.
+// the three products and their sum in double, one rounding to float).  One float4 per thread.
 // ---------------------------------------------------------------------------------------------
-template <int VW>
-struct VecT;
-template <> struct VecT<1> { typedef float type; };
-template <> struct VecT<2> { typedef float2 type; };
-template <> struct VecT<4> { typedef float4 type; };
-
 __device__ __forceinline__ float mix3(float a, float b, float c) {
     return (float)PL_DADD(PL_DADD(PL_DMUL(0.25, (double)a), PL_DMUL(0.5, (double)b)),
                           PL_DMUL(0.25, (double)c));
 }
 
-template <int VW>
 __global__ void __launch_bounds__(256)
 blur_axis(const Header* hdr, const int* __restrict__ nbr_axis, const float* __restrict__ src,
-          float* __restrict__ dst, int vd) {
-    typedef typename VecT<VW>::type V;
+          float* __restrict__ dst, int qpr) {
     if (hdr->status != 0) return;
     const u32 M = hdr->num_vertices;
-    const int per_row = vd / VW;
-    const u64 items = (u64)M * per_row;
-    const V* __restrict__ s = reinterpret_cast<const V*>(src);
-    V* __restrict__ d = reinterpret_cast<V*>(dst);
+    const u64 items = (u64)M * qpr;
+    const float4* __restrict__ s = reinterpret_cast<const float4*>(src);
+    float4* __restrict__ d = reinterpret_cast<float4*>(dst);
     const int2* __restrict__ nb = reinterpret_cast<const int2*>(nbr_axis);
+    const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
     for (u64 e = (u64)blockIdx.x * blockDim.x + threadIdx.x; e < items;
          e += (u64)gridDim.x * blockDim.x) {
-        const u32 v = (u32)(e / per_row);
-        const int j = (int)(e - (u64)v * per_row);
+        const u32 v = (u32)(e / qpr);
+        const int j = (int)(e - (u64)v * qpr);
         const int2 n = __ldg(nb + v);
-        const V b = s[e];
-        V a, c;
-        if constexpr (VW == 1) {
-            a = (n.x >= 0) ? s[(u64)n.x * per_row + j] : 0.f;
-            c = (n.y >= 0) ? s[(u64)n.y * per_row + j] : 0.f;
-            d[e] = mix3(a, b, c);
-        } else if constexpr (VW == 2) {
-            a = (n.x >= 0) ? s[(u64)n.x * per_row + j] : make_float2(0.f, 0.f);
-            c = (n.y >= 0) ? s[(u64)n.y * per_row + j] : make_float2(0.f, 0.f);
-            d[e] = make_float2(mix3(a.x, b.x, c.x), mix3(a.y, b.y, c.y));
-        } else {
-            a = (n.x >= 0) ? s[(u64)n.x * per_row + j] : make_float4(0.f, 0.f, 0.f, 0.f);
-            c = (n.y >= 0) ? s[(u64)n.y * per_row + j] : make_float4(0.f, 0.f, 0.f, 0.f);
-            d[e] = make_float4(mix3(a.x, b.x, c.x), mix3(a.y, b.y, c.y), mix3(a.z, b.z, c.z),
-                               mix3(a.w, b.w, c.w));
-        }
+        const float4 b = s[e];
+        const float4 a = (n.x >= 0) ? s[(u64)n.x * qpr + j] : zero;
+        const float4 c = (n.y >= 0) ? s[(u64)n.y * qpr + j] : zero;
+        d[e] = make_float4(mix3(a.x, b.x, c.x), mix3(a.y, b.y, c.y), mix3(a.z, b.z, c.z),
+                           mix3(a.w, b.w, c.w));
     }
 }
 
 // ---------------------------------------------------------------------------------------------
 // slice_tiles (src/PermutohedralLatticeCPU.h:333-352: float multiply-then-add per remainder in
-// ascending order, reciprocal of the homogeneous channel in double, one multiply per channel)
+// ascending order, reciprocal of the homogeneous channel in double, one multiply per channel).
+// The tile's vertex rows are staged once in shared memory; each thread derives the weights,
+// entry indices and normaliser of its own point; then groups of lanes (one float4 of channels per
+// lane) interpolate and write the output rows.
 // ---------------------------------------------------------------------------------------------
 template <int PD>
+struct SliceCfg {
+    static constexpr int PW = ((2 * (PD + 1) + 1 + 3) / 4) * 4;   // words of a point record
+};
+
+template <int PD, int VD>
 __global__ void __launch_bounds__(Cfg<PD>::TP)
 slice_tiles(Geom g, const float* __restrict__ positions, const float* __restrict__ reference,
             float* __restrict__ output, const Header* hdr, const int2* __restrict__ tile_info,
             const u16* __restrict__ rec, const u32* __restrict__ list_ref,
-            const float* __restrict__ vsrc, int vd, int rows_cap) {
-    constexpr int TP = Cfg<PD>::TP, SPLATS = Cfg<PD>::SPLATS;
-    extern __shared__ __align__(16) float rows[];   // [rows_cap][vd]
+            const float* __restrict__ vsrc, int vd_rt, int rows_cap) {
+    constexpr int TP = Cfg<PD>::TP, SPLATS = Cfg<PD>::SPLATS, PW = SliceCfg<PD>::PW;
+    const int vd = VD ? VD : vd_rt;
+    const int C = vd - 1, VP = padded_vd(vd), QPR = VP >> 2;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    float4* rows4 = reinterpret_cast<float4*>(smem_raw);                            // [rows_cap][QPR]
+    float* prec_s = reinterpret_cast<float*>(rows4 + (size_t)rows_cap * QPR);       // [TP][PW]
+    int* prow_s = reinterpret_cast<int*>(prec_s + (size_t)TP * PW);                 // [TP]
     if (call_failed(hdr)) return;
-    const int tid = threadIdx.x, tile = blockIdx.x;
+    const int tid = threadIdx.x, tile = blockIdx.x, lane = tid & 31, warp = tid >> 5;
     const int2 info = tile_info[tile];
     const int base = info.x, cnt = info.y;
     const int nrows = min(cnt, rows_cap);
-    for (int i = tid; i < nrows * vd; i += TP) {
-        const int l = i / vd, j = i - l * vd;
-        rows[i] = vsrc[(size_t)list_ref[base + l] * vd + j];
+    const float4* v4 = reinterpret_cast<const float4*>(vsrc);
+    for (int i = tid; i < nrows * QPR; i += TP) {
+        const int lrow = i / QPR, q = i - lrow * QPR;
+        cp_async16(rows4 + i, v4 + (size_t)list_ref[base + lrow] * QPR + q);
     }
-    __syncthreads();
 
     int item, pix;
     const bool valid = tile_point(g, tile, tid, item, pix);
-    if (!valid) return;
-    float f[PD];
-    load_features<PD>(g, positions, reference, item, pix, f);
-    Simplex<PD> s;
-    find_simplex<PD>(f, g.scale, s);
+    prow_s[tid] = valid ? item * g.n + pix : -1;
     float w[PD + 1];
-    barycentric<PD>(s, w);
-    const u16* rec_tile = rec + (size_t)tile * SPLATS;
-    const float* rp[PD + 1];
+    int l[PD + 1];
+    if (valid) {
+        float f[PD];
+        load_features<PD>(g, positions, reference, item, pix, f);
+        Simplex<PD> s;
+        find_simplex<PD>(f, g.scale, s);
+        barycentric<PD>(s, w);
+        const u16* rec_tile = rec + (size_t)tile * SPLATS;
 #pragma unroll
-    for (int r = 0; r <= PD; r++) {
-        const int l = rec_tile[r * TP + tid];
-        rp[r] = (l < nrows) ? (rows + l * vd) : (vsrc + (size_t)list_ref[base + l] * vd);
+        for (int r = 0; r <= PD; r++) l[r] = rec_tile[r * TP + tid];
     }
-    const int C = vd - 1;
-    float norm = 0.f;
+    cp_async_wait_all();
+    __syncthreads();
+    if (valid) {
+        const float* rows = reinterpret_cast<const float*>(rows4);
+        float norm = 0.f;
 #pragma unroll
-    for (int r = 0; r <= PD; r++) norm = PL_FADD(norm, PL_FMUL(w[r], rp[r][C]));
-    const float inv = (float)(1.0 / (double)norm);
-    float* out_row = output + ((size_t)item * g.n + pix) * C;
-    for (int j = 0; j < C; j++) {
-        float acc = 0.f;
+        for (int r = 0; r <= PD; r++) {
+            const float hv = (l[r] < nrows) ? rows[l[r] * VP + C]
+                                            : vsrc[(size_t)list_ref[base + l[r]] * VP + C];
+            norm = PL_FADD(norm, PL_FMUL(w[r], hv));
+        }
+        float* pr = prec_s + tid * PW;
 #pragma unroll
-        for (int r = 0; r <= PD; r++) acc = PL_FADD(acc, PL_FMUL(w[r], rp[r][j]));
-        out_row[j] = PL_FMUL(acc, inv);
+        for (int r = 0; r <= PD; r++) {
+            pr[r] = w[r];
+            pr[PD + 2 + r] = __int_as_float(l[r]);
+        }
+        pr[PD + 1] = (float)(1.0 / (double)norm);
+    }
+    __syncthreads();
+
+    const LaneMap lm(QPR, lane);
+    if (!lm.active) return;
+    for (int i = lm.g; i < 32; i += lm.ppw) {
+        const int p = warp * 32 + i;
+        const int row = prow_s[p];
+        if (row < 0) continue;
+        float pr[PW];
+        const float4* pr4 = reinterpret_cast<const float4*>(prec_s + p * PW);
+#pragma unroll
+        for (int k = 0; k < PW / 4; k++) {
+            const float4 t = pr4[k];
+            pr[4 * k] = t.x; pr[4 * k + 1] = t.y; pr[4 * k + 2] = t.z; pr[4 * k + 3] = t.w;
+        }
+        const float inv = pr[PD + 1];
+        const float4* rp[PD + 1];
+#pragma unroll
+        for (int r = 0; r <= PD; r++) {
+            const int lr = __float_as_int(pr[PD + 2 + r]);
+            rp[r] = (lr < nrows) ? (rows4 + lr * QPR) : (v4 + (size_t)list_ref[base + lr] * QPR);
+        }
+        float* out_row = output + (size_t)row * C;
+        for (int q = lm.q0; q < QPR; q += lm.gs) {
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int r = 0; r <= PD; r++) {
+                const float4 x = rp[r][q];
+                acc.x = PL_FADD(acc.x, PL_FMUL(pr[r], x.x));
+                acc.y = PL_FADD(acc.y, PL_FMUL(pr[r], x.y));
+                acc.z = PL_FADD(acc.z, PL_FMUL(pr[r], x.z));
+                acc.w = PL_FADD(acc.w, PL_FMUL(pr[r], x.w));
+            }
+            const int j = 4 * q;
+            if (j < C) out_row[j] = PL_FMUL(acc.x, inv);
+            if (j + 1 < C) out_row[j + 1] = PL_FMUL(acc.y, inv);
+            if (j + 2 < C) out_row[j + 2] = PL_FMUL(acc.z, inv);
+            if (j + 3 < C) out_row[j + 3] = PL_FMUL(acc.w, inv);
+        }
     }
 }
 
@@ -705,8 +875,8 @@ static int make_layout(Layout& L, const Geom& g, int pd, int vd, int64_t max_ent
     L.vowner = off;    off += align_up(sizeof(u32) * E);
     L.table = off;     off += align_up(sizeof(u64) * slots);
     L.nbr = off;       off += align_up(sizeof(int) * 2 * (size_t)(pd + 1) * E);
-    L.v0 = off;        off += align_up(sizeof(float) * (size_t)vd * E);
-    L.v1 = off;        off += align_up(sizeof(float) * (size_t)vd * E);
+    L.v0 = off;        off += align_up(sizeof(float) * (size_t)padded_vd(vd) * E);
+    L.v1 = off;        off += align_up(sizeof(float) * (size_t)padded_vd(vd) * E);
     L.total = off;
     return PL_OK;
 }
@@ -723,14 +893,49 @@ static int num_sms() {
     return g_num_sms;
 }
 
-// Rows of the per-tile shared-memory value cache used by splat_tiles / slice_tiles.
+// Rows of the per-tile shared-memory vertex-row cache of slice_tiles (48 KB of rows at most).
 static int rows_cap_for(int pd, int vd) {
     const int splats = tp_of(pd) * (pd + 1);
-    int cap = (48 * 1024) / (vd * (int)sizeof(float));
+    int cap = (48 * 1024) / (padded_vd(vd) * (int)sizeof(float));
     if (cap > splats) cap = splats;
     if (cap < 1) cap = 1;
     return cap;
 }
+
+// splat_tiles / slice_tiles for value dimension vd: the instantiation with vd fixed at compile time
+// where there is one, else the run-time one.
+template <int PD, int VD>
+static int launch_splat(const Geom& g, const float* positions, const float* reference, const float* input,
+                        const Header* hdr, const int2* tile_info, const u16* rec, const u32* list_ref,
+                        float* v0, int vd, cudaStream_t st) {
+    const size_t smem = SplatSmem<PD, VD>::bytes(vd);
+    if (smem > 200 * 1024) return PL_UNSUPPORTED_DIMS;
+    PL_CUDA(cudaFuncSetAttribute(splat_tiles<PD, VD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    splat_tiles<PD, VD><<<g.num_tiles, Cfg<PD>::TP, smem, st>>>(g, positions, reference, input, hdr, tile_info,
+                                                                rec, list_ref, v0, vd);
+    return PL_OK;
+}
+
+template <int PD, int VD>
+static int launch_slice(const Geom& g, const float* positions, const float* reference, float* output,
+                        const Header* hdr, const int2* tile_info, const u16* rec, const u32* list_ref,
+                        const float* vsrc, int vd, cudaStream_t st) {
+    int rows_cap = rows_cap_for(PD, vd);
+    const size_t fixed = sizeof(float) * Cfg<PD>::TP * SliceCfg<PD>::PW + sizeof(int) * Cfg<PD>::TP;
+    size_t smem = sizeof(float) * (size_t)rows_cap * padded_vd(vd) + fixed;
+    if (smem > 200 * 1024) return PL_UNSUPPORTED_DIMS;
+    PL_CUDA(cudaFuncSetAttribute(slice_tiles<PD, VD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    slice_tiles<PD, VD><<<g.num_tiles, Cfg<PD>::TP, smem, st>>>(g, positions, reference, output, hdr, tile_info,
+                                                                rec, list_ref, vsrc, vd, rows_cap);
+    return PL_OK;
+}
+
+#define PL_DISPATCH_VD(FN, PD_, vd, ...)                                   \
+    ((vd) == 22  ? FN<PD_, 22>(__VA_ARGS__)                                 \
+     : (vd) == 4 ? FN<PD_, 4>(__VA_ARGS__)                                  \
+     : (vd) == 3 ? FN<PD_, 3>(__VA_ARGS__)                                  \
+     : (vd) == 2 ? FN<PD_, 2>(__VA_ARGS__)                                  \
+                 : FN<PD_, 0>(__VA_ARGS__))
 
 template <int PD>
 static int run_filter(const Geom& g, float* output, const float* input, const float* positions,
@@ -772,27 +977,23 @@ static int run_filter(const Geom& g, float* output, const float* input, const fl
     link_vertices<PD><<<wide, 256, 0, st>>>(hdr, table, list_keys, list_ref, vid, vowner, nbr, v0,
                                             L.max_entries, vd);
     if (ev) PL_CUDA(cudaEventRecord(ev[2], st));
-    const int rows_cap = rows_cap_for(PD, vd);
-    const size_t rows_smem = (size_t)rows_cap * vd * sizeof(float);
-    splat_tiles<PD><<<g.num_tiles, TP, rows_smem, st>>>(g, positions, reference, input, hdr,
-                                                        tile_info, rec, list_ref, v0, vd, rows_cap);
+    int rc = PL_DISPATCH_VD(launch_splat, PD, vd, g, positions, reference, input, hdr, tile_info, rec,
+                            list_ref, v0, vd, st);
+    if (rc != PL_OK) return rc;
     if (ev) PL_CUDA(cudaEventRecord(ev[3], st));
     float* src = v0;
     float* dst = v1;
+    const int qpr = padded_vd(vd) / 4;
     for (int step = 0; step <= PD; step++) {
         const int axis = reverse ? PD - step : step;
         const int* nb = nbr + (size_t)axis * L.max_entries * 2;
-        if (vd % 4 == 0)
-            blur_axis<4><<<wide, 256, 0, st>>>(hdr, nb, src, dst, vd);
-        else if (vd % 2 == 0)
-            blur_axis<2><<<wide, 256, 0, st>>>(hdr, nb, src, dst, vd);
-        else
-            blur_axis<1><<<wide, 256, 0, st>>>(hdr, nb, src, dst, vd);
+        blur_axis<<<wide, 256, 0, st>>>(hdr, nb, src, dst, qpr);
         float* tmp = src; src = dst; dst = tmp;
     }
     if (ev) PL_CUDA(cudaEventRecord(ev[4], st));
-    slice_tiles<PD><<<g.num_tiles, TP, rows_smem, st>>>(g, positions, reference, output, hdr,
-                                                        tile_info, rec, list_ref, src, vd, rows_cap);
+    rc = PL_DISPATCH_VD(launch_slice, PD, vd, g, positions, reference, output, hdr, tile_info, rec,
+                        list_ref, src, vd, st);
+    if (rc != PL_OK) return rc;
     if (ev) PL_CUDA(cudaEventRecord(ev[5], st));
     PL_CUDA(cudaGetLastError());
     return PL_OK;
