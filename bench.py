@@ -43,6 +43,8 @@ def parse_args():
     ap.add_argument("--e2e-steps", type=int, default=3)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-threads", type=int, default=0)
+    ap.add_argument("--batch", type=int, default=0,
+                    help="override the batch size of the configuration (profiling of smaller cases)")
     return ap.parse_args()
 
 
@@ -52,9 +54,9 @@ def metric_name(cfg, w):
     return "Mpixels/s %s (pd=%d, vd=%d)" % ("fwd+bwd" if w.backward else "fwd", w.pd, w.vd)
 
 
-def make_workload(cfg, rank):
+def make_workload(cfg, rank, batch=0):
     from permutohedral_lattice_b200 import workloads
-    w = workloads.CONFIGS[cfg]()
+    w = workloads.CONFIGS[cfg](batch=batch) if batch and cfg >= 2 else workloads.CONFIGS[cfg]()
     if rank:   # another rank's batch: same distributions, other content
         rng = np.random.default_rng(1000 + rank)
         perm = rng.permutation(w.batch)
@@ -219,7 +221,7 @@ def run_reference(args, rank, world):
     """--impl reference: the reference's own CPU implementation of the path on the host cores."""
     if rank != 0:
         return
-    w = make_workload(args.config, 0)
+    w = make_workload(args.config, 0, args.batch)
     threads = host_threads(args.cpu_threads, w.batch)
     times = []
     info = None
@@ -267,7 +269,7 @@ def main():
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
 
-    w = make_workload(args.config, rank)
+    w = make_workload(args.config, rank, args.batch)
     b, n, c = w.batch, w.pixels_per_item, w.vd - 1
     use_positions = w.positions is not None
 

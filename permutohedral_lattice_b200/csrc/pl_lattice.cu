@@ -61,7 +61,7 @@ struct Header {   // first 256 bytes of the workspace
 };
 
 struct Layout {   // byte offsets into the workspace
-    size_t tile_info, rec, list_keys, list_ref, vid, vowner, table, nbr, v0, v1, total;
+    size_t tile_info, rec, rec_w, list_keys, list_ref, vid, vowner, table, nbr, v0, v1, total;
     u64 max_entries;   // capacity of entry- and vertex-indexed arrays
     u64 table_slots;   // allocated slots (power of two)
 };
@@ -175,7 +175,7 @@ __device__ __forceinline__ bool call_failed(const Header* hdr) {
 template <int PD>
 __global__ void __launch_bounds__(Cfg<PD>::TP)
 build_tiles(Geom g, const float* __restrict__ positions, const float* __restrict__ reference,
-            Header* hdr, int2* __restrict__ tile_info, u16* __restrict__ rec,
+            Header* hdr, int2* __restrict__ tile_info, u16* __restrict__ rec, float* __restrict__ rec_w,
             Key<Cfg<PD>::KW>* __restrict__ list_keys, u32 max_entries) {
     constexpr int KW = Cfg<PD>::KW, TP = Cfg<PD>::TP, SPLATS = Cfg<PD>::SPLATS, LS = Cfg<PD>::LS;
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -190,11 +190,15 @@ build_tiles(Geom g, const float* __restrict__ positions, const float* __restrict
 
     int item, pix;
     const bool valid = tile_point(g, tile, tid, item, pix);
+    float w[PD + 1];
+#pragma unroll
+    for (int r = 0; r <= PD; r++) w[r] = 0.f;
     if (valid) {
         float f[PD];
         load_features<PD>(g, positions, reference, item, pix, f);
         Simplex<PD> s;
         find_simplex<PD>(f, g.scale, s);
+        barycentric<PD>(s, w);
 #pragma unroll
         for (int r = 0; r <= PD; r++) {
             Key<KW> k;
@@ -249,6 +253,7 @@ build_tiles(Geom g, const float* __restrict__ positions, const float* __restrict
     __syncthreads();
     const int base = base_s;
     u16* rec_tile = rec + (size_t)tile * SPLATS;
+    float* recw_tile = rec_w + (size_t)tile * SPLATS;
 #pragma unroll
     for (int r = 0; r <= PD; r++) {
         const int me = r * TP + tid;
@@ -258,6 +263,7 @@ build_tiles(Geom g, const float* __restrict__ positions, const float* __restrict
             if (rep[r] == me && base >= 0) list_keys[(size_t)base + l] = keys_s[me];
         }
         rec_tile[me] = l;
+        recw_tile[me] = w[r];
     }
 }
 
@@ -439,85 +445,101 @@ struct LaneMap {
 };
 
 // ---------------------------------------------------------------------------------------------
-// splat_tiles: V[vertex] += sum over the tile's splats of weight * [input channels, 1].
-// The splats of a tile are counting-sorted by entry in shared memory, then each entry's run is
-// summed in registers by a group of lanes (one float4 of channels per lane) reading the tile's
-// input rows from shared memory, and leaves the CTA as one vector reduction per 16 bytes.
-// No floating-point atomics in shared memory, no per-entry row cache.
-// VD > 0: value dimension known at compile time; VD == 0: taken from vd_rt.
+// Bulk asynchronous copies (TMA engine, untiled form) with an mbarrier; every wait is bounded.
 // ---------------------------------------------------------------------------------------------
-template <int PD, int VD>
-struct SplatSmem {
-    static constexpr int TP = Cfg<PD>::TP, SPLATS = Cfg<PD>::SPLATS;
-    static size_t bytes(int vd) {
-        return sizeof(float) * (size_t)TP * padded_vd(vd) + sizeof(uint2) * SPLATS + 2 * sizeof(int) * SPLATS +
-               sizeof(int) * TP;
+__device__ __forceinline__ void mbar_init(u64* bar, unsigned count) {
+    const unsigned a = (unsigned)__cvta_generic_to_shared(bar);
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(a), "r"(count) : "memory");
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(u64* bar, unsigned bytes) {
+    const unsigned a = (unsigned)__cvta_generic_to_shared(bar);
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(a), "r"(bytes) : "memory");
+}
+// global -> shared, 16-byte aligned addresses, size a multiple of 16 bytes
+__device__ __forceinline__ void bulk_load(void* smem_dst, const void* gmem_src, unsigned bytes, u64* bar) {
+    const unsigned d = (unsigned)__cvta_generic_to_shared(smem_dst);
+    const unsigned a = (unsigned)__cvta_generic_to_shared(bar);
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(d),
+                 "l"(gmem_src), "r"(bytes), "r"(a)
+                 : "memory");
+}
+// Waits for phase `parity` of the barrier; gives up (returns false) after a bounded number of polls.
+__device__ __forceinline__ bool mbar_wait(u64* bar, unsigned parity) {
+    const unsigned a = (unsigned)__cvta_generic_to_shared(bar);
+    for (int it = 0; it < (1 << 20); it++) {
+        unsigned done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(done)
+            : "r"(a), "r"(parity)
+            : "memory");
+        if (done) return true;
     }
-};
+    return false;
+}
+// shared -> global
+__device__ __forceinline__ void bulk_store(void* gmem_dst, const void* smem_src, unsigned bytes) {
+    const unsigned sa = (unsigned)__cvta_generic_to_shared(smem_src);
+    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gmem_dst), "r"(sa), "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ void bulk_store_finish() {
+    asm volatile("cp.async.bulk.commit_group;\n\tcp.async.bulk.wait_group.read 0;" ::: "memory");
+}
+__device__ __forceinline__ void fence_async_proxy() {
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
 
-template <int PD, int VD>
-__global__ void __launch_bounds__(Cfg<PD>::TP)
-splat_tiles(Geom g, const float* __restrict__ positions, const float* __restrict__ reference,
-            const float* __restrict__ input, const Header* hdr, const int2* __restrict__ tile_info,
-            const u16* __restrict__ rec, const u32* __restrict__ list_ref, float* __restrict__ v0,
-            int vd_rt) {
-    constexpr int TP = Cfg<PD>::TP, SPLATS = Cfg<PD>::SPLATS, NW = TP / 32;
-    const int vd = VD ? VD : vd_rt;
-    const int C = vd - 1, VP = padded_vd(vd), QPR = VP >> 2;
-    extern __shared__ __align__(16) unsigned char smem_raw[];
-    float* in_s = reinterpret_cast<float*>(smem_raw);                       // [TP][VP]
-    uint2* sorted_s = reinterpret_cast<uint2*>(in_s + (size_t)TP * VP);     // [SPLATS] (point, weight)
-    int* cur_s = reinterpret_cast<int*>(sorted_s + SPLATS);                 // [SPLATS] count, then cursor
-    int* off_s = cur_s + SPLATS;                                            // [SPLATS] run start
-    int* prow_s = off_s + SPLATS;                                           // [TP] global row of each point
-    __shared__ int wsum_s[32];
-    if (call_failed(hdr)) return;
-    const int tid = threadIdx.x, tile = blockIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int2 info = tile_info[tile];
-    const int base = info.x, nloc = info.y;
-
+// First point and number of valid points of tile row `ly` (the run of points that is contiguous in
+// memory); returns false if the row lies outside the item.
+__device__ __forceinline__ bool tile_row(const Geom& g, int tile, int ly, int& first_row, int& count) {
     int item, pix;
-    const bool valid = tile_point(g, tile, tid, item, pix);
-    prow_s[tid] = valid ? item * g.n + pix : -1;
-    for (int i = tid; i < nloc; i += TP) cur_s[i] = 0;
-    // homogeneous channel and padding of this point's staged row
-    in_s[tid * VP + C] = 1.f;
-    for (int j = C + 1; j < VP; j++) in_s[tid * VP + j] = 0.f;
-    __syncthreads();
+    if (!tile_point(g, tile, ly * g.TX, item, pix)) return false;
+    const int x0 = pix % g.W;
+    first_row = item * g.n + pix;
+    count = min(g.TX, g.W - x0);
+    return true;
+}
 
-    // stage the tile's input rows: consecutive threads copy consecutive floats of global memory
-    for (int k = tid; k < TP * C; k += TP) {
-        const int p = k / C, j = k - p * C;
-        const int row = prow_s[p];
-        if (row >= 0) cp_async4(in_s + p * VP + j, input + (size_t)row * C + j);
-    }
+// ---------------------------------------------------------------------------------------------
+// splat_tiles: V[vertex] += sum over the tile's splats of weight * [input channels, 1].
+// The splats of a tile are counting-sorted by entry in shared memory, then every entry's run is
+// summed in registers, reading the tile's input rows from shared memory, and leaves the CTA as one
+// vector reduction per 16 bytes.  No floating-point atomics in shared memory.
+//
+// Fast form (VD known at compile time): one THREAD per entry holds the whole row in registers;
+// entries are handed to threads in order of run length so the lanes of a warp finish together; the
+// input block arrives by bulk asynchronous copies when its rows are 16-byte aligned.
+// Generic form (any vd): a group of lanes per entry, one float4 of channels per lane.
+// ---------------------------------------------------------------------------------------------
+template <int PD>
+struct SplatCommon {
+    static constexpr int TP = Cfg<PD>::TP, SPLATS = Cfg<PD>::SPLATS, NW = TP / 32;
 
-    float w[PD + 1];
-    int l[PD + 1];
-    if (valid) {
-        float f[PD];
-        load_features<PD>(g, positions, reference, item, pix, f);
-        Simplex<PD> s;
-        find_simplex<PD>(f, g.scale, s);
-        barycentric<PD>(s, w);
-        const u16* rec_tile = rec + (size_t)tile * SPLATS;
+    // Counting sort of the tile's splats by entry.  On return (after the trailing barrier):
+    // sorted_s[off_s[e] .. cur_s[e]) are entry e's (point, weight) pairs.  With order_s != nullptr,
+    // order_s[0..nloc) lists the entries by decreasing run length (clamped at 32).
+    __device__ static __forceinline__ void sort_splats(bool valid, const int* l, const float* w, int nloc,
+                                                       uint2* sorted_s, int* cur_s, int* off_s, u16* order_s,
+                                                       int* bucket_s, int* wsum_s) {
+        const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+        if (valid) {
 #pragma unroll
-        for (int r = 0; r <= PD; r++) {
-            l[r] = rec_tile[r * TP + tid];
-            atomicAdd(&cur_s[l[r]], 1);
+            for (int r = 0; r <= PD; r++) atomicAdd(&cur_s[l[r]], 1);
         }
-    }
-    __syncthreads();
-
-    // exclusive scan of the per-entry counts
-    {
-        int local[PD + 1];
+        __syncthreads();
+        int cnt[PD + 1], local[PD + 1];
         int sum = 0;
 #pragma unroll
         for (int r = 0; r <= PD; r++) {
             const int i = tid * (PD + 1) + r;
+            cnt[r] = (i < nloc) ? cur_s[i] : 0;
             local[r] = sum;
-            sum += (i < nloc) ? cur_s[i] : 0;
+            sum += cnt[r];
+            if (order_s && i < nloc) atomicAdd(&bucket_s[32 - min(max(cnt[r], 1), 32)], 1);
         }
         int incl = sum;
 #pragma unroll
@@ -536,6 +558,16 @@ splat_tiles(Geom g, const float* __restrict__ positions, const float* __restrict
                 if (lane >= d) vi += t;
             }
             wsum_s[lane] = vi - v;
+            if (order_s) {   // exclusive scan of the 32 run-length buckets (longest runs first)
+                const int b = bucket_s[lane];
+                int bi = b;
+#pragma unroll
+                for (int d = 1; d < 32; d <<= 1) {
+                    const int t = __shfl_up_sync(0xFFFFFFFFu, bi, d);
+                    if (lane >= d) bi += t;
+                }
+                bucket_s[lane] = bi - b;
+            }
         }
         __syncthreads();
         const int excl = incl - sum + wsum_s[warp];
@@ -545,17 +577,172 @@ splat_tiles(Geom g, const float* __restrict__ positions, const float* __restrict
             if (i < nloc) {
                 off_s[i] = excl + local[r];
                 cur_s[i] = excl + local[r];
+                if (order_s) order_s[atomicAdd(&bucket_s[32 - min(max(cnt[r], 1), 32)], 1)] = (u16)i;
             }
         }
-    }
-    __syncthreads();
-    if (valid) {
+        __syncthreads();
+        if (valid) {
 #pragma unroll
-        for (int r = 0; r <= PD; r++) {
-            const int pos = atomicAdd(&cur_s[l[r]], 1);
-            sorted_s[pos] = make_uint2((unsigned)tid, __float_as_uint(w[r]));
+            for (int r = 0; r <= PD; r++) {
+                const int pos = atomicAdd(&cur_s[l[r]], 1);
+                sorted_s[pos] = make_uint2((unsigned)tid, __float_as_uint(w[r]));
+            }
+        }
+        __syncthreads();
+    }
+};
+
+template <int PD, int VD>
+struct SplatFast {
+    static constexpr int TP = Cfg<PD>::TP, SPLATS = Cfg<PD>::SPLATS, C = VD - 1;
+    static constexpr size_t IN_BYTES = ((sizeof(float) * TP * C + 15) / 16) * 16;
+    static constexpr size_t BYTES =
+        IN_BYTES + sizeof(uint2) * SPLATS + 2 * sizeof(int) * SPLATS + sizeof(u16) * SPLATS + sizeof(int) * TP;
+};
+
+template <int PD, int VD>
+__global__ void __launch_bounds__(Cfg<PD>::TP)
+splat_tiles_fast(Geom g, const float* __restrict__ input, Header* hdr, const int2* __restrict__ tile_info,
+                 const u16* __restrict__ rec, const float* __restrict__ rec_w,
+                 const u32* __restrict__ list_ref, float* __restrict__ v0, int bulk_ok) {
+    constexpr int TP = Cfg<PD>::TP, SPLATS = Cfg<PD>::SPLATS, C = VD - 1, VP = (VD + 3) & ~3, QPR = VP / 4;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    float* in_s = reinterpret_cast<float*>(smem_raw);                                       // [TP][C]
+    uint2* sorted_s = reinterpret_cast<uint2*>(smem_raw + SplatFast<PD, VD>::IN_BYTES);     // [SPLATS]
+    int* cur_s = reinterpret_cast<int*>(sorted_s + SPLATS);                                 // [SPLATS]
+    int* off_s = cur_s + SPLATS;                                                            // [SPLATS]
+    int* prow_s = off_s + SPLATS;                                                           // [TP]
+    u16* order_s = reinterpret_cast<u16*>(prow_s + TP);                                     // [SPLATS]
+    __shared__ int wsum_s[32], bucket_s[32];
+    __shared__ __align__(8) u64 bar;
+    if (call_failed(hdr)) return;
+    const int tid = threadIdx.x, tile = blockIdx.x;
+    const int2 info = tile_info[tile];
+    const int base = info.x, nloc = info.y;
+
+    int item, pix;
+    const bool valid = tile_point(g, tile, tid, item, pix);
+    prow_s[tid] = valid ? item * g.n + pix : -1;
+    for (int i = tid; i < nloc; i += TP) cur_s[i] = 0;
+    if (tid < 32) bucket_s[tid] = 0;
+    if (bulk_ok && tid == 0) mbar_init(&bar, 1);
+    __syncthreads();
+
+    // stage the tile's input rows in shared memory, [point][channel] without padding
+    if (bulk_ok) {
+        if (tid == 0) {
+            unsigned total = 0;
+            for (int ly = 0; ly < g.TY; ly++) {
+                int first, count;
+                if (tile_row(g, tile, ly, first, count)) total += (unsigned)count * C * 4u;
+            }
+            mbar_expect_tx(&bar, total);
+            for (int ly = 0; ly < g.TY; ly++) {
+                int first, count;
+                if (tile_row(g, tile, ly, first, count))
+                    bulk_load(in_s + (size_t)ly * g.TX * C, input + (size_t)first * C, (unsigned)count * C * 4u, &bar);
+            }
+        }
+    } else {
+        for (int k = tid; k < TP * C; k += TP) {
+            const int p = k / C, j = k - p * C;
+            const int row = prow_s[p];
+            if (row >= 0) cp_async4(in_s + k, input + (size_t)row * C + j);
         }
     }
+
+    float w[PD + 1];
+    int l[PD + 1];
+    const u16* rec_tile = rec + (size_t)tile * SPLATS;
+    const float* recw_tile = rec_w + (size_t)tile * SPLATS;
+#pragma unroll
+    for (int r = 0; r <= PD; r++) {
+        l[r] = valid ? rec_tile[r * TP + tid] : 0;
+        w[r] = valid ? recw_tile[r * TP + tid] : 0.f;
+    }
+    SplatCommon<PD>::sort_splats(valid, l, w, nloc, sorted_s, cur_s, off_s, order_s, bucket_s, wsum_s);
+
+    if (bulk_ok) {
+        if (!mbar_wait(&bar, 0)) {
+            atomicOr(&hdr->status, 1u << PL_INTERNAL_ERROR);
+            return;
+        }
+    } else {
+        cp_async_wait_all();
+        __syncthreads();
+    }
+
+    for (int k = tid; k < nloc; k += TP) {
+        const int e = order_s[k];
+        const int beg = off_s[e], end = cur_s[e];
+        float acc[VP];
+#pragma unroll
+        for (int j = 0; j < VP; j++) acc[j] = 0.f;
+        for (int sidx = beg; sidx < end; sidx++) {
+            const uint2 pw = sorted_s[sidx];
+            const float wt = __uint_as_float(pw.y);
+            const float* x = in_s + pw.x * C;
+#pragma unroll
+            for (int j = 0; j < C; j++) acc[j] = PL_FADD(acc[j], PL_FMUL(wt, x[j]));
+            acc[C] = PL_FADD(acc[C], wt);
+        }
+        float* vrow = v0 + (size_t)list_ref[base + e] * VP;
+#pragma unroll
+        for (int q = 0; q < QPR; q++)
+            red_add_v4(vrow + 4 * q, make_float4(acc[4 * q], acc[4 * q + 1], acc[4 * q + 2], acc[4 * q + 3]));
+    }
+}
+
+template <int PD>
+struct SplatGeneric {
+    static constexpr int TP = Cfg<PD>::TP, SPLATS = Cfg<PD>::SPLATS;
+    static size_t bytes(int vd) {
+        return sizeof(float) * (size_t)TP * padded_vd(vd) + sizeof(uint2) * SPLATS + 2 * sizeof(int) * SPLATS +
+               sizeof(int) * TP;
+    }
+};
+
+template <int PD>
+__global__ void __launch_bounds__(Cfg<PD>::TP)
+splat_tiles_generic(Geom g, const float* __restrict__ input, Header* hdr, const int2* __restrict__ tile_info,
+                    const u16* __restrict__ rec, const float* __restrict__ rec_w,
+                    const u32* __restrict__ list_ref, float* __restrict__ v0, int vd) {
+    constexpr int TP = Cfg<PD>::TP, SPLATS = Cfg<PD>::SPLATS, NW = TP / 32;
+    const int C = vd - 1, VP = padded_vd(vd), QPR = VP >> 2;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    float* in_s = reinterpret_cast<float*>(smem_raw);                       // [TP][VP]
+    uint2* sorted_s = reinterpret_cast<uint2*>(in_s + (size_t)TP * VP);     // [SPLATS]
+    int* cur_s = reinterpret_cast<int*>(sorted_s + SPLATS);                 // [SPLATS]
+    int* off_s = cur_s + SPLATS;                                            // [SPLATS]
+    int* prow_s = off_s + SPLATS;                                           // [TP]
+    __shared__ int wsum_s[32];
+    if (call_failed(hdr)) return;
+    const int tid = threadIdx.x, tile = blockIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int2 info = tile_info[tile];
+    const int base = info.x, nloc = info.y;
+
+    int item, pix;
+    const bool valid = tile_point(g, tile, tid, item, pix);
+    prow_s[tid] = valid ? item * g.n + pix : -1;
+    for (int i = tid; i < nloc; i += TP) cur_s[i] = 0;
+    in_s[tid * VP + C] = 1.f;   // homogeneous channel, then padding
+    for (int j = C + 1; j < VP; j++) in_s[tid * VP + j] = 0.f;
+    __syncthreads();
+    for (int k = tid; k < TP * C; k += TP) {
+        const int p = k / C, j = k - p * C;
+        const int row = prow_s[p];
+        if (row >= 0) cp_async4(in_s + p * VP + j, input + (size_t)row * C + j);
+    }
+    float w[PD + 1];
+    int l[PD + 1];
+    const u16* rec_tile = rec + (size_t)tile * SPLATS;
+    const float* recw_tile = rec_w + (size_t)tile * SPLATS;
+#pragma unroll
+    for (int r = 0; r <= PD; r++) {
+        l[r] = valid ? rec_tile[r * TP + tid] : 0;
+        w[r] = valid ? recw_tile[r * TP + tid] : 0.f;
+    }
+    SplatCommon<PD>::sort_splats(valid, l, w, nloc, sorted_s, cur_s, off_s, nullptr, nullptr, wsum_s);
     cp_async_wait_all();
     __syncthreads();
 
@@ -616,23 +803,108 @@ blur_axis(const Header* hdr, const int* __restrict__ nbr_axis, const float* __re
 // ---------------------------------------------------------------------------------------------
 // slice_tiles (src/PermutohedralLatticeCPU.h:333-352: float multiply-then-add per remainder in
 // ascending order, reciprocal of the homogeneous channel in double, one multiply per channel).
-// The tile's vertex rows are staged once in shared memory; each thread derives the weights,
-// entry indices and normaliser of its own point; then groups of lanes (one float4 of channels per
-// lane) interpolate and write the output rows.
+// The tile's vertex rows are staged once in shared memory.
+//
+// Fast form (VD known at compile time): one thread per point interpolates the whole row in
+// registers (float4 reads of the cached rows, row stride padded against bank conflicts), the
+// output block is assembled in shared memory and leaves by bulk asynchronous copies when its rows
+// are 16-byte aligned.
+// Generic form (any vd): a group of lanes per point, one float4 of channels per lane.
 // ---------------------------------------------------------------------------------------------
+template <int PD, int VD>
+struct SliceFast {
+    static constexpr int TP = Cfg<PD>::TP, C = VD - 1, VP = (VD + 3) & ~3;
+    static constexpr int RS = VP + 4;   // words between cached rows: 16-byte aligned, spreads banks
+    static constexpr size_t OUT_BYTES = ((sizeof(float) * TP * C + 15) / 16) * 16;
+    static size_t bytes(int rows_cap) { return OUT_BYTES + sizeof(float) * (size_t)rows_cap * RS + sizeof(int) * TP; }
+};
+
+template <int PD, int VD>
+__global__ void __launch_bounds__(Cfg<PD>::TP)
+slice_tiles_fast(Geom g, float* __restrict__ output, const Header* hdr, const int2* __restrict__ tile_info,
+                 const u16* __restrict__ rec, const float* __restrict__ rec_w,
+                 const u32* __restrict__ list_ref, const float* __restrict__ vsrc, int rows_cap, int bulk_ok) {
+    constexpr int TP = Cfg<PD>::TP, SPLATS = Cfg<PD>::SPLATS, C = VD - 1, VP = (VD + 3) & ~3, QPR = VP / 4;
+    constexpr int RS = SliceFast<PD, VD>::RS;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    float* out_s = reinterpret_cast<float*>(smem_raw);                                          // [TP][C]
+    float* rows_s = reinterpret_cast<float*>(smem_raw + SliceFast<PD, VD>::OUT_BYTES);          // [rows_cap][RS]
+    int* prow_s = reinterpret_cast<int*>(rows_s + (size_t)rows_cap * RS);                       // [TP]
+    if (call_failed(hdr)) return;
+    const int tid = threadIdx.x, tile = blockIdx.x;
+    const int2 info = tile_info[tile];
+    const int base = info.x, cnt = info.y;
+    const int nrows = min(cnt, rows_cap);
+    const float4* v4 = reinterpret_cast<const float4*>(vsrc);
+    for (int i = tid; i < nrows * QPR; i += TP) {
+        const int lrow = i / QPR, q = i - lrow * QPR;
+        cp_async16(rows_s + lrow * RS + 4 * q, v4 + (size_t)list_ref[base + lrow] * QPR + q);
+    }
+    int item, pix;
+    const bool valid = tile_point(g, tile, tid, item, pix);
+    prow_s[tid] = valid ? item * g.n + pix : -1;
+    float w[PD + 1];
+    int l[PD + 1];
+    const u16* rec_tile = rec + (size_t)tile * SPLATS;
+    const float* recw_tile = rec_w + (size_t)tile * SPLATS;
+#pragma unroll
+    for (int r = 0; r <= PD; r++) {
+        l[r] = valid ? rec_tile[r * TP + tid] : 0;
+        w[r] = valid ? recw_tile[r * TP + tid] : 0.f;
+    }
+    cp_async_wait_all();
+    __syncthreads();
+    if (valid) {
+        float acc[VP];
+#pragma unroll
+        for (int j = 0; j < VP; j++) acc[j] = 0.f;
+#pragma unroll
+        for (int r = 0; r <= PD; r++) {
+            const float4* row = (l[r] < nrows) ? reinterpret_cast<const float4*>(rows_s + l[r] * RS)
+                                               : v4 + (size_t)list_ref[base + l[r]] * QPR;
+#pragma unroll
+            for (int q = 0; q < QPR; q++) {
+                const float4 x = row[q];
+                acc[4 * q] = PL_FADD(acc[4 * q], PL_FMUL(w[r], x.x));
+                acc[4 * q + 1] = PL_FADD(acc[4 * q + 1], PL_FMUL(w[r], x.y));
+                acc[4 * q + 2] = PL_FADD(acc[4 * q + 2], PL_FMUL(w[r], x.z));
+                acc[4 * q + 3] = PL_FADD(acc[4 * q + 3], PL_FMUL(w[r], x.w));
+            }
+        }
+        const float inv = (float)(1.0 / (double)acc[C]);
+#pragma unroll
+        for (int j = 0; j < C; j++) out_s[tid * C + j] = PL_FMUL(acc[j], inv);
+    }
+    if (bulk_ok) {
+        fence_async_proxy();
+        __syncthreads();
+        if (tid < g.TY) {
+            int first, count;
+            if (tile_row(g, tile, tid, first, count))
+                bulk_store(output + (size_t)first * C, out_s + (size_t)tid * g.TX * C, (unsigned)count * C * 4u);
+            bulk_store_finish();
+        }
+    } else {
+        __syncthreads();
+        for (int k = tid; k < TP * C; k += TP) {
+            const int p = k / C, j = k - p * C;
+            const int row = prow_s[p];
+            if (row >= 0) output[(size_t)row * C + j] = out_s[k];
+        }
+    }
+}
+
 template <int PD>
 struct SliceCfg {
     static constexpr int PW = ((2 * (PD + 1) + 1 + 3) / 4) * 4;   // words of a point record
 };
 
-template <int PD, int VD>
+template <int PD>
 __global__ void __launch_bounds__(Cfg<PD>::TP)
-slice_tiles(Geom g, const float* __restrict__ positions, const float* __restrict__ reference,
-            float* __restrict__ output, const Header* hdr, const int2* __restrict__ tile_info,
-            const u16* __restrict__ rec, const u32* __restrict__ list_ref,
-            const float* __restrict__ vsrc, int vd_rt, int rows_cap) {
+slice_tiles_generic(Geom g, float* __restrict__ output, const Header* hdr, const int2* __restrict__ tile_info,
+                    const u16* __restrict__ rec, const float* __restrict__ rec_w,
+                    const u32* __restrict__ list_ref, const float* __restrict__ vsrc, int vd, int rows_cap) {
     constexpr int TP = Cfg<PD>::TP, SPLATS = Cfg<PD>::SPLATS, PW = SliceCfg<PD>::PW;
-    const int vd = VD ? VD : vd_rt;
     const int C = vd - 1, VP = padded_vd(vd), QPR = VP >> 2;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     float4* rows4 = reinterpret_cast<float4*>(smem_raw);                            // [rows_cap][QPR]
@@ -648,21 +920,17 @@ slice_tiles(Geom g, const float* __restrict__ positions, const float* __restrict
         const int lrow = i / QPR, q = i - lrow * QPR;
         cp_async16(rows4 + i, v4 + (size_t)list_ref[base + lrow] * QPR + q);
     }
-
     int item, pix;
     const bool valid = tile_point(g, tile, tid, item, pix);
     prow_s[tid] = valid ? item * g.n + pix : -1;
     float w[PD + 1];
     int l[PD + 1];
-    if (valid) {
-        float f[PD];
-        load_features<PD>(g, positions, reference, item, pix, f);
-        Simplex<PD> s;
-        find_simplex<PD>(f, g.scale, s);
-        barycentric<PD>(s, w);
-        const u16* rec_tile = rec + (size_t)tile * SPLATS;
+    const u16* rec_tile = rec + (size_t)tile * SPLATS;
+    const float* recw_tile = rec_w + (size_t)tile * SPLATS;
 #pragma unroll
-        for (int r = 0; r <= PD; r++) l[r] = rec_tile[r * TP + tid];
+    for (int r = 0; r <= PD; r++) {
+        l[r] = valid ? rec_tile[r * TP + tid] : 0;
+        w[r] = valid ? recw_tile[r * TP + tid] : 0.f;
     }
     cp_async_wait_all();
     __syncthreads();
@@ -744,28 +1012,22 @@ __global__ void positions_kernel(const float* __restrict__ reference, float* __r
 
 template <int PD>
 __global__ void __launch_bounds__(Cfg<PD>::TP)
-export_points(Geom g, const float* __restrict__ positions, const float* __restrict__ reference,
-              const Header* hdr, const int2* __restrict__ tile_info, const u16* __restrict__ rec,
-              const u32* __restrict__ list_ref, int32_t* __restrict__ pixel_vertex,
-              float* __restrict__ pixel_weight) {
+export_points(Geom g, const Header* hdr, const int2* __restrict__ tile_info, const u16* __restrict__ rec,
+              const float* __restrict__ rec_w, const u32* __restrict__ list_ref,
+              int32_t* __restrict__ pixel_vertex, float* __restrict__ pixel_weight) {
     constexpr int TP = Cfg<PD>::TP, SPLATS = Cfg<PD>::SPLATS;
     if (hdr->status != 0) return;
     const int tid = threadIdx.x, tile = blockIdx.x;
     int item, pix;
     if (!tile_point(g, tile, tid, item, pix)) return;
     const int base = tile_info[tile].x;
-    float f[PD];
-    load_features<PD>(g, positions, reference, item, pix, f);
-    Simplex<PD> s;
-    find_simplex<PD>(f, g.scale, s);
-    float w[PD + 1];
-    barycentric<PD>(s, w);
     const u16* rec_tile = rec + (size_t)tile * SPLATS;
+    const float* recw_tile = rec_w + (size_t)tile * SPLATS;
     const size_t o = ((size_t)item * g.n + pix) * (PD + 1);
 #pragma unroll
     for (int r = 0; r <= PD; r++) {
         if (pixel_vertex) pixel_vertex[o + r] = (int32_t)list_ref[base + rec_tile[r * TP + tid]];
-        if (pixel_weight) pixel_weight[o + r] = w[r];
+        if (pixel_weight) pixel_weight[o + r] = recw_tile[r * TP + tid];
     }
 }
 
@@ -869,6 +1131,7 @@ static int make_layout(Layout& L, const Geom& g, int pd, int vd, int64_t max_ent
     size_t off = align_up(sizeof(Header));
     L.tile_info = off; off += align_up(sizeof(int2) * (size_t)g.num_tiles);
     L.rec = off;       off += align_up(sizeof(u16) * tile_splats * (size_t)g.num_tiles);
+    L.rec_w = off;     off += align_up(sizeof(float) * tile_splats * (size_t)g.num_tiles);
     L.list_keys = off; off += align_up(sizeof(u64) * kw_of(pd) * E);
     L.list_ref = off;  off += align_up(sizeof(u32) * E);
     L.vid = off;       off += align_up(sizeof(u32) * E);
@@ -902,31 +1165,54 @@ static int rows_cap_for(int pd, int vd) {
     return cap;
 }
 
-// splat_tiles / slice_tiles for value dimension vd: the instantiation with vd fixed at compile time
-// where there is one, else the run-time one.
+// True when every contiguous run of a tile's points starts on a 16-byte boundary and has a size that is
+// a multiple of 16 bytes in a [points][channels] float array at `ptr`: then the tile's block can move
+// by bulk asynchronous copies.
+static bool bulk_rows_ok(const Geom& g, const void* ptr, int channels) {
+    const long long row_bytes = 4ll * channels;
+    return ((uintptr_t)ptr % 16 == 0) && (row_bytes * g.W) % 16 == 0 && (row_bytes * g.TX) % 16 == 0 &&
+           (row_bytes * g.n) % 16 == 0 && (row_bytes * g.TX * g.TY) < (1ll << 31);
+}
+
+// splat / slice for value dimension vd: the instantiation with vd fixed at compile time where there
+// is one, else the generic one.
 template <int PD, int VD>
-static int launch_splat(const Geom& g, const float* positions, const float* reference, const float* input,
-                        const Header* hdr, const int2* tile_info, const u16* rec, const u32* list_ref,
-                        float* v0, int vd, cudaStream_t st) {
-    const size_t smem = SplatSmem<PD, VD>::bytes(vd);
-    if (smem > 200 * 1024) return PL_UNSUPPORTED_DIMS;
-    PL_CUDA(cudaFuncSetAttribute(splat_tiles<PD, VD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    splat_tiles<PD, VD><<<g.num_tiles, Cfg<PD>::TP, smem, st>>>(g, positions, reference, input, hdr, tile_info,
-                                                                rec, list_ref, v0, vd);
+static int launch_splat(const Geom& g, const float* input, Header* hdr, const int2* tile_info, const u16* rec,
+                        const float* rec_w, const u32* list_ref, float* v0, int vd, cudaStream_t st) {
+    if constexpr (VD > 0) {
+        const size_t smem = SplatFast<PD, VD>::BYTES;
+        PL_CUDA(cudaFuncSetAttribute(splat_tiles_fast<PD, VD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        splat_tiles_fast<PD, VD><<<g.num_tiles, Cfg<PD>::TP, smem, st>>>(
+            g, input, hdr, tile_info, rec, rec_w, list_ref, v0, bulk_rows_ok(g, input, VD - 1) ? 1 : 0);
+    } else {
+        const size_t smem = SplatGeneric<PD>::bytes(vd);
+        if (smem > 200 * 1024) return PL_UNSUPPORTED_DIMS;
+        PL_CUDA(cudaFuncSetAttribute(splat_tiles_generic<PD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        splat_tiles_generic<PD><<<g.num_tiles, Cfg<PD>::TP, smem, st>>>(g, input, hdr, tile_info, rec, rec_w,
+                                                                        list_ref, v0, vd);
+    }
     return PL_OK;
 }
 
 template <int PD, int VD>
-static int launch_slice(const Geom& g, const float* positions, const float* reference, float* output,
-                        const Header* hdr, const int2* tile_info, const u16* rec, const u32* list_ref,
-                        const float* vsrc, int vd, cudaStream_t st) {
-    int rows_cap = rows_cap_for(PD, vd);
-    const size_t fixed = sizeof(float) * Cfg<PD>::TP * SliceCfg<PD>::PW + sizeof(int) * Cfg<PD>::TP;
-    size_t smem = sizeof(float) * (size_t)rows_cap * padded_vd(vd) + fixed;
-    if (smem > 200 * 1024) return PL_UNSUPPORTED_DIMS;
-    PL_CUDA(cudaFuncSetAttribute(slice_tiles<PD, VD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    slice_tiles<PD, VD><<<g.num_tiles, Cfg<PD>::TP, smem, st>>>(g, positions, reference, output, hdr, tile_info,
-                                                                rec, list_ref, vsrc, vd, rows_cap);
+static int launch_slice(const Geom& g, float* output, const Header* hdr, const int2* tile_info, const u16* rec,
+                        const float* rec_w, const u32* list_ref, const float* vsrc, int vd, cudaStream_t st) {
+    if constexpr (VD > 0) {
+        int rows_cap = (48 * 1024) / (SliceFast<PD, VD>::RS * 4);
+        if (rows_cap > Cfg<PD>::SPLATS) rows_cap = Cfg<PD>::SPLATS;
+        const size_t smem = SliceFast<PD, VD>::bytes(rows_cap);
+        PL_CUDA(cudaFuncSetAttribute(slice_tiles_fast<PD, VD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        slice_tiles_fast<PD, VD><<<g.num_tiles, Cfg<PD>::TP, smem, st>>>(
+            g, output, hdr, tile_info, rec, rec_w, list_ref, vsrc, rows_cap, bulk_rows_ok(g, output, VD - 1) ? 1 : 0);
+    } else {
+        const int rows_cap = rows_cap_for(PD, vd);
+        const size_t fixed = sizeof(float) * Cfg<PD>::TP * SliceCfg<PD>::PW + sizeof(int) * Cfg<PD>::TP;
+        const size_t smem = sizeof(float) * (size_t)rows_cap * padded_vd(vd) + fixed;
+        if (smem > 200 * 1024) return PL_UNSUPPORTED_DIMS;
+        PL_CUDA(cudaFuncSetAttribute(slice_tiles_generic<PD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        slice_tiles_generic<PD><<<g.num_tiles, Cfg<PD>::TP, smem, st>>>(g, output, hdr, tile_info, rec, rec_w,
+                                                                        list_ref, vsrc, vd, rows_cap);
+    }
     return PL_OK;
 }
 
@@ -946,6 +1232,7 @@ static int run_filter(const Geom& g, float* output, const float* input, const fl
     Header* hdr = reinterpret_cast<Header*>(ws);
     int2* tile_info = reinterpret_cast<int2*>(ws + L.tile_info);
     u16* rec = reinterpret_cast<u16*>(ws + L.rec);
+    float* rec_w = reinterpret_cast<float*>(ws + L.rec_w);
     Key<KW>* list_keys = reinterpret_cast<Key<KW>*>(ws + L.list_keys);
     u32* list_ref = reinterpret_cast<u32*>(ws + L.list_ref);
     u32* vid = reinterpret_cast<u32*>(ws + L.vid);
@@ -970,15 +1257,14 @@ static int run_filter(const Geom& g, float* output, const float* input, const fl
     while ((1ull << table_log2) < L.table_slots) table_log2++;
 
     build_tiles<PD><<<g.num_tiles, TP, Cfg<PD>::BUILD_SMEM, st>>>(
-        g, positions, reference, hdr, tile_info, rec, list_keys, (u32)L.max_entries);
+        g, positions, reference, hdr, tile_info, rec, rec_w, list_keys, (u32)L.max_entries);
     if (ev) PL_CUDA(cudaEventRecord(ev[1], st));
     clear_table<<<wide, 256, 0, st>>>(hdr, table, (u32)table_log2);
     insert_entries<KW><<<wide, 256, 0, st>>>(hdr, table, list_keys, list_ref, vid, vowner);
     link_vertices<PD><<<wide, 256, 0, st>>>(hdr, table, list_keys, list_ref, vid, vowner, nbr, v0,
                                             L.max_entries, vd);
     if (ev) PL_CUDA(cudaEventRecord(ev[2], st));
-    int rc = PL_DISPATCH_VD(launch_splat, PD, vd, g, positions, reference, input, hdr, tile_info, rec,
-                            list_ref, v0, vd, st);
+    int rc = PL_DISPATCH_VD(launch_splat, PD, vd, g, input, hdr, tile_info, rec, rec_w, list_ref, v0, vd, st);
     if (rc != PL_OK) return rc;
     if (ev) PL_CUDA(cudaEventRecord(ev[3], st));
     float* src = v0;
@@ -991,8 +1277,7 @@ static int run_filter(const Geom& g, float* output, const float* input, const fl
         float* tmp = src; src = dst; dst = tmp;
     }
     if (ev) PL_CUDA(cudaEventRecord(ev[4], st));
-    rc = PL_DISPATCH_VD(launch_slice, PD, vd, g, positions, reference, output, hdr, tile_info, rec,
-                        list_ref, src, vd, st);
+    rc = PL_DISPATCH_VD(launch_slice, PD, vd, g, output, hdr, tile_info, rec, rec_w, list_ref, src, vd, st);
     if (rc != PL_OK) return rc;
     if (ev) PL_CUDA(cudaEventRecord(ev[5], st));
     PL_CUDA(cudaGetLastError());
@@ -1010,8 +1295,8 @@ static int run_export(const Geom& g, const float* positions, const float* refere
     if (g.num_tiles == 0) return PL_OK;
     if (pixel_vertex || pixel_weight)
         export_points<PD><<<g.num_tiles, TP, 0, st>>>(
-            g, positions, reference, hdr, reinterpret_cast<const int2*>(ws + L.tile_info),
-            reinterpret_cast<const u16*>(ws + L.rec), reinterpret_cast<const u32*>(ws + L.list_ref),
+            g, hdr, reinterpret_cast<const int2*>(ws + L.tile_info), reinterpret_cast<const u16*>(ws + L.rec),
+            reinterpret_cast<const float*>(ws + L.rec_w), reinterpret_cast<const u32*>(ws + L.list_ref),
             pixel_vertex, pixel_weight);
     if (vertex_keys || vertex_item)
         export_vertices<PD><<<num_sms() * 4, 256, 0, st>>>(
