@@ -519,27 +519,24 @@ template <int PD>
 struct SplatCommon {
     static constexpr int TP = Cfg<PD>::TP, SPLATS = Cfg<PD>::SPLATS, NW = TP / 32;
 
-    // Counting sort of the tile's splats by entry.  On return (after the trailing barrier):
-    // sorted_s[off_s[e] .. cur_s[e]) are entry e's (point, weight) pairs.  With order_s != nullptr,
-    // order_s[0..nloc) lists the entries by decreasing run length (clamped at 32).
+    // Counting sort of the tile's splats by entry.  On return (after the trailing barrier)
+    // sorted_s[off_s[e] .. cur_s[e]) are entry e's splats as (point | entry << 16, weight bits);
+    // cur_s must be zero for e < nloc on entry.  off_s may be nullptr when run starts are not needed.
     __device__ static __forceinline__ void sort_splats(bool valid, const int* l, const float* w, int nloc,
-                                                       uint2* sorted_s, int* cur_s, int* off_s, u16* order_s,
-                                                       int* bucket_s, int* wsum_s) {
+                                                       uint2* sorted_s, int* cur_s, int* off_s, int* wsum_s) {
         const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
         if (valid) {
 #pragma unroll
             for (int r = 0; r <= PD; r++) atomicAdd(&cur_s[l[r]], 1);
         }
         __syncthreads();
-        int cnt[PD + 1], local[PD + 1];
+        int local[PD + 1];
         int sum = 0;
 #pragma unroll
         for (int r = 0; r <= PD; r++) {
             const int i = tid * (PD + 1) + r;
-            cnt[r] = (i < nloc) ? cur_s[i] : 0;
             local[r] = sum;
-            sum += cnt[r];
-            if (order_s && i < nloc) atomicAdd(&bucket_s[32 - min(max(cnt[r], 1), 32)], 1);
+            sum += (i < nloc) ? cur_s[i] : 0;
         }
         int incl = sum;
 #pragma unroll
@@ -558,16 +555,6 @@ struct SplatCommon {
                 if (lane >= d) vi += t;
             }
             wsum_s[lane] = vi - v;
-            if (order_s) {   // exclusive scan of the 32 run-length buckets (longest runs first)
-                const int b = bucket_s[lane];
-                int bi = b;
-#pragma unroll
-                for (int d = 1; d < 32; d <<= 1) {
-                    const int t = __shfl_up_sync(0xFFFFFFFFu, bi, d);
-                    if (lane >= d) bi += t;
-                }
-                bucket_s[lane] = bi - b;
-            }
         }
         __syncthreads();
         const int excl = incl - sum + wsum_s[warp];
@@ -575,9 +562,8 @@ struct SplatCommon {
         for (int r = 0; r <= PD; r++) {
             const int i = tid * (PD + 1) + r;
             if (i < nloc) {
-                off_s[i] = excl + local[r];
+                if (off_s) off_s[i] = excl + local[r];
                 cur_s[i] = excl + local[r];
-                if (order_s) order_s[atomicAdd(&bucket_s[32 - min(max(cnt[r], 1), 32)], 1)] = (u16)i;
             }
         }
         __syncthreads();
@@ -585,7 +571,7 @@ struct SplatCommon {
 #pragma unroll
             for (int r = 0; r <= PD; r++) {
                 const int pos = atomicAdd(&cur_s[l[r]], 1);
-                sorted_s[pos] = make_uint2((unsigned)tid, __float_as_uint(w[r]));
+                sorted_s[pos] = make_uint2((unsigned)tid | ((unsigned)l[r] << 16), __float_as_uint(w[r]));
             }
         }
         __syncthreads();
@@ -596,24 +582,31 @@ template <int PD, int VD>
 struct SplatFast {
     static constexpr int TP = Cfg<PD>::TP, SPLATS = Cfg<PD>::SPLATS, C = VD - 1;
     static constexpr size_t IN_BYTES = ((sizeof(float) * TP * C + 15) / 16) * 16;
-    static constexpr size_t BYTES =
-        IN_BYTES + sizeof(uint2) * SPLATS + 2 * sizeof(int) * SPLATS + sizeof(u16) * SPLATS + sizeof(int) * TP;
+    static constexpr size_t BYTES = IN_BYTES + sizeof(uint2) * SPLATS + sizeof(int) * SPLATS + sizeof(int) * TP;
 };
+
+// Adds a row held in registers to vertex row `vrow` (VP floats, 16-byte aligned).
+template <int VP>
+__device__ __forceinline__ void flush_row(float* vrow, float* acc) {
+#pragma unroll
+    for (int q = 0; q < VP / 4; q++)
+        red_add_v4(vrow + 4 * q, make_float4(acc[4 * q], acc[4 * q + 1], acc[4 * q + 2], acc[4 * q + 3]));
+#pragma unroll
+    for (int j = 0; j < VP; j++) acc[j] = 0.f;
+}
 
 template <int PD, int VD>
 __global__ void __launch_bounds__(Cfg<PD>::TP)
 splat_tiles_fast(Geom g, const float* __restrict__ input, Header* hdr, const int2* __restrict__ tile_info,
                  const u16* __restrict__ rec, const float* __restrict__ rec_w,
                  const u32* __restrict__ list_ref, float* __restrict__ v0, int bulk_ok) {
-    constexpr int TP = Cfg<PD>::TP, SPLATS = Cfg<PD>::SPLATS, C = VD - 1, VP = (VD + 3) & ~3, QPR = VP / 4;
+    constexpr int TP = Cfg<PD>::TP, SPLATS = Cfg<PD>::SPLATS, C = VD - 1, VP = (VD + 3) & ~3;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     float* in_s = reinterpret_cast<float*>(smem_raw);                                       // [TP][C]
     uint2* sorted_s = reinterpret_cast<uint2*>(smem_raw + SplatFast<PD, VD>::IN_BYTES);     // [SPLATS]
     int* cur_s = reinterpret_cast<int*>(sorted_s + SPLATS);                                 // [SPLATS]
-    int* off_s = cur_s + SPLATS;                                                            // [SPLATS]
-    int* prow_s = off_s + SPLATS;                                                           // [TP]
-    u16* order_s = reinterpret_cast<u16*>(prow_s + TP);                                     // [SPLATS]
-    __shared__ int wsum_s[32], bucket_s[32];
+    int* prow_s = cur_s + SPLATS;                                                           // [TP]
+    __shared__ int wsum_s[32];
     __shared__ __align__(8) u64 bar;
     if (call_failed(hdr)) return;
     const int tid = threadIdx.x, tile = blockIdx.x;
@@ -624,9 +617,8 @@ splat_tiles_fast(Geom g, const float* __restrict__ input, Header* hdr, const int
     const bool valid = tile_point(g, tile, tid, item, pix);
     prow_s[tid] = valid ? item * g.n + pix : -1;
     for (int i = tid; i < nloc; i += TP) cur_s[i] = 0;
-    if (tid < 32) bucket_s[tid] = 0;
     if (bulk_ok && tid == 0) mbar_init(&bar, 1);
-    __syncthreads();
+    const int nvalid = __syncthreads_count(valid);
 
     // stage the tile's input rows in shared memory, [point][channel] without padding
     if (bulk_ok) {
@@ -660,7 +652,7 @@ splat_tiles_fast(Geom g, const float* __restrict__ input, Header* hdr, const int
         l[r] = valid ? rec_tile[r * TP + tid] : 0;
         w[r] = valid ? recw_tile[r * TP + tid] : 0.f;
     }
-    SplatCommon<PD>::sort_splats(valid, l, w, nloc, sorted_s, cur_s, off_s, order_s, bucket_s, wsum_s);
+    SplatCommon<PD>::sort_splats(valid, l, w, nloc, sorted_s, cur_s, nullptr, wsum_s);
 
     if (bulk_ok) {
         if (!mbar_wait(&bar, 0)) {
@@ -672,25 +664,32 @@ splat_tiles_fast(Geom g, const float* __restrict__ input, Header* hdr, const int
         __syncthreads();
     }
 
-    for (int k = tid; k < nloc; k += TP) {
-        const int e = order_s[k];
-        const int beg = off_s[e], end = cur_s[e];
-        float acc[VP];
+    // Every thread sums a window of PD+1 consecutive sorted splats in registers; whenever the entry
+    // changes, and at the end of the window, the partial row leaves as vector reductions.
+    const int total = nvalid * (PD + 1);
+    const int first = tid * (PD + 1);
+    if (first >= total) return;
+    float acc[VP];
 #pragma unroll
-        for (int j = 0; j < VP; j++) acc[j] = 0.f;
-        for (int sidx = beg; sidx < end; sidx++) {
-            const uint2 pw = sorted_s[sidx];
+    for (int j = 0; j < VP; j++) acc[j] = 0.f;
+    int cur = (int)(sorted_s[first].x >> 16);
+#pragma unroll
+    for (int i = 0; i <= PD; i++) {
+        if (first + i < total) {
+            const uint2 pw = sorted_s[first + i];
+            const int e = (int)(pw.x >> 16);
+            if (e != cur) {
+                flush_row<VP>(v0 + (size_t)list_ref[base + cur] * VP, acc);
+                cur = e;
+            }
             const float wt = __uint_as_float(pw.y);
-            const float* x = in_s + pw.x * C;
+            const float* x = in_s + (pw.x & 0xFFFFu) * C;
 #pragma unroll
             for (int j = 0; j < C; j++) acc[j] = PL_FADD(acc[j], PL_FMUL(wt, x[j]));
             acc[C] = PL_FADD(acc[C], wt);
         }
-        float* vrow = v0 + (size_t)list_ref[base + e] * VP;
-#pragma unroll
-        for (int q = 0; q < QPR; q++)
-            red_add_v4(vrow + 4 * q, make_float4(acc[4 * q], acc[4 * q + 1], acc[4 * q + 2], acc[4 * q + 3]));
     }
+    flush_row<VP>(v0 + (size_t)list_ref[base + cur] * VP, acc);
 }
 
 template <int PD>
@@ -742,7 +741,7 @@ splat_tiles_generic(Geom g, const float* __restrict__ input, Header* hdr, const 
         l[r] = valid ? rec_tile[r * TP + tid] : 0;
         w[r] = valid ? recw_tile[r * TP + tid] : 0.f;
     }
-    SplatCommon<PD>::sort_splats(valid, l, w, nloc, sorted_s, cur_s, off_s, nullptr, nullptr, wsum_s);
+    SplatCommon<PD>::sort_splats(valid, l, w, nloc, sorted_s, cur_s, off_s, wsum_s);
     cp_async_wait_all();
     __syncthreads();
 
@@ -757,7 +756,7 @@ splat_tiles_generic(Geom g, const float* __restrict__ input, Header* hdr, const 
             for (int sidx = beg; sidx < end; sidx++) {
                 const uint2 pw = sorted_s[sidx];
                 const float wt = __uint_as_float(pw.y);
-                const float4 x = in4[pw.x * QPR + q];
+                const float4 x = in4[(pw.x & 0xFFFFu) * QPR + q];
                 acc.x = PL_FADD(acc.x, PL_FMUL(wt, x.x));
                 acc.y = PL_FADD(acc.y, PL_FMUL(wt, x.y));
                 acc.z = PL_FADD(acc.z, PL_FMUL(wt, x.z));
