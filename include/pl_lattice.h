@@ -96,6 +96,28 @@ int pl_lattice_filter_f32(float* output, const float* input, const float* refere
                           float theta_beta, float theta_gamma, int reverse, void* workspace,
                           size_t workspace_bytes, int64_t max_entries, int mode, void* stream);
 
+/* The op for callers that must not allocate device memory and have no buffer to lend: a plugin
+ * loaded into a host application whose memory pool already owns the GPU's memory, or a service that
+ * forbids allocation calls once it is running.  Same arguments and results as
+ * pl_lattice_filter_f32 (atomic mode), but the scratch is an array built into the library image:
+ * PL_STATIC_SCRATCH_BYTES on every GPU that loads the library, held until the process exits.
+ * This entry point has no counterpart in the reference.
+ *  - It calls no cudaMalloc / cudaFree and no allocating library routine.
+ *  - A call whose pl_workspace_bytes exceeds PL_STATIC_SCRATCH_BYTES returns
+ *    PL_WORKSPACE_TOO_SMALL before launching anything (pl_last_cuda_error then holds the two sizes);
+ *    a smaller max_entries shrinks the need.
+ *  - The first call on each device looks up the scratch's device address (the device must be
+ *    current, as for every call); make that first call outside any stream capture.
+ *  - All calls on a device share the one scratch, which keeps the previous call's contents; each call
+ *    clears what it needs zeroed.  Two calls that overlap on the GPU (different streams, different
+ *    host threads) race on it: serialise them. */
+#define PL_STATIC_SCRATCH_BYTES (64u << 20)
+int pl_lattice_filter_f32_noalloc(float* output, const float* input, const float* reference, int batch,
+                                  int n_spatial_dims, const int* spatial_dims, int n_input_channels,
+                                  int n_reference_channels, int bilateral, float theta_alpha,
+                                  float theta_beta, float theta_gamma, int reverse, int64_t max_entries,
+                                  void* stream);
+
 /* Profiling aid: the next pl_filter_f32 / pl_lattice_filter_f32 call made by this host thread records
  * the PL_NUM_STAGE_EVENTS cudaEvent_t handles of stage_events[] on its stream at the stage
  * boundaries (start, after build, after index, after splat, after blur, after slice), then forgets

@@ -20,6 +20,7 @@
 // compared through the entry list, which a previous launch has completely written, so there are no
 // locks, no waiting and no duplicate vertices.  All device loops are bounded.
 #include <cuda_runtime.h>
+#include <mutex>
 #include <stdint.h>
 #include <stdio.h>
 #include <string.h>
@@ -1332,6 +1333,28 @@ static int filter_common(const Geom& g, float* output, const float* input, const
 #undef CALL
 }
 
+// Scratch of pl_lattice_filter_f32_noalloc: lives in the library image, one copy on every GPU that
+// loads the library, until the process exits.  In host code the array's name is only a handle; the
+// device address comes from cudaGetSymbolAddress, once per device, with that device current.
+static __device__ __align__(256) unsigned char g_static_scratch[PL_STATIC_SCRATCH_BYTES];
+constexpr int MAX_DEVICES = 64;
+static void* g_static_scratch_addr[MAX_DEVICES] = {nullptr};
+static std::mutex g_static_scratch_mutex;
+
+static int static_scratch_of_current_device(void** out) {
+    int dev = -1;
+    PL_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= MAX_DEVICES) return PL_INVALID_ARGUMENT;
+    std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
+    if (!g_static_scratch_addr[dev]) {
+        void* addr = nullptr;
+        PL_CUDA(cudaGetSymbolAddress(&addr, g_static_scratch));
+        g_static_scratch_addr[dev] = addr;
+    }
+    *out = g_static_scratch_addr[dev];
+    return PL_OK;
+}
+
 }  // namespace pl
 
 using namespace pl;
@@ -1453,6 +1476,40 @@ int pl_lattice_filter_f32(float* output, const float* input, const float* refere
     if (!output || !input || !workspace || (g.R > 0 && !reference)) return PL_INVALID_ARGUMENT;
     return filter_common(g, output, input, nullptr, reference, pd, vd, reverse, workspace,
                          workspace_bytes, max_entries, mode, (cudaStream_t)stream);
+}
+
+int pl_lattice_filter_f32_noalloc(float* output, const float* input, const float* reference, int batch,
+                                  int n_spatial_dims, const int* spatial_dims, int n_input_channels,
+                                  int n_reference_channels, int bilateral, float theta_alpha,
+                                  float theta_beta, float theta_gamma, int reverse, int64_t max_entries,
+                                  void* stream) {
+    if (n_input_channels < 1) return PL_INVALID_ARGUMENT;
+    Geom g;
+    int pd = 0, n = 0;
+    int rc = op_geom(g, batch, n_spatial_dims, spatial_dims, n_reference_channels, bilateral, theta_alpha,
+                     theta_beta, theta_gamma, &pd, &n);
+    if (rc != PL_OK) return rc;
+    const int vd = n_input_channels + 1;
+    if (!pl_supported(pd, vd)) return PL_UNSUPPORTED_DIMS;
+    if (batch == 0 || n == 0) return PL_OK;
+    if (!output || !input || (g.R > 0 && !reference)) return PL_INVALID_ARGUMENT;
+    // sizes beyond the built-in scratch are refused before anything is launched
+    Layout L;
+    rc = make_layout(L, g, pd, vd, max_entries);
+    if (rc != PL_OK) return rc;
+    if (L.total > (size_t)PL_STATIC_SCRATCH_BYTES) {
+        snprintf(g_cuda_error, sizeof(g_cuda_error),
+                 "pl_lattice_filter_f32_noalloc: this call needs %zu bytes of scratch, the built-in scratch holds %zu",
+                 L.total, (size_t)PL_STATIC_SCRATCH_BYTES);
+        return PL_WORKSPACE_TOO_SMALL;
+    }
+    void* scratch = nullptr;
+    rc = static_scratch_of_current_device(&scratch);   // first call on a device: looks the address up
+    if (rc != PL_OK) return rc;
+    // the call itself zeroes the counters it needs (the 256-byte header) and the value rows it sums
+    // into; everything else in the scratch is written before it is read
+    return filter_common(g, output, input, nullptr, reference, pd, vd, reverse, scratch,
+                         (size_t)PL_STATIC_SCRATCH_BYTES, max_entries, PL_MODE_ATOMIC, (cudaStream_t)stream);
 }
 
 int pl_profile_next_call(void** stage_events) {
