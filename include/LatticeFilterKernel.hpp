@@ -1,0 +1,172 @@
+// C++ host layer over the C ABI (pl_lattice.h): the reference's device functors and op class with
+// their own parameter lists, for callers that used src/LatticeFilterKernel.h.
+//
+//   pl::ComputeKernel<pl::GpuDevice, float>   <->  ComputeKernel<GPUDevice, T>   src/LatticeFilterKernel.h:40-54
+//   pl::LatticeFilter<pl::GpuDevice, float>   <->  LatticeFilter<GPUDevice, T>   src/LatticeFilterKernel.h:28-38
+//   pl::LatticeFilterOp                       <->  LatticeFilterOp<GPUDevice, T> src/LatticeFilterKernel.cpp:87-181
+//
+// The TensorFlow slots become two small types: GpuDevice carries the stream (Eigen::GpuDevice::stream()),
+// OpContext lends scratch memory the way OpKernelContext::allocate_temp does.  Errors are C++ exceptions
+// carrying the pl_status (the reference aborts the process: LOG(FATAL), exit, throw 1).
+#ifndef PL_LATTICE_FILTER_KERNEL_HPP
+#define PL_LATTICE_FILTER_KERNEL_HPP
+
+#include <cstddef>
+#include <cstdint>
+#include <functional>
+#include <stdexcept>
+#include <string>
+#include <vector>
+
+#include "pl_lattice.h"
+
+namespace pl {
+
+struct Error : std::runtime_error {
+    int status;
+    Error(int status_, const std::string& where)
+        : std::runtime_error(where + ": " + pl_strerror(status_) +
+                             (status_ == PL_CUDA_ERROR ? std::string(" (") + pl_last_cuda_error() + ")" : "")),
+          status(status_) {}
+};
+
+inline void check(int status, const char* where) {
+    if (status != PL_OK) throw Error(status, where);
+}
+
+// Stands for Eigen::GpuDevice: the stream all work is ordered on (a cudaStream_t).
+struct GpuDevice {
+    void* stream_ = nullptr;
+    void* stream() const { return stream_; }
+};
+
+// Stands for OpKernelContext: lends device scratch for the duration of one Compute.  The caller
+// supplies the allocator (a framework's temp allocator, a pool, cudaMalloc...); this layer never
+// allocates device memory by itself.  The buffer is kept and reused while it is large enough.
+class OpContext {
+public:
+    using Alloc = std::function<void*(size_t)>;
+    using Free = std::function<void(void*)>;
+    OpContext(Alloc alloc, Free free) : alloc_(std::move(alloc)), free_(std::move(free)) {}
+    ~OpContext() { release(); }
+    OpContext(const OpContext&) = delete;
+    OpContext& operator=(const OpContext&) = delete;
+
+    void* allocate_temp(size_t bytes) {
+        if (bytes > bytes_) {
+            release();
+            ptr_ = alloc_(bytes);
+            if (!ptr_) throw Error(PL_WORKSPACE_TOO_SMALL, "OpContext::allocate_temp");
+            bytes_ = bytes;
+        }
+        return ptr_;
+    }
+    size_t temp_bytes() const { return bytes_; }
+    void* temp() const { return ptr_; }
+    void release() {
+        if (ptr_) free_(ptr_);
+        ptr_ = nullptr;
+        bytes_ = 0;
+    }
+
+private:
+    Alloc alloc_;
+    Free free_;
+    void* ptr_ = nullptr;
+    size_t bytes_ = 0;
+};
+
+template <typename Device, typename T>
+struct ComputeKernel;
+template <typename Device, typename T>
+struct LatticeFilter;
+
+// positions <- [coordinate / spatial_std ..., reference / features_std ...] for one batch item.
+template <>
+struct ComputeKernel<GpuDevice, float> {
+    void operator()(const GpuDevice& d, OpContext* /*context*/, const float* reference_image, float* positions,
+                    int num_super_pixels, int n_spatial_dims, int* spatial_dims /* host */,
+                    int n_reference_channels, float spatial_std, float features_std) {
+        check(pl_compute_positions_f32(reference_image, positions, num_super_pixels, n_reference_channels,
+                                       n_spatial_dims, spatial_dims, spatial_std, features_std, d.stream()),
+              "ComputeKernel");
+    }
+};
+
+// output <- lattice filter of input at positions, one batch item (any supported pd, vd at run time;
+// the reference accepts exactly one compiled pair, src/LatticeFilterKernel.cu:87-100).
+template <>
+struct LatticeFilter<GpuDevice, float> {
+    void operator()(const GpuDevice& d, OpContext* context, float* output, const float* input,
+                    const float* positions, int num_super_pixels, int pd, int vd, bool reverse) {
+        size_t bytes = 0;
+        check(pl_workspace_bytes(1, num_super_pixels, pd, vd, 0, nullptr, 0, &bytes), "LatticeFilter");
+        void* ws = context->allocate_temp(bytes);
+        check(pl_filter_f32(output, input, positions, 1, num_super_pixels, pd, vd, reverse ? 1 : 0, ws,
+                            context->temp_bytes(), 0, PL_MODE_ATOMIC, d.stream()),
+              "LatticeFilter");
+    }
+};
+
+// The op: attributes at construction, Compute on device tensors [batch, *spatial, channels].
+class LatticeFilterOp {
+public:
+    LatticeFilterOp(bool reverse = false, bool bilateral = true, float theta_alpha = 1.f, float theta_beta = 1.f,
+                    float theta_gamma = 1.f)
+        : reverse_(reverse), bilateral_(bilateral), theta_alpha_(theta_alpha), theta_beta_(theta_beta),
+          theta_gamma_(theta_gamma) {}
+
+    // input_shape = {batch, s_1..s_k, channels}; reference has the same batch and spatial dims and
+    // n_reference_channels channels (ignored when bilateral is false).  One launch sequence for the
+    // whole batch, features fused (no positions tensor).
+    void Compute(const GpuDevice& d, OpContext* context, const float* input, const std::vector<int>& input_shape,
+                 const float* reference, int n_reference_channels, float* output) const {
+        if (input_shape.size() < 3) throw Error(PL_INVALID_ARGUMENT, "LatticeFilterOp::Compute");
+        const int batch = input_shape.front(), channels = input_shape.back();
+        std::vector<int> sdims(input_shape.begin() + 1, input_shape.end() - 1);
+        long long n = 1;
+        for (int s : sdims) n *= s;
+        const int pd = (int)sdims.size() + (bilateral_ ? n_reference_channels : 0), vd = channels + 1;
+        if (batch == 0 || n == 0) return;
+        size_t bytes = 0;
+        check(pl_workspace_bytes(batch, (int)n, pd, vd, (int)sdims.size(), sdims.data(), 0, &bytes),
+              "LatticeFilterOp::Compute");
+        void* ws = context->allocate_temp(bytes);
+        check(pl_lattice_filter_f32(output, input, reference, batch, (int)sdims.size(), sdims.data(), channels,
+                                    n_reference_channels, bilateral_ ? 1 : 0, theta_alpha_, theta_beta_,
+                                    theta_gamma_, reverse_ ? 1 : 0, ws, context->temp_bytes(), 0, PL_MODE_ATOMIC,
+                                    d.stream()),
+              "LatticeFilterOp::Compute");
+    }
+
+    // The reference's own structure (src/LatticeFilterKernel.cpp:145-179): a positions buffer, then
+    // ComputeKernel + LatticeFilter per batch item.  positions must hold n * pd floats (device).
+    void ComputePerItem(const GpuDevice& d, OpContext* context, const float* input,
+                        const std::vector<int>& input_shape, const float* reference, int n_reference_channels,
+                        float* positions, float* output) const {
+        if (input_shape.size() < 3) throw Error(PL_INVALID_ARGUMENT, "LatticeFilterOp::ComputePerItem");
+        const int batch = input_shape.front(), channels = input_shape.back();
+        std::vector<int> sdims(input_shape.begin() + 1, input_shape.end() - 1);
+        long long n = 1;
+        for (int s : sdims) n *= s;
+        const int r = bilateral_ ? n_reference_channels : 0;
+        const int pd = (int)sdims.size() + r, vd = channels + 1;
+        const float spatial_std = bilateral_ ? theta_alpha_ : theta_gamma_;
+        const float features_std = bilateral_ ? theta_beta_ : -1.f;
+        for (int b = 0; b < batch; b++) {
+            ComputeKernel<GpuDevice, float>()(d, context, r ? reference + (size_t)b * n * r : nullptr, positions,
+                                              (int)n, (int)sdims.size(), sdims.data(), r, spatial_std,
+                                              features_std);
+            LatticeFilter<GpuDevice, float>()(d, context, output + (size_t)b * n * channels,
+                                              input + (size_t)b * n * channels, positions, (int)n, pd, vd,
+                                              reverse_);
+        }
+    }
+
+private:
+    bool reverse_, bilateral_;
+    float theta_alpha_, theta_beta_, theta_gamma_;
+};
+
+}  // namespace pl
+#endif  // PL_LATTICE_FILTER_KERNEL_HPP

@@ -39,3 +39,23 @@ def build(force=False, verbose=False):
 
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))
+
+
+HOST_TEST_SRC = os.path.join(ROOT, "tests", "helpers", "host_class_test.cpp")
+HOST_TEST_BIN = os.path.join(ROOT, "tests", "helpers", "host_class_test.bin")
+
+
+def build_host_class_test(force=False):
+    """C++ program over include/LatticeFilterKernel.hpp used by the GPU tests (built here, runs on the
+    GPU box)."""
+    deps = [HOST_TEST_SRC, os.path.join(ROOT, "include", "LatticeFilterKernel.hpp"), LIB]
+    if not force and os.path.exists(HOST_TEST_BIN) and all(
+            os.path.getmtime(HOST_TEST_BIN) >= os.path.getmtime(d) for d in deps):
+        return HOST_TEST_BIN
+    cuda = os.path.dirname(os.path.dirname(nvcc_path())) if os.path.sep in nvcc_path() else "/usr/local/cuda"
+    cmd = ["g++", "-O2", "-std=c++17", "-I", os.path.join(ROOT, "include"), "-I", os.path.join(cuda, "include"),
+           HOST_TEST_SRC, "-o", HOST_TEST_BIN, "-L", PKG, "-lpl_lattice", "-L", os.path.join(cuda, "lib64"),
+           "-lcudart", "-Wl,-rpath,$ORIGIN/../../permutohedral_lattice_b200",
+           "-Wl,-rpath," + os.path.join(cuda, "lib64")]
+    subprocess.check_call(cmd)
+    return HOST_TEST_BIN

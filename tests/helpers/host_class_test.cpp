@@ -1,0 +1,75 @@
+// Drives include/LatticeFilterKernel.hpp on a GPU: reads a problem from a binary file, runs the op
+// both ways (whole batch, and the reference's per-item ComputeKernel + LatticeFilter structure) and
+// writes both outputs back.  File layout (little endian): int32 header
+// {batch, n_sdims, sdims[3], C, R, bilateral, reverse}, float32 {theta_alpha, theta_beta, theta_gamma},
+// then input [batch, n, C] and reference [batch, n, R] as float32.
+#include <cuda_runtime.h>
+
+#include <cstdio>
+#include <cstdlib>
+#include <vector>
+
+#include "LatticeFilterKernel.hpp"
+
+static void die(const char* what) {
+    fprintf(stderr, "host_class_test: %s\n", what);
+    exit(2);
+}
+
+int main(int argc, char** argv) {
+    if (argc != 3) die("usage: host_class_test <in> <out>");
+    FILE* f = fopen(argv[1], "rb");
+    if (!f) die("cannot open input");
+    int hdr[9];
+    float theta[3];
+    if (fread(hdr, 4, 9, f) != 9 || fread(theta, 4, 3, f) != 3) die("short header");
+    const int batch = hdr[0], n_sdims = hdr[1], C = hdr[5], R = hdr[6], bilateral = hdr[7], reverse = hdr[8];
+    std::vector<int> shape = {batch};
+    size_t n = 1;
+    for (int i = 0; i < n_sdims; i++) { shape.push_back(hdr[2 + i]); n *= hdr[2 + i]; }
+    shape.push_back(C);
+    std::vector<float> in(batch * n * C), ref(batch * n * R), out(batch * n * C), out2(batch * n * C);
+    if (fread(in.data(), 4, in.size(), f) != in.size()) die("short input");
+    if (R && fread(ref.data(), 4, ref.size(), f) != ref.size()) die("short reference");
+    fclose(f);
+
+    float *d_in, *d_ref = nullptr, *d_out, *d_pos;
+    cudaStream_t stream;
+    if (cudaStreamCreate(&stream) != cudaSuccess) die("no CUDA device");
+    cudaMalloc(&d_in, in.size() * 4);
+    cudaMalloc(&d_out, out.size() * 4);
+    if (R) cudaMalloc(&d_ref, ref.size() * 4);
+    cudaMalloc(&d_pos, n * (n_sdims + R) * 4 + 16);
+    cudaMemcpyAsync(d_in, in.data(), in.size() * 4, cudaMemcpyHostToDevice, stream);
+    if (R) cudaMemcpyAsync(d_ref, ref.data(), ref.size() * 4, cudaMemcpyHostToDevice, stream);
+
+    int n_allocs = 0;
+    pl::OpContext context([&](size_t bytes) { void* p = nullptr; cudaMalloc(&p, bytes); n_allocs++; return p; },
+                          [](void* p) { cudaFree(p); });
+    pl::GpuDevice device{stream};
+    try {
+        pl::LatticeFilterOp op(reverse != 0, bilateral != 0, theta[0], theta[1], theta[2]);
+        op.Compute(device, &context, d_in, shape, d_ref, R, d_out);
+        cudaMemcpyAsync(out.data(), d_out, out.size() * 4, cudaMemcpyDeviceToHost, stream);
+        op.ComputePerItem(device, &context, d_in, shape, d_ref, R, d_pos, d_out);
+        cudaMemcpyAsync(out2.data(), d_out, out2.size() * 4, cudaMemcpyDeviceToHost, stream);
+        // an unsupported position dimension must surface as an exception, not abort the process
+        bool threw = false;
+        try {
+            pl::LatticeFilter<pl::GpuDevice, float>()(device, &context, d_out, d_in, d_pos, 16, 11, 4, false);
+        } catch (const pl::Error& e) {
+            threw = e.status == PL_UNSUPPORTED_DIMS;
+        }
+        if (!threw) die("unsupported dims did not throw");
+    } catch (const pl::Error& e) {
+        fprintf(stderr, "host_class_test: %s\n", e.what());
+        return 3;
+    }
+    if (cudaStreamSynchronize(stream) != cudaSuccess) die("stream failed");
+    f = fopen(argv[2], "wb");
+    fwrite(out.data(), 4, out.size(), f);
+    fwrite(out2.data(), 4, out2.size(), f);
+    fclose(f);
+    printf("ok allocs=%d\n", n_allocs);
+    return 0;
+}
