@@ -30,8 +30,9 @@ typedef enum pl_status {
 
 /* Accumulation order of the splat stage. */
 typedef enum pl_mode {
-    PL_MODE_ATOMIC = 0,        /* floating-point atomics; sums differ run to run in the last bits */
-    PL_MODE_DETERMINISTIC = 1  /* sorted, segmented reduction; bitwise reproducible */
+    PL_MODE_ATOMIC = 0,        /* floating-point reductions; sums differ run to run in the last bits */
+    PL_MODE_DETERMINISTIC = 1  /* sorted, segmented reduction with exact (64-bit fixed-point) sums:
+                                  bitwise reproducible; finite inputs, grid 2^-36 of max(|input|, 1) */
 } pl_mode;
 
 /* Counters read back from a workspace after a call (pl_lattice_stats). */

@@ -58,11 +58,12 @@ struct Header {   // first 256 bytes of the workspace
     u32 num_vertices;
     u32 status;
     u32 table_log2;
-    u32 pad[60];
+    u32 absmax_bits;   // deterministic mode: bit pattern of max |input| (non-negative floats order as integers)
+    u32 pad[59];
 };
 
 struct Layout {   // byte offsets into the workspace
-    size_t tile_info, rec, rec_w, list_keys, list_ref, vid, vowner, table, nbr, v0, v1, total;
+    size_t tile_info, rec, rec_w, list_keys, list_ref, vid, vowner, table, nbr, v0, v1, v64, total;
     u64 max_entries;   // capacity of entry- and vertex-indexed arrays
     u64 table_slots;   // allocated slots (power of two)
 };
@@ -370,7 +371,7 @@ __global__ void __launch_bounds__(256)
 link_vertices(Header* hdr, const u64* __restrict__ table,
               const Key<Cfg<PD>::KW>* __restrict__ list_keys, u32* __restrict__ list_ref,
               const u32* __restrict__ vid, const u32* __restrict__ vowner, int* __restrict__ nbr,
-              float* __restrict__ v0, u64 max_entries, int vd) {
+              float* __restrict__ v0, long long* __restrict__ v64, u64 max_entries, int vd) {
     constexpr int KW = Cfg<PD>::KW;
     if (hdr->status != 0) return;
     const u32 T = hdr->num_entries, M = hdr->num_vertices;
@@ -405,7 +406,11 @@ link_vertices(Header* hdr, const u64* __restrict__ table,
     }
 
     const u64 cells = (u64)M * padded_vd(vd);
-    for (u64 e = gtid; e < cells; e += gsz) v0[e] = 0.f;
+    if (v64) {
+        for (u64 e = gtid; e < cells; e += gsz) v64[e] = 0;
+    } else {
+        for (u64 e = gtid; e < cells; e += gsz) v0[e] = 0.f;
+    }
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -766,6 +771,119 @@ splat_tiles_generic(Geom g, const float* __restrict__ input, Header* hdr, const 
             red_add_v4(vrow + 4 * q, acc);
         }
     }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Deterministic splat (PL_MODE_DETERMINISTIC): the same sort-by-entry and segmented reduction, but
+// every product weight * value is rounded once onto a fixed-point grid and summed as a 64-bit
+// integer, in registers and in global memory.  Integer addition is associative, so the sums do not
+// depend on the order in which splats, windows or tiles arrive: results are bitwise reproducible.
+// Grid spacing: 2^-36 of the next power of two above max(|input|, 1), found by a first pass.
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+absmax_kernel(const float* __restrict__ input, u64 count, Header* hdr) {
+    u32 m = 0;
+    for (u64 i = (u64)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += (u64)gridDim.x * blockDim.x)
+        m = max(m, __float_as_uint(fabsf(input[i])));
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) m = max(m, __shfl_xor_sync(0xFFFFFFFFu, m, d));
+    if ((threadIdx.x & 31) == 0 && m) atomicMax(&hdr->absmax_bits, m);
+}
+
+// 2^(36 - e) with 2^e > max(|input|, 1); finite inputs only.
+__device__ __forceinline__ double fixed_scale(const Header* hdr) {
+    const u32 bits = max(hdr->absmax_bits, __float_as_uint(1.0f));
+    const int e = (int)((bits >> 23) & 0xFF) - 127 + 1;
+    return __longlong_as_double((long long)(1023 + 36 - e) << 52);
+}
+
+template <int PD>
+struct SplatDet {
+    static constexpr int TP = Cfg<PD>::TP, SPLATS = Cfg<PD>::SPLATS;
+    static size_t bytes(int vd) {
+        return ((sizeof(float) * (size_t)TP * (vd - 1) + 15) / 16) * 16 + sizeof(uint2) * SPLATS +
+               sizeof(int) * SPLATS + sizeof(int) * TP;
+    }
+};
+
+template <int PD>
+__global__ void __launch_bounds__(Cfg<PD>::TP)
+splat_tiles_det(Geom g, const float* __restrict__ input, Header* hdr, const int2* __restrict__ tile_info,
+                const u16* __restrict__ rec, const float* __restrict__ rec_w,
+                const u32* __restrict__ list_ref, long long* __restrict__ v64, int vd) {
+    constexpr int TP = Cfg<PD>::TP, SPLATS = Cfg<PD>::SPLATS, NW = TP / 32;
+    const int C = vd - 1, VP = padded_vd(vd);
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    float* in_s = reinterpret_cast<float*>(smem_raw);                                                // [TP][C]
+    uint2* sorted_s = reinterpret_cast<uint2*>(smem_raw + ((sizeof(float) * (size_t)TP * C + 15) / 16) * 16);
+    int* cur_s = reinterpret_cast<int*>(sorted_s + SPLATS);
+    int* prow_s = cur_s + SPLATS;
+    __shared__ int wsum_s[32];
+    if (call_failed(hdr)) return;
+    const int tid = threadIdx.x, tile = blockIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int2 info = tile_info[tile];
+    const int base = info.x, nloc = info.y;
+    int item, pix;
+    const bool valid = tile_point(g, tile, tid, item, pix);
+    prow_s[tid] = valid ? item * g.n + pix : -1;
+    for (int i = tid; i < nloc; i += TP) cur_s[i] = 0;
+    const int nvalid = __syncthreads_count(valid);
+    for (int k = tid; k < TP * C; k += TP) {
+        const int p = k / C, j = k - p * C;
+        const int row = prow_s[p];
+        if (row >= 0) cp_async4(in_s + k, input + (size_t)row * C + j);
+    }
+    float w[PD + 1];
+    int l[PD + 1];
+    const u16* rec_tile = rec + (size_t)tile * SPLATS;
+    const float* recw_tile = rec_w + (size_t)tile * SPLATS;
+#pragma unroll
+    for (int r = 0; r <= PD; r++) {
+        l[r] = valid ? rec_tile[r * TP + tid] : 0;
+        w[r] = valid ? recw_tile[r * TP + tid] : 0.f;
+    }
+    SplatCommon<PD>::sort_splats(valid, l, w, nloc, sorted_s, cur_s, nullptr, wsum_s);
+    cp_async_wait_all();
+    __syncthreads();
+
+    // warp-uniform walk over a contiguous chunk of the sorted splats, lanes over channels
+    const double scale = fixed_scale(hdr);
+    const int total = nvalid * (PD + 1);
+    const int chunk = (total + NW - 1) / NW;
+    const int beg = warp * chunk, end = min(total, beg + chunk);
+    if (beg >= end) return;
+    for (int j0 = 0; j0 < vd; j0 += 32) {
+        const int j = j0 + lane;
+        long long acc = 0;
+        int cur = (int)(sorted_s[beg].x >> 16);
+        for (int sidx = beg; sidx < end; sidx++) {
+            const uint2 pw = sorted_s[sidx];
+            const int e = (int)(pw.x >> 16);
+            if (e != cur) {
+                if (j < vd && acc)
+                    atomicAdd(reinterpret_cast<u64*>(v64 + (size_t)list_ref[base + cur] * VP + j), (u64)acc);
+                acc = 0;
+                cur = e;
+            }
+            if (j < vd) {
+                const float wt = __uint_as_float(pw.y);
+                const float prod = (j < C) ? PL_FMUL(wt, in_s[(pw.x & 0xFFFFu) * C + j]) : wt;
+                acc += __double2ll_rn(PL_DMUL((double)prod, scale));
+            }
+        }
+        if (j < vd && acc)
+            atomicAdd(reinterpret_cast<u64*>(v64 + (size_t)list_ref[base + cur] * VP + j), (u64)acc);
+    }
+}
+
+// fixed-point sums -> float rows
+__global__ void __launch_bounds__(256)
+convert_fixed(const Header* hdr, const long long* __restrict__ v64, float* __restrict__ v0, int vp) {
+    if (hdr->status != 0) return;
+    const double inv = 1.0 / fixed_scale(hdr);
+    const u64 cells = (u64)hdr->num_vertices * vp;
+    for (u64 i = (u64)blockIdx.x * blockDim.x + threadIdx.x; i < cells; i += (u64)gridDim.x * blockDim.x)
+        v0[i] = (float)PL_DMUL(__ll2double_rn(v64[i]), inv);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -1140,6 +1258,7 @@ static int make_layout(Layout& L, const Geom& g, int pd, int vd, int64_t max_ent
     L.nbr = off;       off += align_up(sizeof(int) * 2 * (size_t)(pd + 1) * E);
     L.v0 = off;        off += align_up(sizeof(float) * (size_t)padded_vd(vd) * E);
     L.v1 = off;        off += align_up(sizeof(float) * (size_t)padded_vd(vd) * E);
+    L.v64 = off;       off += align_up(sizeof(long long) * (size_t)padded_vd(vd) * E);   // deterministic mode sums
     L.total = off;
     return PL_OK;
 }
@@ -1225,7 +1344,7 @@ static int launch_slice(const Geom& g, float* output, const Header* hdr, const i
 
 template <int PD>
 static int run_filter(const Geom& g, float* output, const float* input, const float* positions,
-                      const float* reference, int vd, int reverse, void* workspace,
+                      const float* reference, int vd, int reverse, int mode, void* workspace,
                       const Layout& L, cudaStream_t st) {
     constexpr int KW = Cfg<PD>::KW, TP = Cfg<PD>::TP;
     unsigned char* ws = static_cast<unsigned char*>(workspace);
@@ -1241,6 +1360,7 @@ static int run_filter(const Geom& g, float* output, const float* input, const fl
     int* nbr = reinterpret_cast<int*>(ws + L.nbr);
     float* v0 = reinterpret_cast<float*>(ws + L.v0);
     float* v1 = reinterpret_cast<float*>(ws + L.v1);
+    long long* v64 = (mode == PL_MODE_DETERMINISTIC) ? reinterpret_cast<long long*>(ws + L.v64) : nullptr;
 
     cudaEvent_t* ev = g_stage_events;
     g_stage_events = nullptr;
@@ -1261,10 +1381,20 @@ static int run_filter(const Geom& g, float* output, const float* input, const fl
     if (ev) PL_CUDA(cudaEventRecord(ev[1], st));
     clear_table<<<wide, 256, 0, st>>>(hdr, table, (u32)table_log2);
     insert_entries<KW><<<wide, 256, 0, st>>>(hdr, table, list_keys, list_ref, vid, vowner);
-    link_vertices<PD><<<wide, 256, 0, st>>>(hdr, table, list_keys, list_ref, vid, vowner, nbr, v0,
+    link_vertices<PD><<<wide, 256, 0, st>>>(hdr, table, list_keys, list_ref, vid, vowner, nbr, v0, v64,
                                             L.max_entries, vd);
     if (ev) PL_CUDA(cudaEventRecord(ev[2], st));
-    int rc = PL_DISPATCH_VD(launch_splat, PD, vd, g, input, hdr, tile_info, rec, rec_w, list_ref, v0, vd, st);
+    int rc = PL_OK;
+    if (v64) {
+        const size_t smem = SplatDet<PD>::bytes(vd);
+        if (smem > 200 * 1024) return PL_UNSUPPORTED_DIMS;
+        PL_CUDA(cudaFuncSetAttribute(splat_tiles_det<PD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        absmax_kernel<<<wide, 256, 0, st>>>(input, (u64)g.batch * g.n * (vd - 1), hdr);
+        splat_tiles_det<PD><<<g.num_tiles, TP, smem, st>>>(g, input, hdr, tile_info, rec, rec_w, list_ref, v64, vd);
+        convert_fixed<<<wide, 256, 0, st>>>(hdr, v64, v0, padded_vd(vd));
+    } else {
+        rc = PL_DISPATCH_VD(launch_splat, PD, vd, g, input, hdr, tile_info, rec, rec_w, list_ref, v0, vd, st);
+    }
     if (rc != PL_OK) return rc;
     if (ev) PL_CUDA(cudaEventRecord(ev[3], st));
     float* src = v0;
@@ -1323,12 +1453,12 @@ static int run_export(const Geom& g, const float* positions, const float* refere
 static int filter_common(const Geom& g, float* output, const float* input, const float* positions,
                          const float* reference, int pd, int vd, int reverse, void* workspace,
                          size_t workspace_bytes, int64_t max_entries, int mode, cudaStream_t st) {
-    if (mode != PL_MODE_ATOMIC) return PL_INVALID_ARGUMENT;
+    if (mode != PL_MODE_ATOMIC && mode != PL_MODE_DETERMINISTIC) return PL_INVALID_ARGUMENT;
     Layout L;
     int rc = make_layout(L, g, pd, vd, max_entries);
     if (rc != PL_OK) return rc;
     if (workspace_bytes < L.total) return PL_WORKSPACE_TOO_SMALL;
-#define CALL(P) run_filter<P>(g, output, input, positions, reference, vd, reverse, workspace, L, st)
+#define CALL(P) run_filter<P>(g, output, input, positions, reference, vd, reverse, mode, workspace, L, st)
     PL_DISPATCH_PD(pd, CALL)
 #undef CALL
 }

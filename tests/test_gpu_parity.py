@@ -200,3 +200,35 @@ def test_compute_positions_matches_oracle(gpu, oracle):
     got = plb.compute_positions(None, [9, 4], 3.0, 1.0).cpu().numpy()
     want = oracle.compute_positions(None, [9, 4], 3.0, -1.0)
     assert np.array_equal(bits(got), bits(want))
+
+
+@pytest.mark.parametrize("config", [0, 2, 3])
+def test_deterministic_mode_is_bitwise_reproducible(config, gpu, oracle):
+    from permutohedral_lattice_b200 import workloads
+    from conftest import bits
+    w = workloads.small(config)
+    want = oracle.lattice_filter(w.input, w.reference, True, w.theta_alpha, w.theta_beta, 1.0, False)
+    runs = []
+    for _ in range(3):
+        out = gpu.run_op(w.input, w.reference, True, w.theta_alpha, w.theta_beta, 1.0, False,
+                         mode="deterministic")[0]
+        runs.append(out.cpu().numpy())
+    gpu.assert_outputs_close(runs[0], want, w.name + " deterministic")
+    assert np.array_equal(bits(runs[0]), bits(runs[1]))
+    assert np.array_equal(bits(runs[0]), bits(runs[2]))
+
+
+def test_deterministic_mode_positions_path_and_large_values(gpu, oracle):
+    import torch
+    import permutohedral_lattice_b200 as plb
+    from conftest import bits
+    rng = np.random.default_rng(12)
+    x = (rng.standard_normal((2, 3000, 5)) * 1e4).astype(np.float32)       # values far from 1
+    p = (rng.standard_normal((2, 3000, 4)) * 2).astype(np.float32)
+    xt, pt = torch.from_numpy(x).cuda(), torch.from_numpy(p).cuda()
+    a = plb.filter_positions(xt, pt, mode="deterministic")[0].cpu().numpy()
+    b = plb.filter_positions(xt, pt, mode="deterministic")[0].cpu().numpy()
+    assert np.array_equal(bits(a), bits(b))
+    want = np.stack([oracle.filter(x[i], p[i], structure=False).out for i in range(2)])
+    from conftest import rel_l2
+    assert rel_l2(a, want) <= 1e-5
