@@ -11,7 +11,8 @@ configuration 2, dense-CRF message passing, 16 x 512x512, 21 channels guided by 
 The line also carries: `roofline` for the slowest kernel (algorithmic bytes / CUDA-event time, against
 the measured HBM copy bandwidth in MEASURED_PEAKS.json), `roofline_call` for the whole step,
 `stages_ms` (per-call stage times from events recorded inside the timed steps), `e2e` (the same
-step through the public API from pinned host buffers, copies included) and `cpu_baseline` (the CPU
+step through the public host-buffer API, `HostPipeline.filter`, from pinned host memory: copies in
+both directions inside the timed region, overlapped with the filter chunk by chunk) and `cpu_baseline` (the CPU
 oracle on this box's host cores, bounded sample).  `--impl reference` times the reference CPU
 implementation alone.
 """
@@ -379,25 +380,27 @@ def main():
     hgrad = None if w.grad is None else torch.from_numpy(w.grad).pin_memory()
     hout_f = torch.empty_like(hx).pin_memory()
     hout_b = torch.empty_like(hx).pin_memory()
-    h2d = hx.numel() * 4 + (href.numel() * 4 if href is not None else 0) + \
+    # the op is stateless: the reference image travels with the forward and again with the backward call
+    h2d = hx.numel() * 4 + (href.numel() * 4 * calls_per_step if href is not None else 0) + \
         (hpos.numel() * 4 if hpos is not None else 0) + (hgrad.numel() * 4 if w.backward else 0)
     d2h = hx.numel() * 4 * calls_per_step
 
+    pipe = plb.HostPipeline(dev, n_streams=3, chunk_items=2)
+
     def e2e_step():
-        dx = hx.to(dev, non_blocking=True)
         if use_positions:
+            dx = hx.to(dev, non_blocking=True)
             dp = hpos.to(dev, non_blocking=True)
             o, _ = plb.filter_positions(dx.view(b, n, c), dp)
             hout_f.copy_(o.view_as(hout_f), non_blocking=True)
+            torch.cuda.current_stream().synchronize()
         else:
-            dr = None if href is None else href.to(dev, non_blocking=True)
-            o = plb.lattice_filter(dx, dr, w.bilateral, w.theta_alpha, w.theta_beta, w.theta_gamma)
-            hout_f.copy_(o, non_blocking=True)
+            pipe.filter(hx, href, w.bilateral, w.theta_alpha, w.theta_beta, w.theta_gamma, reverse=False,
+                        out_host=hout_f, wait=False)
             if w.backward:
-                dg = hgrad.to(dev, non_blocking=True)
-                g = plb.lattice_filter(dg, dr, w.bilateral, w.theta_alpha, w.theta_beta,
-                                       w.theta_gamma, reverse=True)
-                hout_b.copy_(g, non_blocking=True)
+                pipe.filter(hgrad, href, w.bilateral, w.theta_alpha, w.theta_beta, w.theta_gamma, reverse=True,
+                            out_host=hout_b, wait=False)
+            pipe.synchronize()     # both results are complete in host memory when the step ends
 
     e2e_step()
     barrier()

@@ -2,3 +2,4 @@
 (include/pl_lattice.h), with a host-side mirror of the reference operator."""
 from .lattice_filter import (compute_positions, export_lattice, filter_positions, lattice_filter,  # noqa: F401
                              lattice_filter_raw, lattice_stats, release_workspaces)
+from .host_pipeline import HostPipeline  # noqa: F401,E402

@@ -1,0 +1,65 @@
+"""The op on HOST buffers: host -> device copies, filter and device -> host copies of consecutive
+batch chunks overlap on a few CUDA streams (both copy engines and the SMs busy at once).  Each batch
+item is an independent lattice, so chunking the batch changes no result."""
+import torch
+
+from .lattice_filter import lattice_filter_raw
+
+
+class HostPipeline:
+    """Reusable pipeline for one device.  `filter` takes pinned host tensors [B, *S, C] / [B, *S, R]
+    and writes a pinned host tensor of the input's shape; it returns when the result is complete."""
+
+    def __init__(self, device=None, n_streams=3, chunk_items=2):
+        self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        self.streams = [torch.cuda.Stream(self.device) for _ in range(max(1, n_streams))]
+        self.chunk_items = max(1, chunk_items)
+        self._bufs = {}
+
+    def _buf(self, slot, name, shape):
+        key = (slot, name)
+        t = self._bufs.get(key)
+        if t is None or tuple(t.shape[1:]) != tuple(shape[1:]) or t.shape[0] < shape[0]:
+            t = torch.empty(shape, dtype=torch.float32, device=self.device)
+            self._bufs[key] = t
+        return t[:shape[0]]
+
+    def filter(self, input_host, reference_host, bilateral=True, theta_alpha=1.0, theta_beta=1.0,
+               theta_gamma=1.0, reverse=False, mode="atomic", out_host=None, wait=True):
+        """wait=False returns as soon as the work is queued; call `synchronize()` before reading
+        out_host.  Consecutive calls may be queued back to back: they share the streams, so their
+        copies and kernels keep overlapping across the call boundary."""
+        for t, name in ((input_host, "input_host"), (reference_host, "reference_host")):
+            if t is not None and (t.is_cuda or t.dtype != torch.float32 or not t.is_contiguous()):
+                raise ValueError("%s must be a contiguous float32 host tensor" % name)
+        if bilateral and reference_host is None:
+            raise ValueError("bilateral filtering needs reference_host")
+        if out_host is None:
+            out_host = torch.empty_like(input_host).pin_memory()
+        batch = input_host.shape[0]
+        main = torch.cuda.current_stream(self.device)
+        ready = torch.cuda.Event()
+        ready.record(main)
+        for i, lo in enumerate(range(0, batch, self.chunk_items)):
+            hi = min(batch, lo + self.chunk_items)
+            slot = i % len(self.streams)
+            stream = self.streams[slot]
+            stream.wait_event(ready)
+            with torch.cuda.stream(stream):
+                dx = self._buf(slot, "x", (hi - lo,) + tuple(input_host.shape[1:]))
+                dx.copy_(input_host[lo:hi], non_blocking=True)
+                dr = None
+                if bilateral:
+                    dr = self._buf(slot, "r", (hi - lo,) + tuple(reference_host.shape[1:]))
+                    dr.copy_(reference_host[lo:hi], non_blocking=True)
+                do = self._buf(slot, "o", (hi - lo,) + tuple(input_host.shape[1:]))
+                lattice_filter_raw(dx, dr, bilateral, theta_alpha, theta_beta, theta_gamma, reverse, mode,
+                                   out=do)
+                out_host[lo:hi].copy_(do, non_blocking=True)
+        if wait:
+            self.synchronize()
+        return out_host
+
+    def synchronize(self):
+        for stream in self.streams:
+            stream.synchronize()

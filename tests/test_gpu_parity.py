@@ -232,3 +232,16 @@ def test_deterministic_mode_positions_path_and_large_values(gpu, oracle):
     want = np.stack([oracle.filter(x[i], p[i], structure=False).out for i in range(2)])
     from conftest import rel_l2
     assert rel_l2(a, want) <= 1e-5
+
+
+def test_host_pipeline_matches_device_call(gpu, oracle):
+    import torch
+    import permutohedral_lattice_b200 as plb
+    rng = np.random.default_rng(31)
+    ref = torch.from_numpy(rng.random((5, 24, 40, 3), dtype=np.float32)).pin_memory()
+    inp = torch.from_numpy(rng.random((5, 24, 40, 6), dtype=np.float32)).pin_memory()
+    pipe = plb.HostPipeline(n_streams=3, chunk_items=2)
+    for reverse in (False, True):
+        got = pipe.filter(inp, ref, True, 5.0, 0.2, reverse=reverse).numpy()
+        want = oracle.lattice_filter(inp.numpy(), ref.numpy(), True, 5.0, 0.2, 1.0, reverse)
+        gpu.assert_outputs_close(got, want, "host pipeline")
