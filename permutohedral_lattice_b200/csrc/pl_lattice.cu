@@ -20,6 +20,7 @@
 // compared through the entry list, which a previous launch has completely written, so there are no
 // locks, no waiting and no duplicate vertices.  All device loops are bounded.
 #include <cuda_runtime.h>
+#include <cmath>
 #include <mutex>
 #include <stdint.h>
 #include <stdio.h>
@@ -49,6 +50,8 @@ struct Geom {
     int n_sdims, R;         // op path: spatial dims and reference channels (pd = n_sdims + R)
     int sdims[MAX_SDIMS];
     float spatial_std, feature_std;
+    float spatial_rcp, feature_rcp;   // correctly rounded reciprocals of the two (host-computed)
+    int rcp_div;            // 1: divide through the reciprocals (exact for these operands), 0: IEEE divide
     int from_positions;     // 1: features are read from a positions array
     float scale[MAX_PD];    // host-computed scale factors (double arithmetic rounded to float)
 };
@@ -108,7 +111,8 @@ __device__ __forceinline__ bool key_equal(const Key<KW>& a, const Key<KW>& b) {
     return eq;
 }
 
-// 16-bit field f of a key (fields 0..PD-1: coordinates, field PD: batch item).
+// 16-bit field f of a key.  Fields 0..PD-1: lattice coordinates biased by 0x8000 (so that adding small
+// offsets to a packed word never carries between fields); field PD: batch item.
 template <int KW>
 __device__ __forceinline__ void key_set(Key<KW>& k, int f, u16 v) {
     k.w[f >> 2] |= (u64)v << (16 * (f & 3));
@@ -118,42 +122,85 @@ __device__ __forceinline__ u16 key_get(const Key<KW>& k, int f) {
     return (u16)(k.w[f >> 2] >> (16 * (f & 3)));
 }
 
-// Point handled by thread `tid` of tile `tile`: item, point index inside the item, validity.
-__device__ __forceinline__ bool tile_point(const Geom& g, int tile, int tid, int& item, int& pix) {
+// 0x0001 in every coordinate field of key word j.
+template <int PD>
+__device__ __forceinline__ constexpr u64 coord_ones(int j) {
+    u64 m = 0;
+    for (int f = 4 * j; f < 4 * j + 4; f++)
+        if (f < PD) m |= 1ull << (16 * (f & 3));
+    return m;
+}
+
+// Cheap 32-bit hash for the per-tile shared-memory table (placement only).
+template <int KW>
+__device__ __forceinline__ u32 tile_hash(const Key<KW>& k) {
+    u32 h = 0;
+#pragma unroll
+    for (int j = 0; j < KW; j++) {
+        h = (h ^ (u32)k.w[j]) * 0x9E3779B1u;
+        h = (h ^ (u32)(k.w[j] >> 32)) * 0x85EBCA77u;
+    }
+    h ^= h >> 15;
+    h *= 0x2C1B3C6Du;
+    return h ^ (h >> 13);
+}
+
+// Point handled by thread `tid` of tile `tile`: item, point index inside the item, validity; the
+// long form also gives the point's position (outer index, row, column).
+__device__ __forceinline__ bool tile_point(const Geom& g, int tile, int tid, int& item, int& pix, int& o,
+                                           int& y, int& x) {
     item = tile / g.tiles_per_item;
     int t = tile - item * g.tiles_per_item;
     int per_plane = g.tiles_x * g.tiles_y;
-    int o = t / per_plane;
+    o = t / per_plane;
     t -= o * per_plane;
     int ty = t / g.tiles_x, tx = t - ty * g.tiles_x;
     int ly = tid / g.TX, lx = tid - ly * g.TX;
-    int y = ty * g.TY + ly, x = tx * g.TX + lx;
+    y = ty * g.TY + ly;
+    x = tx * g.TX + lx;
     pix = (o * g.H + y) * g.W + x;
     return (y < g.H) && (x < g.W);
+}
+__device__ __forceinline__ bool tile_point(const Geom& g, int tile, int tid, int& item, int& pix) {
+    int o, y, x;
+    return tile_point(g, tile, tid, item, pix, o, y, x);
 }
 
 // Feature vector of a point.  Op path: src/PermutohedralLatticeCPU.h:464-473 (coordinate of each
 // spatial dimension as float divided by spatial_std, reference channel divided by feature_std; IEEE
-// divisions, not reciprocal multiplies).  Positions path: a row of the positions array.
+// divisions, not reciprocal multiplies).  The last two spatial coordinates are the point's row and
+// column in its tile grid; only deeper dimensions need the reference's divide-and-modulo.
+// Positions path: a row of the positions array.
 template <int PD>
 __device__ __forceinline__ void load_features(const Geom& g, const float* __restrict__ positions,
-                                              const float* __restrict__ reference, int item, int pix,
-                                              float* f) {
+                                              const float* __restrict__ reference, int item, int pix, int o,
+                                              int y, int x, float* f) {
     if (g.from_positions) {
         const float* p = positions + ((size_t)item * g.n + pix) * PD;
 #pragma unroll
         for (int i = 0; i < PD; i++) f[i] = __ldg(p + i);
     } else {
-        int divisor = 1;
+        const float* ref = reference + ((size_t)item * g.n + pix) * g.R;
+        int rest = o;
 #pragma unroll
         for (int i = PD - 1; i >= 0; i--) {
-            if (i < g.n_sdims) {
-                int c = (pix / divisor) % g.sdims[i];
-                f[i] = PL_FDIV((float)c, g.spatial_std);
-                divisor *= g.sdims[i];
+            if (i >= g.n_sdims) {
+                const float a = __ldg(ref + (i - g.n_sdims));
+                f[i] = g.rcp_div ? div_by_rcp(a, g.feature_std, g.feature_rcp) : PL_FDIV(a, g.feature_std);
             } else {
-                f[i] = PL_FDIV(__ldg(reference + ((size_t)item * g.n + pix) * g.R + (i - g.n_sdims)),
-                               g.feature_std);
+                int c;
+                if (i == g.n_sdims - 1 && g.n_sdims >= 2) {
+                    c = x;
+                } else if (i == g.n_sdims - 2) {
+                    c = y;
+                } else if (g.n_sdims == 1) {
+                    c = x;
+                } else {
+                    c = rest % g.sdims[i];
+                    rest /= g.sdims[i];
+                }
+                const float a = small_int_to_float(c);
+                f[i] = g.rcp_div ? div_by_rcp(a, g.spatial_std, g.spatial_rcp) : PL_FDIV(a, g.spatial_std);
             }
         }
     }
@@ -190,54 +237,103 @@ build_tiles(Geom g, const float* __restrict__ positions, const float* __restrict
     for (int i = tid; i < LS; i += TP) hslots[i] = -1;
     if (tid == 0) nloc_s = 0;
 
-    int item, pix;
-    const bool valid = tile_point(g, tile, tid, item, pix);
-    float w[PD + 1];
-#pragma unroll
-    for (int r = 0; r <= PD; r++) w[r] = 0.f;
+    int item, pix, po, py, px;
+    const bool valid = tile_point(g, tile, tid, item, pix, po, py, px);
     if (valid) {
         float f[PD];
-        load_features<PD>(g, positions, reference, item, pix, f);
+        float w[PD + 1];
+        load_features<PD>(g, positions, reference, item, pix, po, py, px, f);
         Simplex<PD> s;
         find_simplex<PD>(f, g.scale, s);
         barycentric<PD>(s, w);
+        // the weights are final: store them now so the writes overlap the de-duplication below
+        float* recw_tile = rec_w + (size_t)tile * SPLATS;
 #pragma unroll
-        for (int r = 0; r <= PD; r++) {
-            Key<KW> k;
+        for (int r = 0; r <= PD; r++) recw_tile[r * TP + tid] = w[r];
+        // Remainder-r vertex: coordinate i = rem0_i + r - (PD+1) [rank_i > PD - r]
+        // (src/PermutohedralLatticeCPU.h:297-304).  In packed form: start from the remainder-0 key,
+        // then per step add one to every coordinate field and take PD+1 off the one coordinate whose
+        // rank is PD - r + 1.
+        Key<KW> k;
 #pragma unroll
-            for (int j = 0; j < KW; j++) k.w[j] = 0;
+        for (int j = 0; j < KW; j++) k.w[j] = 0;
 #pragma unroll
-            for (int i = 0; i < PD; i++) key_set<KW>(k, i, (u16)vertex_coord<PD>(s, i, r));
-            key_set<KW>(k, PD, (u16)item);
+        for (int i = 0; i < PD; i++) key_set<KW>(k, i, (u16)(s.rem0[i] + 0x8000));
+        key_set<KW>(k, PD, (u16)item);
+        keys_s[tid] = k;
+#pragma unroll
+        for (int r = 1; r <= PD; r++) {
+#pragma unroll
+            for (int i = 0; i < PD; i++)
+                if (s.rank[i] == PD - r + 1) k.w[i >> 2] -= (u64)(PD + 1) << (16 * (i & 3));
+#pragma unroll
+            for (int j = 0; j < KW; j++) k.w[j] += coord_ones<PD>(j);
             keys_s[r * TP + tid] = k;
         }
     }
     __syncthreads();
 
-    // de-duplicate: the first splat to claim a slot for a key represents it
+    // de-duplicate: the first splat to claim a slot for a key represents it.  The first probes of all
+    // PD+1 keys are issued together (independent shared-memory accesses); most keys resolve there,
+    // the rest walk on one at a time.
     int rep[PD + 1];
+    {
+        u32 slot[PD + 1];
+        int cand[PD + 1];
 #pragma unroll
-    for (int r = 0; r <= PD; r++) {
-        rep[r] = -1;
-        if (valid) {
-            const int me = r * TP + tid;
-            const Key<KW> k = keys_s[me];
-            u32 s = (u32)hash_key<KW>(k) & (LS - 1);
-            for (int it = 0; it < LS; it++) {
-                int o = hslots[s];
-                if (o < 0) {
-                    o = atomicCAS(&hslots[s], -1, me);
-                    if (o < 0) { rep[r] = me; break; }
+        for (int r = 0; r <= PD; r++) {
+            rep[r] = -1;
+            slot[r] = 0;
+            cand[r] = -1;
+            if (valid) {
+                slot[r] = tile_hash<KW>(keys_s[r * TP + tid]) & (LS - 1);
+                cand[r] = hslots[slot[r]];
+            }
+        }
+#pragma unroll
+        for (int r = 0; r <= PD; r++) {
+            if (valid && cand[r] < 0) {
+                cand[r] = atomicCAS(&hslots[slot[r]], -1, r * TP + tid);
+                if (cand[r] < 0) rep[r] = r * TP + tid;
+            }
+        }
+#pragma unroll
+        for (int r = 0; r <= PD; r++) {
+            if (valid && rep[r] < 0 && key_equal<KW>(keys_s[cand[r]], keys_s[r * TP + tid])) rep[r] = cand[r];
+        }
+#pragma unroll
+        for (int r = 0; r <= PD; r++) {
+            if (valid && rep[r] < 0) {
+                const int me = r * TP + tid;
+                const Key<KW> k = keys_s[me];
+                u32 s = (slot[r] + 1) & (LS - 1);
+                int found = -1;
+                for (int it = 0; it < LS; it++) {
+                    int o = hslots[s];
+                    if (o < 0) {
+                        o = atomicCAS(&hslots[s], -1, me);
+                        if (o < 0) { found = me; break; }
+                    }
+                    if (key_equal<KW>(keys_s[o], k)) { found = o; break; }
+                    s = (s + 1) & (LS - 1);
                 }
-                if (key_equal<KW>(keys_s[o], k)) { rep[r] = o; break; }
-                s = (s + 1) & (LS - 1);
+                rep[r] = found;
             }
         }
     }
     __syncthreads();
+    // number the tile's entries: one shared-memory atomic per warp and remainder, not per owner
 #pragma unroll
     for (int r = 0; r <= PD; r++) {
-        if (valid && rep[r] == r * TP + tid) lidx_s[r * TP + tid] = (u16)atomicAdd(&nloc_s, 1);
+        const bool own = valid && rep[r] == r * TP + tid;
+        const unsigned owners = __ballot_sync(0xFFFFFFFFu, own);
+        if (owners) {
+            const int lane = tid & 31, leader = __ffs(owners) - 1;
+            int first = 0;
+            if (lane == leader) first = atomicAdd(&nloc_s, __popc(owners));
+            first = __shfl_sync(0xFFFFFFFFu, first, leader);
+            if (own) lidx_s[r * TP + tid] = (u16)(first + __popc(owners & ((1u << lane) - 1u)));
+        }
     }
     __syncthreads();
     if (tid == 0) {
@@ -255,7 +351,6 @@ build_tiles(Geom g, const float* __restrict__ positions, const float* __restrict
     __syncthreads();
     const int base = base_s;
     u16* rec_tile = rec + (size_t)tile * SPLATS;
-    float* recw_tile = rec_w + (size_t)tile * SPLATS;
 #pragma unroll
     for (int r = 0; r <= PD; r++) {
         const int me = r * TP + tid;
@@ -265,7 +360,6 @@ build_tiles(Geom g, const float* __restrict__ positions, const float* __restrict
             if (rep[r] == me && base >= 0) list_keys[(size_t)base + l] = keys_s[me];
         }
         rec_tile[me] = l;
-        recw_tile[me] = w[r];
     }
 }
 
@@ -395,10 +489,8 @@ link_vertices(Header* hdr, const u64* __restrict__ table,
         for (int j = 0; j < KW; j++) nk.w[j] = 0;
 #pragma unroll
         for (int i = 0; i < PD; i++) {
-            int c = (int16_t)key_get<KW>(k, i);
-            int step = (i == a) ? -PD : 1;
-            c += d ? -step : step;
-            key_set<KW>(nk, i, (u16)(int16_t)c);
+            const int step = (i == a) ? -PD : 1;
+            key_set<KW>(nk, i, (u16)(key_get<KW>(k, i) + (d ? -step : step)));
         }
         key_set<KW>(nk, PD, key_get<KW>(k, PD));
         const int o = table_find<KW>(table, mask, list_keys, nk);
@@ -588,7 +680,7 @@ template <int PD, int VD>
 struct SplatFast {
     static constexpr int TP = Cfg<PD>::TP, SPLATS = Cfg<PD>::SPLATS, C = VD - 1;
     static constexpr size_t IN_BYTES = ((sizeof(float) * TP * C + 15) / 16) * 16;
-    static constexpr size_t BYTES = IN_BYTES + sizeof(uint2) * SPLATS + sizeof(int) * SPLATS + sizeof(int) * TP;
+    static constexpr size_t BYTES = IN_BYTES + sizeof(uint2) * SPLATS + 2 * sizeof(int) * SPLATS + sizeof(int) * TP;
 };
 
 // Adds a row held in registers to vertex row `vrow` (VP floats, 16-byte aligned).
@@ -612,6 +704,7 @@ splat_tiles_fast(Geom g, const float* __restrict__ input, Header* hdr, const int
     uint2* sorted_s = reinterpret_cast<uint2*>(smem_raw + SplatFast<PD, VD>::IN_BYTES);     // [SPLATS]
     int* cur_s = reinterpret_cast<int*>(sorted_s + SPLATS);                                 // [SPLATS]
     int* prow_s = cur_s + SPLATS;                                                           // [TP]
+    u32* vid_s = reinterpret_cast<u32*>(prow_s + TP);                                       // [SPLATS] entry -> vertex
     __shared__ int wsum_s[32];
     __shared__ __align__(8) u64 bar;
     if (call_failed(hdr)) return;
@@ -622,24 +715,21 @@ splat_tiles_fast(Geom g, const float* __restrict__ input, Header* hdr, const int
     int item, pix;
     const bool valid = tile_point(g, tile, tid, item, pix);
     prow_s[tid] = valid ? item * g.n + pix : -1;
-    for (int i = tid; i < nloc; i += TP) cur_s[i] = 0;
+    for (int i = tid; i < nloc; i += TP) {
+        cur_s[i] = 0;
+        vid_s[i] = list_ref[base + i];
+    }
     if (bulk_ok && tid == 0) mbar_init(&bar, 1);
     const int nvalid = __syncthreads_count(valid);
 
-    // stage the tile's input rows in shared memory, [point][channel] without padding
+    // stage the tile's input rows in shared memory, [point][channel] without padding: one bulk copy
+    // per tile row, each issued by its own thread; thread 0 announces the byte total (nvalid points)
     if (bulk_ok) {
-        if (tid == 0) {
-            unsigned total = 0;
-            for (int ly = 0; ly < g.TY; ly++) {
-                int first, count;
-                if (tile_row(g, tile, ly, first, count)) total += (unsigned)count * C * 4u;
-            }
-            mbar_expect_tx(&bar, total);
-            for (int ly = 0; ly < g.TY; ly++) {
-                int first, count;
-                if (tile_row(g, tile, ly, first, count))
-                    bulk_load(in_s + (size_t)ly * g.TX * C, input + (size_t)first * C, (unsigned)count * C * 4u, &bar);
-            }
+        if (tid == 0) mbar_expect_tx(&bar, (unsigned)nvalid * C * 4u);
+        if (tid < g.TY) {
+            int first, count;
+            if (tile_row(g, tile, tid, first, count))
+                bulk_load(in_s + (size_t)tid * g.TX * C, input + (size_t)first * C, (unsigned)count * C * 4u, &bar);
         }
     } else {
         for (int k = tid; k < TP * C; k += TP) {
@@ -685,7 +775,7 @@ splat_tiles_fast(Geom g, const float* __restrict__ input, Header* hdr, const int
             const uint2 pw = sorted_s[first + i];
             const int e = (int)(pw.x >> 16);
             if (e != cur) {
-                flush_row<VP>(v0 + (size_t)list_ref[base + cur] * VP, acc);
+                flush_row<VP>(v0 + (size_t)vid_s[cur] * VP, acc);
                 cur = e;
             }
             const float wt = __uint_as_float(pw.y);
@@ -695,7 +785,7 @@ splat_tiles_fast(Geom g, const float* __restrict__ input, Header* hdr, const int
             acc[C] = PL_FADD(acc[C], wt);
         }
     }
-    flush_row<VP>(v0 + (size_t)list_ref[base + cur] * VP, acc);
+    flush_row<VP>(v0 + (size_t)vid_s[cur] * VP, acc);
 }
 
 template <int PD>
@@ -1161,7 +1251,7 @@ __global__ void export_vertices(const Header* hdr, const Key<Cfg<PD>::KW>* __res
         const Key<KW> k = list_keys[vowner[v]];
         if (vertex_keys) {
 #pragma unroll
-            for (int i = 0; i < PD; i++) vertex_keys[v * PD + i] = (int16_t)key_get<KW>(k, i);
+            for (int i = 0; i < PD; i++) vertex_keys[v * PD + i] = (int16_t)(key_get<KW>(k, i) ^ 0x8000);
         }
         if (vertex_item) vertex_item[v] = (int32_t)key_get<KW>(k, PD);
     }
@@ -1211,6 +1301,12 @@ static int make_geom(Geom& g, int batch, int n, int pd, int n_sdims, const int* 
     g.R = R;
     g.spatial_std = spatial_std;
     g.feature_std = feature_std;
+    // Division through a correctly rounded reciprocal and one fused correction gives the IEEE quotient
+    // as long as nothing leaves the normal range; keep the plain divide for extreme sigmas.
+    auto tame = [](float v) { return std::isfinite(v) && std::fabs(v) >= 1e-18f && std::fabs(v) <= 1e18f; };
+    g.spatial_rcp = 1.0f / spatial_std;
+    g.feature_rcp = 1.0f / feature_std;
+    g.rcp_div = (tame(spatial_std) && tame(feature_std)) ? 1 : 0;
     const int tp = tp_of(pd);
     if (from_positions || n_sdims < 2) {
         g.W = n; g.H = 1; g.outer = 1;

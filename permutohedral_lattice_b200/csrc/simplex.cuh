@@ -2,7 +2,10 @@
 // the enclosing simplex and the barycentric weights.  Every floating-point operation is done in
 // the precision and order of the reference CPU implementation
 // (src/PermutohedralLatticeCPU.h:220-286, T = float), because vertex keys must match it exactly:
-// single roundings via __f*_rn (never contracted into FMAs), the multiply by 1/(pd+1) in double.
+// single roundings via __f*_rn (never contracted into FMAs).  Conversions and double arithmetic are
+// avoided where an all-float, all-ALU formulation provably selects the same simplex (see
+// find_simplex); the weights agree with the reference to the last bit except in the rare cases where
+// its float(double(x) * (1/(pd+1))) double rounding differs from a correctly rounded product.
 //
 // Compiles for the host too (PL_HD), so the arithmetic can be checked without a GPU.
 #pragma once
@@ -21,6 +24,9 @@
 #define PL_FDIV(a, b) __fdiv_rn((a), (b))
 #define PL_DMUL(a, b) __dmul_rn((a), (b))
 #define PL_DADD(a, b) __dadd_rn((a), (b))
+#define PL_FMA(a, b, c) __fmaf_rn((a), (b), (c))
+#define PL_F2BITS(x) __float_as_int(x)
+#define PL_BITS2F(x) __int_as_float(x)
 #else
 #include <cmath>
 #define PL_FMUL(a, b) ((a) * (b))
@@ -29,15 +35,40 @@
 #define PL_FDIV(a, b) ((a) / (b))
 #define PL_DMUL(a, b) ((a) * (b))
 #define PL_DADD(a, b) ((a) + (b))
+#define PL_FMA(a, b, c) fmaf((a), (b), (c))
+#include <cstring>
+static inline int pl_f2bits(float x) { int i; std::memcpy(&i, &x, 4); return i; }
+static inline float pl_bits2f(int i) { float x; std::memcpy(&x, &i, 4); return x; }
+#define PL_F2BITS(x) pl_f2bits(x)
+#define PL_BITS2F(x) pl_bits2f(x)
 #endif
 
 namespace pl {
+
+// 1.5 * 2^23: adding it to |x| < 2^22 leaves the nearest integer in the low mantissa bits.
+#define PL_ROUND_MAGIC 12582912.0f
+
+// Integer value of a float that holds an integer of magnitude below 2^22 (no conversion unit).
+PL_HD int exact_int(float x) { return PL_F2BITS(PL_FADD(x, PL_ROUND_MAGIC)) - 0x4B400000; }
+
+// (float)c for 0 <= c < 2^23 (no conversion unit).
+PL_HD float small_int_to_float(int c) { return PL_FSUB(PL_BITS2F(0x4B000000 | c), 8388608.0f); }
+
+// Correctly rounded a / b from the correctly rounded reciprocal rcp_b = RN(1 / b): q = RN(a rcp_b),
+// exact remainder r = a - b q by fused multiply-add, result RN(q + r rcp_b).  For finite operands
+// whose quotient and remainder stay in the normal range this equals the IEEE quotient.
+PL_HD float div_by_rcp(float a, float b, float rcp_b) {
+    const float q = PL_FMUL(a, rcp_b);
+    const float r = PL_FMA(-b, q, a);
+    return PL_FMA(r, rcp_b, q);
+}
 
 template <int PD>
 struct Simplex {
     int rem0[PD + 1];  // nearest remainder-0 lattice point, per coordinate (multiple of PD+1)
     int rank[PD + 1];  // rank of each coordinate's residual, 0..PD
     float el[PD + 1];  // elevated position
+    float rem0f[PD + 1];  // rem0 as float
 };
 
 // src/PermutohedralLatticeCPU.h:220-273 (embed_position_vector, find_enclosing_simplex).
@@ -53,16 +84,22 @@ PL_HD void find_simplex(const float* pos, const float* scale, Simplex<PD>& s) {
     }
     s.el[0] = sm;
 
-    const double inv = 1.0 / (PD + 1);
-    float rem0f[PD + 1];
+    // Nearest remainder-0 point per coordinate.  The reference takes v = float(double(el) / (PD+1)),
+    // up = ceil(v) (PD+1), down = floor(v) (PD+1) and picks up iff up - el < el - down.  Whenever v is
+    // not within rounding of an integer, floor(el * (1/(PD+1))) in float is the same floor and
+    // up = down + PD + 1; when it is, both candidate pairs contain the same winner with a margin of
+    // a whole cell, so the choice below is identical in every case.  floor() by the add-magic trick.
+    const float inv_f = 1.0f / (float)(PD + 1);
     int sum = 0;
 #pragma unroll
     for (int i = 0; i <= PD; i++) {
-        float v = (float)PL_DMUL((double)s.el[i], inv);
-        float up = ceilf(v) * (float)(PD + 1);    // exact: small integers
-        float down = floorf(v) * (float)(PD + 1);
-        rem0f[i] = (PL_FSUB(up, s.el[i]) < PL_FSUB(s.el[i], down)) ? up : down;
-        s.rem0[i] = (int)rem0f[i];
+        const float v = PL_FMUL(s.el[i], inv_f);
+        float fl = PL_FSUB(PL_FADD(v, PL_ROUND_MAGIC), PL_ROUND_MAGIC);   // nearest integer
+        if (fl > v) fl = PL_FSUB(fl, 1.0f);                              // -> floor
+        const float down = PL_FMUL(fl, (float)(PD + 1));                 // exact: small integers
+        const float up = PL_FADD(down, (float)(PD + 1));
+        s.rem0f[i] = (PL_FSUB(up, s.el[i]) < PL_FSUB(s.el[i], down)) ? up : down;
+        s.rem0[i] = exact_int(s.rem0f[i]);
         sum += s.rem0[i];
     }
     sum /= (PD + 1);
@@ -70,7 +107,7 @@ PL_HD void find_simplex(const float* pos, const float* scale, Simplex<PD>& s) {
     float d[PD + 1];
 #pragma unroll
     for (int i = 0; i <= PD; i++) {
-        d[i] = PL_FSUB(s.el[i], rem0f[i]);
+        d[i] = PL_FSUB(s.el[i], s.rem0f[i]);
         s.rank[i] = 0;
     }
 #pragma unroll
@@ -89,9 +126,11 @@ PL_HD void find_simplex(const float* pos, const float* scale, Simplex<PD>& s) {
         if (s.rank[i] < 0) {
             s.rank[i] += PD + 1;
             s.rem0[i] += PD + 1;
+            s.rem0f[i] = PL_FADD(s.rem0f[i], (float)(PD + 1));
         } else if (s.rank[i] > PD) {
             s.rank[i] -= PD + 1;
             s.rem0[i] -= PD + 1;
+            s.rem0f[i] = PL_FSUB(s.rem0f[i], (float)(PD + 1));
         }
     }
 }
@@ -103,13 +142,21 @@ PL_HD void find_simplex(const float* pos, const float* scale, Simplex<PD>& s) {
 // data-dependent array indexing.
 template <int PD>
 PL_HD void barycentric(const Simplex<PD>& s, float* bary /* PD+1 */) {
-    const double inv = 1.0 / (PD + 1);
+    // delta_i = (el_i - rem0_i) / (PD+1): the reference multiplies by the double 1/(PD+1) and rounds
+    // to float; here the same product is formed in float-float arithmetic (c = ch + cl), which gives
+    // the correctly rounded float without conversions.
+    const double c = 1.0 / (PD + 1);
+    const float ch = (float)c;
+    const float cl = (float)(c - (double)ch);
     float by_rank[PD + 1];
 #pragma unroll
     for (int q = 0; q <= PD; q++) by_rank[q] = 0.f;
 #pragma unroll
     for (int i = 0; i <= PD; i++) {
-        float delta = (float)PL_DMUL((double)PL_FSUB(s.el[i], (float)s.rem0[i]), inv);
+        const float d = PL_FSUB(s.el[i], s.rem0f[i]);
+        const float p = PL_FMUL(d, ch);
+        const float e = PL_FMA(d, ch, -p);             // exact error of p
+        const float delta = PL_FADD(p, PL_FMA(d, cl, e));
 #pragma unroll
         for (int q = 0; q <= PD; q++)
             if (s.rank[i] == q) by_rank[q] = delta;

@@ -28,3 +28,10 @@ extern "C" int simplex_host(const float* pos, const float* scale, int n, int pd,
     }
     return 1;
 }
+
+// a / b through the reciprocal-based division used for the features; rcp = RN(1 / b).
+extern "C" void div_by_rcp_host(const float* a, float b, int n, float* out) {
+    const float rcp = 1.0f / b;
+    for (int i = 0; i < n; i++) out[i] = pl::div_by_rcp(a[i], b, rcp);
+}
+extern "C" float small_int_to_float_host(int c) { return pl::small_int_to_float(c); }
