@@ -788,6 +788,122 @@ splat_tiles_fast(Geom g, const float* __restrict__ input, Header* hdr, const int
     flush_row<VP>(v0 + (size_t)vid_s[cur] * VP, acc);
 }
 
+template <int PD, int VD>
+__global__ void __launch_bounds__(Cfg<PD>::TP)
+splat_tiles_pair(Geom g, const float* __restrict__ input, Header* hdr, const int2* __restrict__ tile_info,
+                 const u16* __restrict__ rec, const float* __restrict__ rec_w,
+                 const u32* __restrict__ list_ref, float* __restrict__ v0, int bulk_ok) {
+    constexpr int TP = Cfg<PD>::TP, SPLATS = Cfg<PD>::SPLATS, C = VD - 1, VP = (VD + 3) & ~3;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    float* in_s = reinterpret_cast<float*>(smem_raw);                                       // [TP][C]
+    uint2* sorted_s = reinterpret_cast<uint2*>(smem_raw + SplatFast<PD, VD>::IN_BYTES);     // [SPLATS]
+    int* cur_s = reinterpret_cast<int*>(sorted_s + SPLATS);                                 // [SPLATS]
+    int* prow_s = cur_s + SPLATS;                                                           // [TP]
+    u32* vid_s = reinterpret_cast<u32*>(prow_s + TP);                                       // [SPLATS] entry -> vertex
+    __shared__ int wsum_s[32];
+    __shared__ __align__(8) u64 bar;
+    if (call_failed(hdr)) return;
+    const int tid = threadIdx.x, tile = blockIdx.x;
+    const int2 info = tile_info[tile];
+    const int base = info.x, nloc = info.y;
+
+    int item, pix;
+    const bool valid = tile_point(g, tile, tid, item, pix);
+    prow_s[tid] = valid ? item * g.n + pix : -1;
+    for (int i = tid; i < nloc; i += TP) {
+        cur_s[i] = 0;
+        vid_s[i] = list_ref[base + i];
+    }
+    if (bulk_ok && tid == 0) mbar_init(&bar, 1);
+    const int nvalid = __syncthreads_count(valid);
+
+    // stage the tile's input rows in shared memory, [point][channel] without padding: one bulk copy
+    // per tile row, each issued by its own thread; thread 0 announces the byte total (nvalid points)
+    if (bulk_ok) {
+        if (tid == 0) mbar_expect_tx(&bar, (unsigned)nvalid * C * 4u);
+        if (tid < g.TY) {
+            int first, count;
+            if (tile_row(g, tile, tid, first, count))
+                bulk_load(in_s + (size_t)tid * g.TX * C, input + (size_t)first * C, (unsigned)count * C * 4u, &bar);
+        }
+    } else {
+        for (int k = tid; k < TP * C; k += TP) {
+            const int p = k / C, j = k - p * C;
+            const int row = prow_s[p];
+            if (row >= 0) cp_async4(in_s + k, input + (size_t)row * C + j);
+        }
+    }
+
+    float w[PD + 1];
+    int l[PD + 1];
+    const u16* rec_tile = rec + (size_t)tile * SPLATS;
+    const float* recw_tile = rec_w + (size_t)tile * SPLATS;
+#pragma unroll
+    for (int r = 0; r <= PD; r++) {
+        l[r] = valid ? rec_tile[r * TP + tid] : 0;
+        w[r] = valid ? recw_tile[r * TP + tid] : 0.f;
+    }
+    SplatCommon<PD>::sort_splats(valid, l, w, nloc, sorted_s, cur_s, nullptr, wsum_s);
+
+    if (bulk_ok) {
+        if (!mbar_wait(&bar, 0)) {
+            atomicOr(&hdr->status, 1u << PL_INTERNAL_ERROR);
+            return;
+        }
+    } else {
+        cp_async_wait_all();
+        __syncthreads();
+    }
+
+    // Two lanes share a window of 2(PD+1) consecutive sorted splats: the even lane sums the even
+    // 16-byte quads of the row, the odd lane the odd quads.  Whenever the entry changes, and at the
+    // end of the window, the partial row leaves as vector reductions; the two lanes' quads of one
+    // step are neighbours in memory, so each pair of reductions is one 32-byte request.
+    constexpr int QPR = VP / 4, NQ = (QPR + 1) / 2, WL = 2 * (PD + 1);
+    const int total = nvalid * (PD + 1);
+    const int half = tid & 1, first = (tid >> 1) * WL;
+    if (first >= total) return;
+    float acc[NQ * 4];
+#pragma unroll
+    for (int j = 0; j < NQ * 4; j++) acc[j] = 0.f;
+    int cur = (int)(sorted_s[first].x >> 16);
+    auto flush = [&](int entry) {
+        float* vrow = v0 + (size_t)vid_s[entry] * VP + 4 * half;
+#pragma unroll
+        for (int k = 0; k < NQ; k++) {
+            if (2 * k + half < QPR)
+                red_add_v4(vrow + 8 * k, make_float4(acc[4 * k], acc[4 * k + 1], acc[4 * k + 2], acc[4 * k + 3]));
+        }
+#pragma unroll
+        for (int j = 0; j < NQ * 4; j++) acc[j] = 0.f;
+    };
+#pragma unroll
+    for (int i = 0; i < WL; i++) {
+        if (first + i < total) {
+            const uint2 pw = sorted_s[first + i];
+            const int e = (int)(pw.x >> 16);
+            if (e != cur) {
+                flush(cur);
+                cur = e;
+            }
+            const float wt = __uint_as_float(pw.y);
+            const float* x = in_s + (pw.x & 0xFFFFu) * C + 4 * half;
+#pragma unroll
+            for (int k = 0; k < NQ; k++) {
+#pragma unroll
+                for (int c = 0; c < 4; c++) {
+                    const int j = 8 * k + 4 * half + c;      // channel of this lane's slot
+                    if (j < C)
+                        acc[4 * k + c] = PL_FADD(acc[4 * k + c], PL_FMUL(wt, x[8 * k + c]));
+                    else if (j == C)
+                        acc[4 * k + c] = PL_FADD(acc[4 * k + c], wt);
+                }
+            }
+        }
+    }
+    flush(cur);
+}
+
 template <int PD>
 struct SplatGeneric {
     static constexpr int TP = Cfg<PD>::TP, SPLATS = Cfg<PD>::SPLATS;
@@ -1394,7 +1510,12 @@ static bool bulk_rows_ok(const Geom& g, const void* ptr, int channels) {
 template <int PD, int VD>
 static int launch_splat(const Geom& g, const float* input, Header* hdr, const int2* tile_info, const u16* rec,
                         const float* rec_w, const u32* list_ref, float* v0, int vd, cudaStream_t st) {
-    if constexpr (VD > 0) {
+    if constexpr (VD > 8) {          // wide rows: two lanes per window, paired 32-byte reductions
+        const size_t smem = SplatFast<PD, VD>::BYTES;
+        PL_CUDA(cudaFuncSetAttribute(splat_tiles_pair<PD, VD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        splat_tiles_pair<PD, VD><<<g.num_tiles, Cfg<PD>::TP, smem, st>>>(
+            g, input, hdr, tile_info, rec, rec_w, list_ref, v0, bulk_rows_ok(g, input, VD - 1) ? 1 : 0);
+    } else if constexpr (VD > 0) {
         const size_t smem = SplatFast<PD, VD>::BYTES;
         PL_CUDA(cudaFuncSetAttribute(splat_tiles_fast<PD, VD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         splat_tiles_fast<PD, VD><<<g.num_tiles, Cfg<PD>::TP, smem, st>>>(
