@@ -1140,7 +1140,12 @@ struct SliceFast {
     static constexpr int TP = Cfg<PD>::TP, C = VD - 1, VP = (VD + 3) & ~3;
     static constexpr int RS = VP + 4;   // words between cached rows: 16-byte aligned, spreads banks
     static constexpr size_t OUT_BYTES = ((sizeof(float) * TP * C + 15) / 16) * 16;
-    static size_t bytes(int rows_cap) { return OUT_BYTES + sizeof(float) * (size_t)rows_cap * RS + sizeof(int) * TP; }
+    // the output block reuses the space of the cached rows once every thread has read them
+    __host__ __device__ static size_t region(int rows_cap) {
+        const size_t rows = ((sizeof(float) * (size_t)rows_cap * RS + 15) / 16) * 16;
+        return rows > OUT_BYTES ? rows : OUT_BYTES;
+    }
+    static size_t bytes(int rows_cap) { return region(rows_cap) + sizeof(int) * TP; }
 };
 
 template <int PD, int VD>
@@ -1151,9 +1156,9 @@ slice_tiles_fast(Geom g, float* __restrict__ output, const Header* hdr, const in
     constexpr int TP = Cfg<PD>::TP, SPLATS = Cfg<PD>::SPLATS, C = VD - 1, VP = (VD + 3) & ~3, QPR = VP / 4;
     constexpr int RS = SliceFast<PD, VD>::RS;
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    float* out_s = reinterpret_cast<float*>(smem_raw);                                          // [TP][C]
-    float* rows_s = reinterpret_cast<float*>(smem_raw + SliceFast<PD, VD>::OUT_BYTES);          // [rows_cap][RS]
-    int* prow_s = reinterpret_cast<int*>(rows_s + (size_t)rows_cap * RS);                       // [TP]
+    float* rows_s = reinterpret_cast<float*>(smem_raw);                                         // [rows_cap][RS]
+    float* out_s = reinterpret_cast<float*>(smem_raw);                                          // [TP][C], later
+    int* prow_s = reinterpret_cast<int*>(smem_raw + SliceFast<PD, VD>::region(rows_cap));       // [TP]
     if (call_failed(hdr)) return;
     const int tid = threadIdx.x, tile = blockIdx.x;
     const int2 info = tile_info[tile];
@@ -1178,10 +1183,10 @@ slice_tiles_fast(Geom g, float* __restrict__ output, const Header* hdr, const in
     }
     cp_async_wait_all();
     __syncthreads();
-    if (valid) {
-        float acc[VP];
+    float acc[VP];
 #pragma unroll
-        for (int j = 0; j < VP; j++) acc[j] = 0.f;
+    for (int j = 0; j < VP; j++) acc[j] = 0.f;
+    if (valid) {
 #pragma unroll
         for (int r = 0; r <= PD; r++) {
             const float4* row = (l[r] < nrows) ? reinterpret_cast<const float4*>(rows_s + l[r] * RS)
@@ -1195,6 +1200,9 @@ slice_tiles_fast(Geom g, float* __restrict__ output, const Header* hdr, const in
                 acc[4 * q + 3] = PL_FADD(acc[4 * q + 3], PL_FMUL(w[r], x.w));
             }
         }
+    }
+    __syncthreads();   // every cached row has been read: the output block may overwrite them
+    if (valid) {
         const float inv = (float)(1.0 / (double)acc[C]);
 #pragma unroll
         for (int j = 0; j < C; j++) out_s[tid * C + j] = PL_FMUL(acc[j], inv);
@@ -1534,7 +1542,7 @@ template <int PD, int VD>
 static int launch_slice(const Geom& g, float* output, const Header* hdr, const int2* tile_info, const u16* rec,
                         const float* rec_w, const u32* list_ref, const float* vsrc, int vd, cudaStream_t st) {
     if constexpr (VD > 0) {
-        int rows_cap = (48 * 1024) / (SliceFast<PD, VD>::RS * 4);
+        int rows_cap = (40 * 1024) / (SliceFast<PD, VD>::RS * 4);
         if (rows_cap > Cfg<PD>::SPLATS) rows_cap = Cfg<PD>::SPLATS;
         const size_t smem = SliceFast<PD, VD>::bytes(rows_cap);
         PL_CUDA(cudaFuncSetAttribute(slice_tiles_fast<PD, VD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
