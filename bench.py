@@ -418,7 +418,7 @@ def main():
         e2e_ms = float(t.item())
     e2e_value = total_pixels / (e2e_ms / args.e2e_steps * 1e-3) / 1e6
 
-    kernels_per_call = 6 + (w.pd + 1)   # build, clear, insert, link, splat, slice + blur passes
+    kernels_per_call = 7 + (w.pd + 1)   # build, clear, insert, link x2, splat, slice + blur passes
     line = {
         "metric": metric_name(args.config, w), "value": value, "unit": "Mpixels/s", "n_gpus": world,
         "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step,

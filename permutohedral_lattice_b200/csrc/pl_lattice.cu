@@ -8,8 +8,9 @@
 //                   splat records the 16-bit index of its entry inside the tile.
 //   clear_table     sizes the global hash table from the entry count (on the device) and clears it.
 //   insert_entries  one CAS per entry into the table; the first entry of a key owns a new vertex.
-//   link_vertices   entry -> vertex index; the +-1 neighbours of every vertex along each of the
-//                   pd+1 axes; zeroes the value rows.
+//   link_vertices   entry -> vertex index; presets the neighbour table, zeroes the value rows.
+//   link_neighbours the +-1 neighbours of every vertex along each of the pd+1 axes: one table lookup
+//                   per vertex and axis fills both directions.
 //   splat_tiles     one CTA per tile: barycentric weights recomputed, values accumulated per entry
 //                   in shared memory, one row of global atomics per entry.
 //   blur_axis       pd+1 launches: V'[v] = (V[n1] + 2 V[v] + V[n2]) / 4, Jacobi, ping-pong buffers.
@@ -458,50 +459,58 @@ insert_entries(Header* hdr, u64* __restrict__ table, const Key<KW>* __restrict__
 }
 
 // ---------------------------------------------------------------------------------------------
-// link_vertices: entry -> vertex, neighbour table, zeroed value rows
+// link_vertices: entry -> vertex, neighbour table preset to "missing", zeroed value rows.
+// link_neighbours: the +-1 neighbours of every vertex along each of the PD+1 lattice axes.
 // ---------------------------------------------------------------------------------------------
-template <int PD>
 __global__ void __launch_bounds__(256)
-link_vertices(Header* hdr, const u64* __restrict__ table,
-              const Key<Cfg<PD>::KW>* __restrict__ list_keys, u32* __restrict__ list_ref,
-              const u32* __restrict__ vid, const u32* __restrict__ vowner, int* __restrict__ nbr,
-              float* __restrict__ v0, long long* __restrict__ v64, u64 max_entries, int vd) {
-    constexpr int KW = Cfg<PD>::KW;
+link_vertices(Header* hdr, u32* __restrict__ list_ref, const u32* __restrict__ vid, int* __restrict__ nbr,
+              float* __restrict__ v0, long long* __restrict__ v64, u64 max_entries, int pd, int vd) {
     if (hdr->status != 0) return;
     const u32 T = hdr->num_entries, M = hdr->num_vertices;
-    const u64 mask = (1ull << hdr->table_log2) - 1;
     const u64 gtid = (u64)blockIdx.x * blockDim.x + threadIdx.x;
     const u64 gsz = (u64)gridDim.x * blockDim.x;
-
     for (u64 t = gtid; t < T; t += gsz) list_ref[t] = vid[list_ref[t]];
-
-    // neighbours: item (v, axis a, direction d).  Along axis a < PD the neighbour key is every
-    // stored coordinate +1 (d = 0) or -1 (d = 1), except coordinate a which moves by -PD / +PD;
-    // along axis PD no stored coordinate is special (src/PermutohedralLatticeCPU.h:381-388).
-    const u64 items = (u64)M * (PD + 1) * 2;
-    for (u64 e = gtid; e < items; e += gsz) {
-        const u32 v = (u32)(e / (2 * (PD + 1)));
-        const int rem = (int)(e - (u64)v * (2 * (PD + 1)));
-        const int a = rem >> 1, d = rem & 1;
-        const Key<KW> k = list_keys[vowner[v]];
-        Key<KW> nk;
-#pragma unroll
-        for (int j = 0; j < KW; j++) nk.w[j] = 0;
-#pragma unroll
-        for (int i = 0; i < PD; i++) {
-            const int step = (i == a) ? -PD : 1;
-            key_set<KW>(nk, i, (u16)(key_get<KW>(k, i) + (d ? -step : step)));
-        }
-        key_set<KW>(nk, PD, key_get<KW>(k, PD));
-        const int o = table_find<KW>(table, mask, list_keys, nk);
-        nbr[((u64)a * max_entries + v) * 2 + d] = (o < 0) ? -1 : (int)vid[o];
-    }
-
+    int2* nb = reinterpret_cast<int2*>(nbr);
+    for (int a = 0; a <= pd; a++)
+        for (u64 v = gtid; v < M; v += gsz) nb[(u64)a * max_entries + v] = make_int2(-1, -1);
     const u64 cells = (u64)M * padded_vd(vd);
     if (v64) {
         for (u64 e = gtid; e < cells; e += gsz) v64[e] = 0;
     } else {
         for (u64 e = gtid; e < cells; e += gsz) v0[e] = 0.f;
+    }
+}
+
+// One table lookup per (vertex v, axis a): the neighbour u whose key is v's key with every stored
+// coordinate +1, except coordinate a which moves by -PD (along axis PD no stored coordinate is
+// special; src/PermutohedralLatticeCPU.h:381-388).  Then u is v's "+" neighbour and v is u's "-"
+// neighbour, so the second lookup of the reference is not needed.
+template <int PD>
+__global__ void __launch_bounds__(256)
+link_neighbours(const Header* hdr, const u64* __restrict__ table,
+                const Key<Cfg<PD>::KW>* __restrict__ list_keys, const u32* __restrict__ vid,
+                const u32* __restrict__ vowner, int* __restrict__ nbr, u64 max_entries) {
+    constexpr int KW = Cfg<PD>::KW;
+    if (hdr->status != 0) return;
+    const u32 M = hdr->num_vertices;
+    const u64 mask = (1ull << hdr->table_log2) - 1;
+    const u64 items = (u64)M * (PD + 1);
+    for (u64 e = (u64)blockIdx.x * blockDim.x + threadIdx.x; e < items; e += (u64)gridDim.x * blockDim.x) {
+        const u32 v = (u32)(e / (PD + 1));
+        const int a = (int)(e - (u64)v * (PD + 1));
+        const Key<KW> k = list_keys[vowner[v]];
+        Key<KW> nk;
+#pragma unroll
+        for (int j = 0; j < KW; j++) nk.w[j] = 0;
+#pragma unroll
+        for (int i = 0; i < PD; i++) key_set<KW>(nk, i, (u16)(key_get<KW>(k, i) + ((i == a) ? -PD : 1)));
+        key_set<KW>(nk, PD, key_get<KW>(k, PD));
+        const int o = table_find<KW>(table, mask, list_keys, nk);
+        if (o >= 0) {
+            const u32 u = vid[o];
+            nbr[((u64)a * max_entries + v) * 2] = (int)u;
+            nbr[((u64)a * max_entries + u) * 2 + 1] = (int)v;
+        }
     }
 }
 
@@ -1606,8 +1615,8 @@ static int run_filter(const Geom& g, float* output, const float* input, const fl
     if (ev) PL_CUDA(cudaEventRecord(ev[1], st));
     clear_table<<<wide, 256, 0, st>>>(hdr, table, (u32)table_log2);
     insert_entries<KW><<<wide, 256, 0, st>>>(hdr, table, list_keys, list_ref, vid, vowner);
-    link_vertices<PD><<<wide, 256, 0, st>>>(hdr, table, list_keys, list_ref, vid, vowner, nbr, v0, v64,
-                                            L.max_entries, vd);
+    link_vertices<<<wide, 256, 0, st>>>(hdr, list_ref, vid, nbr, v0, v64, L.max_entries, PD, vd);
+    link_neighbours<PD><<<wide, 256, 0, st>>>(hdr, table, list_keys, vid, vowner, nbr, L.max_entries);
     if (ev) PL_CUDA(cudaEventRecord(ev[2], st));
     int rc = PL_OK;
     if (v64) {
