@@ -82,11 +82,11 @@ struct Cfg {
     static constexpr int KW = (PD + 1 + 3) / 4;          // 16-bit fields: PD coordinates + item
     static constexpr int TP = (PD <= 8) ? 256 : 128;     // points per tile = threads per CTA
     static constexpr int SPLATS = TP * (PD + 1);
-    static constexpr int LS = (2 * SPLATS <= 1024)   ? 1024
-                              : (2 * SPLATS <= 2048) ? 2048
-                              : (2 * SPLATS <= 4096) ? 4096
-                              : (2 * SPLATS <= 8192) ? 8192
-                                                     : 16384;   // shared hash slots (>= 2 * SPLATS)
+    static constexpr int LS = (5 * SPLATS <= 4 * 1024)   ? 1024
+                              : (5 * SPLATS <= 4 * 2048) ? 2048
+                              : (5 * SPLATS <= 4 * 4096) ? 4096
+                              : (5 * SPLATS <= 4 * 8192) ? 8192
+                                                         : 16384;   // shared hash slots (>= 1.25 * SPLATS)
     static constexpr size_t BUILD_SMEM = sizeof(Key<KW>) * SPLATS + sizeof(int) * LS + sizeof(u16) * SPLATS;
 };
 
@@ -629,6 +629,17 @@ struct SplatCommon {
     // Counting sort of the tile's splats by entry.  On return (after the trailing barrier)
     // sorted_s[off_s[e] .. cur_s[e]) are entry e's splats as (point | entry << 16, weight bits);
     // cur_s must be zero for e < nloc on entry.  off_s may be nullptr when run starts are not needed.
+    // WL > 0 stores sorted position pos at slot(pos): the list is cut into windows of WL splats and
+    // laid out step-major, so that threads walking neighbouring windows in step read neighbouring words.
+    template <int WL>
+    __device__ static __forceinline__ int slot(int pos) {
+        if constexpr (WL == 0)
+            return pos;
+        else
+            return (pos % WL) * (SPLATS / WL) + pos / WL;
+    }
+
+    template <int WL>
     __device__ static __forceinline__ void sort_splats(bool valid, const int* l, const float* w, int nloc,
                                                        uint2* sorted_s, int* cur_s, int* off_s, int* wsum_s) {
         const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -678,7 +689,7 @@ struct SplatCommon {
 #pragma unroll
             for (int r = 0; r <= PD; r++) {
                 const int pos = atomicAdd(&cur_s[l[r]], 1);
-                sorted_s[pos] = make_uint2((unsigned)tid | ((unsigned)l[r] << 16), __float_as_uint(w[r]));
+                sorted_s[slot<WL>(pos)] = make_uint2((unsigned)tid | ((unsigned)l[r] << 16), __float_as_uint(w[r]));
             }
         }
         __syncthreads();
@@ -757,7 +768,7 @@ splat_tiles_fast(Geom g, const float* __restrict__ input, Header* hdr, const int
         l[r] = valid ? rec_tile[r * TP + tid] : 0;
         w[r] = valid ? recw_tile[r * TP + tid] : 0.f;
     }
-    SplatCommon<PD>::sort_splats(valid, l, w, nloc, sorted_s, cur_s, nullptr, wsum_s);
+    SplatCommon<PD>::template sort_splats<PD + 1>(valid, l, w, nloc, sorted_s, cur_s, nullptr, wsum_s);
 
     if (bulk_ok) {
         if (!mbar_wait(&bar, 0)) {
@@ -777,11 +788,12 @@ splat_tiles_fast(Geom g, const float* __restrict__ input, Header* hdr, const int
     float acc[VP];
 #pragma unroll
     for (int j = 0; j < VP; j++) acc[j] = 0.f;
-    int cur = (int)(sorted_s[first].x >> 16);
+    using SC = SplatCommon<PD>;
+    int cur = (int)(sorted_s[SC::template slot<PD + 1>(first)].x >> 16);
 #pragma unroll
     for (int i = 0; i <= PD; i++) {
         if (first + i < total) {
-            const uint2 pw = sorted_s[first + i];
+            const uint2 pw = sorted_s[SC::template slot<PD + 1>(first + i)];
             const int e = (int)(pw.x >> 16);
             if (e != cur) {
                 flush_row<VP>(v0 + (size_t)vid_s[cur] * VP, acc);
@@ -808,7 +820,6 @@ splat_tiles_pair(Geom g, const float* __restrict__ input, Header* hdr, const int
     uint2* sorted_s = reinterpret_cast<uint2*>(smem_raw + SplatFast<PD, VD>::IN_BYTES);     // [SPLATS]
     int* cur_s = reinterpret_cast<int*>(sorted_s + SPLATS);                                 // [SPLATS]
     int* prow_s = cur_s + SPLATS;                                                           // [TP]
-    u32* vid_s = reinterpret_cast<u32*>(prow_s + TP);                                       // [SPLATS] entry -> vertex
     __shared__ int wsum_s[32];
     __shared__ __align__(8) u64 bar;
     if (call_failed(hdr)) return;
@@ -819,10 +830,7 @@ splat_tiles_pair(Geom g, const float* __restrict__ input, Header* hdr, const int
     int item, pix;
     const bool valid = tile_point(g, tile, tid, item, pix);
     prow_s[tid] = valid ? item * g.n + pix : -1;
-    for (int i = tid; i < nloc; i += TP) {
-        cur_s[i] = 0;
-        vid_s[i] = list_ref[base + i];
-    }
+    for (int i = tid; i < nloc; i += TP) cur_s[i] = 0;
     if (bulk_ok && tid == 0) mbar_init(&bar, 1);
     const int nvalid = __syncthreads_count(valid);
 
@@ -852,7 +860,7 @@ splat_tiles_pair(Geom g, const float* __restrict__ input, Header* hdr, const int
         l[r] = valid ? rec_tile[r * TP + tid] : 0;
         w[r] = valid ? recw_tile[r * TP + tid] : 0.f;
     }
-    SplatCommon<PD>::sort_splats(valid, l, w, nloc, sorted_s, cur_s, nullptr, wsum_s);
+    SplatCommon<PD>::template sort_splats<2 * (PD + 1)>(valid, l, w, nloc, sorted_s, cur_s, nullptr, wsum_s);
 
     if (bulk_ok) {
         if (!mbar_wait(&bar, 0)) {
@@ -875,9 +883,10 @@ splat_tiles_pair(Geom g, const float* __restrict__ input, Header* hdr, const int
     float acc[NQ * 4];
 #pragma unroll
     for (int j = 0; j < NQ * 4; j++) acc[j] = 0.f;
-    int cur = (int)(sorted_s[first].x >> 16);
+    using SC = SplatCommon<PD>;
+    int cur = (int)(sorted_s[SC::template slot<WL>(first)].x >> 16);
     auto flush = [&](int entry) {
-        float* vrow = v0 + (size_t)vid_s[entry] * VP + 4 * half;
+        float* vrow = v0 + (size_t)list_ref[base + entry] * VP + 4 * half;
 #pragma unroll
         for (int k = 0; k < NQ; k++) {
             if (2 * k + half < QPR)
@@ -889,7 +898,7 @@ splat_tiles_pair(Geom g, const float* __restrict__ input, Header* hdr, const int
 #pragma unroll
     for (int i = 0; i < WL; i++) {
         if (first + i < total) {
-            const uint2 pw = sorted_s[first + i];
+            const uint2 pw = sorted_s[SC::template slot<WL>(first + i)];
             const int e = (int)(pw.x >> 16);
             if (e != cur) {
                 flush(cur);
@@ -962,7 +971,7 @@ splat_tiles_generic(Geom g, const float* __restrict__ input, Header* hdr, const 
         l[r] = valid ? rec_tile[r * TP + tid] : 0;
         w[r] = valid ? recw_tile[r * TP + tid] : 0.f;
     }
-    SplatCommon<PD>::sort_splats(valid, l, w, nloc, sorted_s, cur_s, off_s, wsum_s);
+    SplatCommon<PD>::template sort_splats<0>(valid, l, w, nloc, sorted_s, cur_s, off_s, wsum_s);
     cp_async_wait_all();
     __syncthreads();
 
@@ -1057,7 +1066,7 @@ splat_tiles_det(Geom g, const float* __restrict__ input, Header* hdr, const int2
         l[r] = valid ? rec_tile[r * TP + tid] : 0;
         w[r] = valid ? recw_tile[r * TP + tid] : 0.f;
     }
-    SplatCommon<PD>::sort_splats(valid, l, w, nloc, sorted_s, cur_s, nullptr, wsum_s);
+    SplatCommon<PD>::template sort_splats<0>(valid, l, w, nloc, sorted_s, cur_s, nullptr, wsum_s);
     cp_async_wait_all();
     __syncthreads();
 
@@ -1158,7 +1167,7 @@ struct SliceFast {
 };
 
 template <int PD, int VD>
-__global__ void __launch_bounds__(Cfg<PD>::TP)
+__global__ void __launch_bounds__(Cfg<PD>::TP, (Cfg<PD>::TP == 256) ? 5 : 8)
 slice_tiles_fast(Geom g, float* __restrict__ output, const Header* hdr, const int2* __restrict__ tile_info,
                  const u16* __restrict__ rec, const float* __restrict__ rec_w,
                  const u32* __restrict__ list_ref, const float* __restrict__ vsrc, int rows_cap, int bulk_ok) {
@@ -1528,7 +1537,7 @@ template <int PD, int VD>
 static int launch_splat(const Geom& g, const float* input, Header* hdr, const int2* tile_info, const u16* rec,
                         const float* rec_w, const u32* list_ref, float* v0, int vd, cudaStream_t st) {
     if constexpr (VD > 8) {          // wide rows: two lanes per window, paired 32-byte reductions
-        const size_t smem = SplatFast<PD, VD>::BYTES;
+        const size_t smem = SplatFast<PD, VD>::BYTES - sizeof(int) * Cfg<PD>::SPLATS;   // no vertex-id cache
         PL_CUDA(cudaFuncSetAttribute(splat_tiles_pair<PD, VD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         splat_tiles_pair<PD, VD><<<g.num_tiles, Cfg<PD>::TP, smem, st>>>(
             g, input, hdr, tile_info, rec, rec_w, list_ref, v0, bulk_rows_ok(g, input, VD - 1) ? 1 : 0);
