@@ -525,6 +525,12 @@ __device__ __forceinline__ void red_add_v4(float* addr, float4 v) {
                  "f"(v.w)
                  : "memory");
 }
+__device__ __forceinline__ void red_add_v2(float* addr, float a, float b) {
+    asm volatile("red.global.add.v2.f32 [%0], {%1, %2};" ::"l"(addr), "f"(a), "f"(b) : "memory");
+}
+__device__ __forceinline__ void red_add_f32(float* addr, float a) {
+    asm volatile("red.global.add.f32 [%0], %1;" ::"l"(addr), "f"(a) : "memory");
+}
 __device__ __forceinline__ void cp_async4(void* smem, const void* gmem) {
     const unsigned sa = (unsigned)__cvta_generic_to_shared(smem);
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(sa), "l"(gmem) : "memory");
@@ -809,9 +815,9 @@ splat_tiles_fast(Geom g, const float* __restrict__ input, Header* hdr, const int
     flush_row<VP>(v0 + (size_t)vid_s[cur] * VP, acc);
 }
 
-template <int PD, int VD>
+template <int PD, int VD, int GL>
 __global__ void __launch_bounds__(Cfg<PD>::TP)
-splat_tiles_pair(Geom g, const float* __restrict__ input, Header* hdr, const int2* __restrict__ tile_info,
+splat_tiles_group(Geom g, const float* __restrict__ input, Header* hdr, const int2* __restrict__ tile_info,
                  const u16* __restrict__ rec, const float* __restrict__ rec_w,
                  const u32* __restrict__ list_ref, float* __restrict__ v0, int bulk_ok) {
     constexpr int TP = Cfg<PD>::TP, SPLATS = Cfg<PD>::SPLATS, C = VD - 1, VP = (VD + 3) & ~3;
@@ -860,7 +866,7 @@ splat_tiles_pair(Geom g, const float* __restrict__ input, Header* hdr, const int
         l[r] = valid ? rec_tile[r * TP + tid] : 0;
         w[r] = valid ? recw_tile[r * TP + tid] : 0.f;
     }
-    SplatCommon<PD>::template sort_splats<2 * (PD + 1)>(valid, l, w, nloc, sorted_s, cur_s, nullptr, wsum_s);
+    SplatCommon<PD>::template sort_splats<GL * (PD + 1)>(valid, l, w, nloc, sorted_s, cur_s, nullptr, wsum_s);
 
     if (bulk_ok) {
         if (!mbar_wait(&bar, 0)) {
@@ -872,30 +878,40 @@ splat_tiles_pair(Geom g, const float* __restrict__ input, Header* hdr, const int
         __syncthreads();
     }
 
-    // Two lanes share a window of 2(PD+1) consecutive sorted splats: the even lane sums the even
-    // 16-byte quads of the row, the odd lane the odd quads.  Whenever the entry changes, and at the
-    // end of the window, the partial row leaves as vector reductions; the two lanes' quads of one
-    // step are neighbours in memory, so each pair of reductions is one 32-byte request.
-    constexpr int QPR = VP / 4, NQ = (QPR + 1) / 2, WL = 2 * (PD + 1);
-    const int total = nvalid * (PD + 1);
-    const int half = tid & 1, first = (tid >> 1) * WL;
-    if (first >= total) return;
-    float acc[NQ * 4];
-#pragma unroll
-    for (int j = 0; j < NQ * 4; j++) acc[j] = 0.f;
+    // GL lanes share a window of GL (PD+1) consecutive sorted splats.  A row is cut into pieces of
+    // 32 / GL bytes; lane h of the group sums pieces h, h + GL, h + 2 GL, ...  Whenever the entry
+    // changes, and at the end of the window, the partial row leaves as reductions: the GL lanes'
+    // pieces of one step are neighbours in memory, so each group issues one 32-byte request per step.
+    constexpr int PF = 8 / GL;                 // floats per piece: 4, 2 or 1
+    constexpr int NP = VP / PF;                // pieces per row
+    constexpr int NPL = (NP + GL - 1) / GL;    // pieces per lane
+    constexpr int WL = GL * (PD + 1);
     using SC = SplatCommon<PD>;
+    const int total = nvalid * (PD + 1);
+    const int h = tid % GL, first = (tid / GL) * WL;
+    if (first >= total) return;
+    float acc[NPL * PF];
+#pragma unroll
+    for (int j = 0; j < NPL * PF; j++) acc[j] = 0.f;
     int cur = (int)(sorted_s[SC::template slot<WL>(first)].x >> 16);
     auto flush = [&](int entry) {
-        float* vrow = v0 + (size_t)list_ref[base + entry] * VP + 4 * half;
+        float* vrow = v0 + (size_t)list_ref[base + entry] * VP + h * PF;
 #pragma unroll
-        for (int k = 0; k < NQ; k++) {
-            if (2 * k + half < QPR)
-                red_add_v4(vrow + 8 * k, make_float4(acc[4 * k], acc[4 * k + 1], acc[4 * k + 2], acc[4 * k + 3]));
+        for (int k = 0; k < NPL; k++) {
+            if (h + GL * k < NP) {
+                float* dst = vrow + GL * PF * k;
+                if constexpr (PF == 4)
+                    red_add_v4(dst, make_float4(acc[4 * k], acc[4 * k + 1], acc[4 * k + 2], acc[4 * k + 3]));
+                else if constexpr (PF == 2)
+                    red_add_v2(dst, acc[2 * k], acc[2 * k + 1]);
+                else
+                    red_add_f32(dst, acc[k]);
+            }
         }
 #pragma unroll
-        for (int j = 0; j < NQ * 4; j++) acc[j] = 0.f;
+        for (int j = 0; j < NPL * PF; j++) acc[j] = 0.f;
     };
-#pragma unroll
+#pragma unroll 4
     for (int i = 0; i < WL; i++) {
         if (first + i < total) {
             const uint2 pw = sorted_s[SC::template slot<WL>(first + i)];
@@ -905,16 +921,16 @@ splat_tiles_pair(Geom g, const float* __restrict__ input, Header* hdr, const int
                 cur = e;
             }
             const float wt = __uint_as_float(pw.y);
-            const float* x = in_s + (pw.x & 0xFFFFu) * C + 4 * half;
+            const float* x = in_s + (pw.x & 0xFFFFu) * C + h * PF;
 #pragma unroll
-            for (int k = 0; k < NQ; k++) {
+            for (int k = 0; k < NPL; k++) {
 #pragma unroll
-                for (int c = 0; c < 4; c++) {
-                    const int j = 8 * k + 4 * half + c;      // channel of this lane's slot
+                for (int c = 0; c < PF; c++) {
+                    const int j = (h + GL * k) * PF + c;      // channel of this lane's slot
                     if (j < C)
-                        acc[4 * k + c] = PL_FADD(acc[4 * k + c], PL_FMUL(wt, x[8 * k + c]));
+                        acc[PF * k + c] = PL_FADD(acc[PF * k + c], PL_FMUL(wt, x[GL * PF * k + c]));
                     else if (j == C)
-                        acc[4 * k + c] = PL_FADD(acc[4 * k + c], wt);
+                        acc[PF * k + c] = PL_FADD(acc[PF * k + c], wt);
                 }
             }
         }
@@ -1536,10 +1552,12 @@ static bool bulk_rows_ok(const Geom& g, const void* ptr, int channels) {
 template <int PD, int VD>
 static int launch_splat(const Geom& g, const float* input, Header* hdr, const int2* tile_info, const u16* rec,
                         const float* rec_w, const u32* list_ref, float* v0, int vd, cudaStream_t st) {
-    if constexpr (VD > 8) {          // wide rows: two lanes per window, paired 32-byte reductions
+    if constexpr (VD > 8) {          // wide rows: a group of lanes per window, 32-byte reduction requests
         const size_t smem = SplatFast<PD, VD>::BYTES - sizeof(int) * Cfg<PD>::SPLATS;   // no vertex-id cache
-        PL_CUDA(cudaFuncSetAttribute(splat_tiles_pair<PD, VD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        splat_tiles_pair<PD, VD><<<g.num_tiles, Cfg<PD>::TP, smem, st>>>(
+        // four lanes per window measured best for 24-float rows (two and eight lanes are within 10 %)
+        PL_CUDA(cudaFuncSetAttribute(splat_tiles_group<PD, VD, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     (int)smem));
+        splat_tiles_group<PD, VD, 4><<<g.num_tiles, Cfg<PD>::TP, smem, st>>>(
             g, input, hdr, tile_info, rec, rec_w, list_ref, v0, bulk_rows_ok(g, input, VD - 1) ? 1 : 0);
     } else if constexpr (VD > 0) {
         const size_t smem = SplatFast<PD, VD>::BYTES;
