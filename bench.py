@@ -31,6 +31,10 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 METRIC = "Mpixels/s fwd+bwd (pd=5, vd=22 CRF)"
+# DRAM bytes per point and launch (dram__bytes_read.sum + dram__bytes_write.sum) of the kernels of configuration 2,
+# from the one-pass ncu capture of the full-size workload summarised in
+# profiles/dram_traffic_c2_dense_crf_16x512.txt; traffic is proportional to the number of points.
+NCU_DRAM_BYTES_PER_POINT_C2 = {"build_tiles": 50.8, "splat_tiles": 150.0, "slice_tiles": 125.1, "blur_axis": 20.6}
 FALLBACK_HBM_GBS = 6650.0
 
 
@@ -363,9 +367,12 @@ def main():
                     "slice": "slice_tiles"}
     dominant = max(kernel_names, key=lambda k: stage_ms[k])
     achieved = kernel_bytes[dominant] / (kernel_ms[dominant] * 1e-3) / 1e9
+    traffic = None
+    if args.config == 2:
+        traffic = NCU_DRAM_BYTES_PER_POINT_C2[kernel_names[dominant]] * b * n
     roofline = {"bound": "hbm", "kernel": kernel_names[dominant], "achieved": achieved,
                 "peak": hbm_gbs, "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / hbm_gbs,
-                "traffic": None, "algorithmic_bytes_per_launch": kernel_bytes[dominant],
+                "traffic": traffic, "algorithmic_bytes_per_launch": kernel_bytes[dominant],
                 "ms_per_launch": kernel_ms[dominant]}
     call_ms = ms_per_step / calls_per_step
     call_gbs = call_bytes / (call_ms * 1e-3) / 1e9
