@@ -266,7 +266,7 @@ build_tiles(Geom g, const float* __restrict__ positions, const float* __restrict
         for (int r = 1; r <= PD; r++) {
 #pragma unroll
             for (int i = 0; i < PD; i++)
-                if (s.rank[i] == PD - r + 1) k.w[i >> 2] -= (u64)(PD + 1) << (16 * (i & 3));
+                k.w[i >> 2] -= (s.rank[i] == PD - r + 1) ? ((u64)(PD + 1) << (16 * (i & 3))) : 0ull;
 #pragma unroll
             for (int j = 0; j < KW; j++) k.w[j] += coord_ones<PD>(j);
             keys_s[r * TP + tid] = k;

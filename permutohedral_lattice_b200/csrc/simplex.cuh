@@ -95,7 +95,7 @@ PL_HD void find_simplex(const float* pos, const float* scale, Simplex<PD>& s) {
     for (int i = 0; i <= PD; i++) {
         const float v = PL_FMUL(s.el[i], inv_f);
         float fl = PL_FSUB(PL_FADD(v, PL_ROUND_MAGIC), PL_ROUND_MAGIC);   // nearest integer
-        if (fl > v) fl = PL_FSUB(fl, 1.0f);                              // -> floor
+        fl = (fl > v) ? PL_FSUB(fl, 1.0f) : fl;                          // -> floor
         const float down = PL_FMUL(fl, (float)(PD + 1));                 // exact: small integers
         const float up = PL_FADD(down, (float)(PD + 1));
         s.rem0f[i] = (PL_FSUB(up, s.el[i]) < PL_FSUB(s.el[i], down)) ? up : down;
@@ -114,24 +114,21 @@ PL_HD void find_simplex(const float* pos, const float* scale, Simplex<PD>& s) {
     for (int i = 0; i < PD; i++) {
 #pragma unroll
         for (int j = i + 1; j <= PD; j++) {
-            if (d[i] < d[j])
-                s.rank[i]++;
-            else
-                s.rank[j]++;
+            const int lt = d[i] < d[j] ? 1 : 0;   // arithmetic on the predicate: no branches
+            s.rank[i] += lt;
+            s.rank[j] += 1 - lt;
         }
     }
 #pragma unroll
     for (int i = 0; i <= PD; i++) {
         s.rank[i] += sum;
-        if (s.rank[i] < 0) {
-            s.rank[i] += PD + 1;
-            s.rem0[i] += PD + 1;
-            s.rem0f[i] = PL_FADD(s.rem0f[i], (float)(PD + 1));
-        } else if (s.rank[i] > PD) {
-            s.rank[i] -= PD + 1;
-            s.rem0[i] -= PD + 1;
-            s.rem0f[i] = PL_FSUB(s.rem0f[i], (float)(PD + 1));
-        }
+        // wrap into 0..PD: +1 cell when below, -1 cell when above (selects, no branches)
+        const int wrap = (s.rank[i] < 0 ? 1 : 0) - (s.rank[i] > PD ? 1 : 0);
+        s.rank[i] += wrap * (PD + 1);
+        s.rem0[i] += wrap * (PD + 1);
+        s.rem0f[i] = (wrap > 0)   ? PL_FADD(s.rem0f[i], (float)(PD + 1))
+                     : (wrap < 0) ? PL_FSUB(s.rem0f[i], (float)(PD + 1))
+                                  : s.rem0f[i];
     }
 }
 
@@ -158,8 +155,7 @@ PL_HD void barycentric(const Simplex<PD>& s, float* bary /* PD+1 */) {
         const float e = PL_FMA(d, ch, -p);             // exact error of p
         const float delta = PL_FADD(p, PL_FMA(d, cl, e));
 #pragma unroll
-        for (int q = 0; q <= PD; q++)
-            if (s.rank[i] == q) by_rank[q] = delta;
+        for (int q = 0; q <= PD; q++) by_rank[q] = (s.rank[i] == q) ? delta : by_rank[q];   // select, not branch
     }
 #pragma unroll
     for (int k = 1; k <= PD; k++) bary[k] = PL_FSUB(by_rank[PD - k], by_rank[PD - k + 1]);
@@ -169,8 +165,7 @@ PL_HD void barycentric(const Simplex<PD>& s, float* bary /* PD+1 */) {
 // Coordinate i (< PD) of the remainder-r vertex of the simplex (src/PermutohedralLatticeCPU.h:297-304).
 template <int PD>
 PL_HD int16_t vertex_coord(const Simplex<PD>& s, int i, int r) {
-    int k = s.rem0[i] + r;
-    if (s.rank[i] > PD - r) k -= PD + 1;
+    const int k = s.rem0[i] + r - ((s.rank[i] > PD - r) ? PD + 1 : 0);
     return (int16_t)k;
 }
 
