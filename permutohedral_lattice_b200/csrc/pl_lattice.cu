@@ -1220,7 +1220,22 @@ slice_tiles_fast(Geom g, float* __restrict__ output, const Header* hdr, const in
     float acc[VP];
 #pragma unroll
     for (int j = 0; j < VP; j++) acc[j] = 0.f;
-    if (valid) {
+    if (valid && cnt <= rows_cap) {
+        // every row of the tile is cached (the usual case): plain shared-memory reads
+#pragma unroll
+        for (int r = 0; r <= PD; r++) {
+            const float4* row = reinterpret_cast<const float4*>(rows_s + l[r] * RS);
+#pragma unroll
+            for (int q = 0; q < QPR; q++) {
+                const float4 x = row[q];
+                acc[4 * q] = PL_FADD(acc[4 * q], PL_FMUL(w[r], x.x));
+                acc[4 * q + 1] = PL_FADD(acc[4 * q + 1], PL_FMUL(w[r], x.y));
+                acc[4 * q + 2] = PL_FADD(acc[4 * q + 2], PL_FMUL(w[r], x.z));
+                acc[4 * q + 3] = PL_FADD(acc[4 * q + 3], PL_FMUL(w[r], x.w));
+            }
+        }
+    } else if (valid) {
+        // a tile with more entries than the cache holds: the rest comes straight from global memory
 #pragma unroll
         for (int r = 0; r <= PD; r++) {
             const float4* row = (l[r] < nrows) ? reinterpret_cast<const float4*>(rows_s + l[r] * RS)
