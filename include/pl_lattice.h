@@ -97,6 +97,28 @@ int pl_lattice_filter_f32(float* output, const float* input, const float* refere
                           float theta_beta, float theta_gamma, int reverse, void* workspace,
                           size_t workspace_bytes, int64_t max_entries, int mode, void* stream);
 
+/* The same filter in two halves, for callers that filter several value tensors through ONE reference
+ * (forward and backward of a layer, the iterations of CRF mean-field inference: the use the reference
+ * library was written for, README.md:15-16, which rebuilds its lattice on every call,
+ * src/LatticeFilterKernel.cpp:79, src/LatticeFilterKernel.cu:88).
+ * pl_lattice_build*_f32 constructs the lattice of a batch in `workspace` (entries, vertices, neighbour
+ * table, per-point records); pl_lattice_apply_f32 then splats, blurs and slices `input` through it and
+ * may be called any number of times, with any number of channels up to max_value_dim - 1, forward or
+ * reverse, while the workspace is left untouched in between.  build + apply gives bit-for-bit what
+ * pl_lattice_filter_f32 / pl_filter_f32 give (in deterministic mode; in atomic mode up to the order of
+ * the sums).  The geometry arguments of apply (batch, n, pd, spatial_dims or NULL for a lattice built
+ * from positions, max_entries) must repeat those of the build; workspace_bytes must cover
+ * pl_workspace_bytes(..., vd = max_value_dim, ...). */
+int pl_lattice_build_f32(const float* reference, int batch, int n_spatial_dims, const int* spatial_dims,
+                         int n_reference_channels, int bilateral, float theta_alpha, float theta_beta,
+                         float theta_gamma, int max_value_dim, void* workspace, size_t workspace_bytes,
+                         int64_t max_entries, void* stream);
+int pl_lattice_build_positions_f32(const float* positions, int batch, int n, int pd, int max_value_dim,
+                                   void* workspace, size_t workspace_bytes, int64_t max_entries, void* stream);
+int pl_lattice_apply_f32(float* output, const float* input, int n_input_channels, int reverse, int mode, int batch,
+                         int n, int pd, int n_spatial_dims, const int* spatial_dims, void* workspace,
+                         size_t workspace_bytes, int64_t max_entries, void* stream);
+
 /* The op for callers that must not allocate device memory and have no buffer to lend: a plugin
  * loaded into a host application whose memory pool already owns the GPU's memory, or a service that
  * forbids allocation calls once it is running.  Same arguments and results as

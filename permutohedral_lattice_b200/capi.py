@@ -23,6 +23,7 @@ EXPORTED_SYMBOLS = [
     "pl_supported", "pl_strerror", "pl_last_cuda_error", "pl_workspace_bytes",
     "pl_compute_positions_f32", "pl_filter_f32", "pl_lattice_filter_f32", "pl_lattice_stats",
     "pl_export_lattice", "pl_profile_next_call", "pl_lattice_filter_f32_noalloc",
+    "pl_lattice_build_f32", "pl_lattice_build_positions_f32", "pl_lattice_apply_f32",
 ]
 STATIC_SCRATCH_BYTES = 64 << 20
 NUM_STAGE_EVENTS = 6
@@ -70,6 +71,9 @@ def lib():
         L.pl_export_lattice.argtypes = [vp, vp, vp, i, i, i, i, i, ip, i, f, f, i64, i64, vp, vp, vp,
                                         vp, vp]
         L.pl_lattice_filter_f32_noalloc.argtypes = [vp, vp, vp, i, i, ip, i, i, i, f, f, f, i, i64, vp]
+        L.pl_lattice_build_f32.argtypes = [vp, i, i, ip, i, i, f, f, f, i, vp, ctypes.c_size_t, i64, vp]
+        L.pl_lattice_build_positions_f32.argtypes = [vp, i, i, i, i, vp, ctypes.c_size_t, i64, vp]
+        L.pl_lattice_apply_f32.argtypes = [vp, vp, i, i, i, i, i, i, i, ip, vp, ctypes.c_size_t, i64, vp]
         L.pl_profile_next_call.argtypes = [ctypes.POINTER(ctypes.c_void_p)]
         _lib = L
     return _lib

@@ -473,6 +473,7 @@ link_vertices(Header* hdr, u32* __restrict__ list_ref, const u32* __restrict__ v
     int2* nb = reinterpret_cast<int2*>(nbr);
     for (int a = 0; a <= pd; a++)
         for (u64 v = gtid; v < M; v += gsz) nb[(u64)a * max_entries + v] = make_int2(-1, -1);
+    if (vd == 0) return;   // lattice built ahead of its use: rows are zeroed by each apply
     const u64 cells = (u64)M * padded_vd(vd);
     if (v64) {
         for (u64 e = gtid; e < cells; e += gsz) v64[e] = 0;
@@ -1126,6 +1127,20 @@ convert_fixed(const Header* hdr, const long long* __restrict__ v64, float* __res
         v0[i] = (float)PL_DMUL(__ll2double_rn(v64[i]), inv);
 }
 
+// Start of an apply on an already built lattice: value rows (or fixed-point sums) back to zero.
+__global__ void __launch_bounds__(256)
+zero_rows(Header* hdr, float* __restrict__ v0, long long* __restrict__ v64, int vp) {
+    if (hdr->status != 0) return;
+    if (blockIdx.x == 0 && threadIdx.x == 0) hdr->absmax_bits = 0;
+    const u64 cells = (u64)hdr->num_vertices * vp;
+    const u64 gtid = (u64)blockIdx.x * blockDim.x + threadIdx.x, gsz = (u64)gridDim.x * blockDim.x;
+    if (v64) {
+        for (u64 e = gtid; e < cells; e += gsz) v64[e] = 0;
+    } else {
+        for (u64 e = gtid; e < cells; e += gsz) v0[e] = 0.f;
+    }
+}
+
 // ---------------------------------------------------------------------------------------------
 // blur_axis: one [1 2 1]/4 pass along lattice axis `axis` (src/PermutohedralLatticeCPU.h:403-405:
 // the three products and their sum in double, one rounding to float).  One float4 per thread.
@@ -1618,10 +1633,12 @@ static int launch_slice(const Geom& g, float* output, const Header* hdr, const i
      : (vd) == 2 ? FN<PD_, 2>(__VA_ARGS__)                                  \
                  : FN<PD_, 0>(__VA_ARGS__))
 
+enum { PH_BUILD = 1, PH_APPLY = 2 };   // halves of a call: lattice structure / values through it
+
 template <int PD>
 static int run_filter(const Geom& g, float* output, const float* input, const float* positions,
                       const float* reference, int vd, int reverse, int mode, void* workspace,
-                      const Layout& L, cudaStream_t st) {
+                      const Layout& L, cudaStream_t st, int phases = PH_BUILD | PH_APPLY) {
     constexpr int KW = Cfg<PD>::KW, TP = Cfg<PD>::TP;
     unsigned char* ws = static_cast<unsigned char*>(workspace);
     Header* hdr = reinterpret_cast<Header*>(ws);
@@ -1641,7 +1658,7 @@ static int run_filter(const Geom& g, float* output, const float* input, const fl
     cudaEvent_t* ev = g_stage_events;
     g_stage_events = nullptr;
     if (ev) PL_CUDA(cudaEventRecord(ev[0], st));
-    PL_CUDA(cudaMemsetAsync(hdr, 0, sizeof(Header), st));
+    if (phases & PH_BUILD) PL_CUDA(cudaMemsetAsync(hdr, 0, sizeof(Header), st));
     if (g.num_tiles == 0) return PL_OK;
 
     // per device and cheap, so set on every call rather than cached
@@ -1652,14 +1669,25 @@ static int run_filter(const Geom& g, float* output, const float* input, const fl
     int table_log2 = 0;
     while ((1ull << table_log2) < L.table_slots) table_log2++;
 
-    build_tiles<PD><<<g.num_tiles, TP, Cfg<PD>::BUILD_SMEM, st>>>(
-        g, positions, reference, hdr, tile_info, rec, rec_w, list_keys, (u32)L.max_entries);
-    if (ev) PL_CUDA(cudaEventRecord(ev[1], st));
-    clear_table<<<wide, 256, 0, st>>>(hdr, table, (u32)table_log2);
-    insert_entries<KW><<<wide, 256, 0, st>>>(hdr, table, list_keys, list_ref, vid, vowner);
-    link_vertices<<<wide, 256, 0, st>>>(hdr, list_ref, vid, nbr, v0, v64, L.max_entries, PD, vd);
-    link_neighbours<PD><<<wide, 256, 0, st>>>(hdr, table, list_keys, vid, vowner, nbr, L.max_entries);
-    if (ev) PL_CUDA(cudaEventRecord(ev[2], st));
+    if (phases & PH_BUILD) {
+        build_tiles<PD><<<g.num_tiles, TP, Cfg<PD>::BUILD_SMEM, st>>>(
+            g, positions, reference, hdr, tile_info, rec, rec_w, list_keys, (u32)L.max_entries);
+        if (ev) PL_CUDA(cudaEventRecord(ev[1], st));
+        clear_table<<<wide, 256, 0, st>>>(hdr, table, (u32)table_log2);
+        insert_entries<KW><<<wide, 256, 0, st>>>(hdr, table, list_keys, list_ref, vid, vowner);
+        link_vertices<<<wide, 256, 0, st>>>(hdr, list_ref, vid, nbr, v0, v64, L.max_entries, PD,
+                                            (phases & PH_APPLY) ? vd : 0);
+        link_neighbours<PD><<<wide, 256, 0, st>>>(hdr, table, list_keys, vid, vowner, nbr, L.max_entries);
+        if (ev) PL_CUDA(cudaEventRecord(ev[2], st));
+    } else {
+        if (ev) { PL_CUDA(cudaEventRecord(ev[1], st)); }
+        zero_rows<<<wide, 256, 0, st>>>(hdr, v0, v64, padded_vd(vd));
+        if (ev) { PL_CUDA(cudaEventRecord(ev[2], st)); }
+    }
+    if (!(phases & PH_APPLY)) {
+        PL_CUDA(cudaGetLastError());
+        return PL_OK;
+    }
     int rc = PL_OK;
     if (v64) {
         const size_t smem = SplatDet<PD>::bytes(vd);
@@ -1728,13 +1756,14 @@ static int run_export(const Geom& g, const float* positions, const float* refere
 
 static int filter_common(const Geom& g, float* output, const float* input, const float* positions,
                          const float* reference, int pd, int vd, int reverse, void* workspace,
-                         size_t workspace_bytes, int64_t max_entries, int mode, cudaStream_t st) {
+                         size_t workspace_bytes, int64_t max_entries, int mode, cudaStream_t st,
+                         int phases = PH_BUILD | PH_APPLY) {
     if (mode != PL_MODE_ATOMIC && mode != PL_MODE_DETERMINISTIC) return PL_INVALID_ARGUMENT;
     Layout L;
     int rc = make_layout(L, g, pd, vd, max_entries);
     if (rc != PL_OK) return rc;
     if (workspace_bytes < L.total) return PL_WORKSPACE_TOO_SMALL;
-#define CALL(P) run_filter<P>(g, output, input, positions, reference, vd, reverse, mode, workspace, L, st)
+#define CALL(P) run_filter<P>(g, output, input, positions, reference, vd, reverse, mode, workspace, L, st, phases)
     PL_DISPATCH_PD(pd, CALL)
 #undef CALL
 }
@@ -1916,6 +1945,61 @@ int pl_lattice_filter_f32_noalloc(float* output, const float* input, const float
     // into; everything else in the scratch is written before it is read
     return filter_common(g, output, input, nullptr, reference, pd, vd, reverse, scratch,
                          (size_t)PL_STATIC_SCRATCH_BYTES, max_entries, PL_MODE_ATOMIC, (cudaStream_t)stream);
+}
+
+int pl_lattice_build_f32(const float* reference, int batch, int n_spatial_dims, const int* spatial_dims,
+                         int n_reference_channels, int bilateral, float theta_alpha, float theta_beta,
+                         float theta_gamma, int max_value_dim, void* workspace, size_t workspace_bytes,
+                         int64_t max_entries, void* stream) {
+    Geom g;
+    int pd = 0, n = 0;
+    int rc = op_geom(g, batch, n_spatial_dims, spatial_dims, n_reference_channels, bilateral, theta_alpha,
+                     theta_beta, theta_gamma, &pd, &n);
+    if (rc != PL_OK) return rc;
+    if (!pl_supported(pd, max_value_dim)) return PL_UNSUPPORTED_DIMS;
+    if (batch == 0 || n == 0) return PL_OK;
+    if (!workspace || (g.R > 0 && !reference)) return PL_INVALID_ARGUMENT;
+    return filter_common(g, nullptr, nullptr, nullptr, reference, pd, max_value_dim, 0, workspace, workspace_bytes,
+                         max_entries, PL_MODE_ATOMIC, (cudaStream_t)stream, PH_BUILD);
+}
+
+int pl_lattice_build_positions_f32(const float* positions, int batch, int n, int pd, int max_value_dim,
+                                   void* workspace, size_t workspace_bytes, int64_t max_entries, void* stream) {
+    if (batch < 0 || n < 0 || batch > 65535) return PL_INVALID_ARGUMENT;
+    if (!pl_supported(pd, max_value_dim)) return PL_UNSUPPORTED_DIMS;
+    if (batch == 0 || n == 0) return PL_OK;
+    if (!positions || !workspace) return PL_INVALID_ARGUMENT;
+    Geom g;
+    int one = n;
+    int rc = make_geom(g, batch, n, pd, 1, &one, pd - 1, 1.f, 1.f, true);
+    if (rc != PL_OK) return rc;
+    return filter_common(g, nullptr, nullptr, positions, nullptr, pd, max_value_dim, 0, workspace, workspace_bytes,
+                         max_entries, PL_MODE_ATOMIC, (cudaStream_t)stream, PH_BUILD);
+}
+
+int pl_lattice_apply_f32(float* output, const float* input, int n_input_channels, int reverse, int mode, int batch,
+                         int n, int pd, int n_spatial_dims, const int* spatial_dims, void* workspace,
+                         size_t workspace_bytes, int64_t max_entries, void* stream) {
+    if (n_input_channels < 1 || batch < 0 || n < 0 || batch > 65535) return PL_INVALID_ARGUMENT;
+    const int vd = n_input_channels + 1;
+    if (!pl_supported(pd, vd)) return PL_UNSUPPORTED_DIMS;
+    if (batch == 0 || n == 0) return PL_OK;
+    if (!output || !input || !workspace) return PL_INVALID_ARGUMENT;
+    Geom g;
+    int rc;
+    if (spatial_dims) {
+        if (n_spatial_dims < 1 || n_spatial_dims > MAX_SDIMS || n_spatial_dims > pd) return PL_INVALID_ARGUMENT;
+        long long prod = 1;
+        for (int i = 0; i < n_spatial_dims; i++) prod *= spatial_dims[i];
+        if (prod != n) return PL_INVALID_ARGUMENT;
+        rc = make_geom(g, batch, n, pd, n_spatial_dims, spatial_dims, pd - n_spatial_dims, 1.f, 1.f, false);
+    } else {
+        int one = n;
+        rc = make_geom(g, batch, n, pd, 1, &one, pd - 1, 1.f, 1.f, true);
+    }
+    if (rc != PL_OK) return rc;
+    return filter_common(g, output, input, nullptr, nullptr, pd, vd, reverse, workspace, workspace_bytes,
+                         max_entries, mode, (cudaStream_t)stream, PH_APPLY);
 }
 
 int pl_profile_next_call(void** stage_events) {

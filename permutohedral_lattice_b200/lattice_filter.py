@@ -121,6 +121,90 @@ def lattice_stats(workspace, stream=None):
     return st
 
 
+class Lattice:
+    """A lattice built once and applied many times (pl_lattice_build_f32 / pl_lattice_apply_f32).
+
+    The reference rebuilds its lattice on every call; its main user, CRF mean-field inference, filters
+    many tensors through the same reference image (forward, backward, every iteration).  `Lattice`
+    keeps the structure (entries, vertices, neighbour table, per-point records) in a workspace of its
+    own and only splats, blurs and slices per call."""
+
+    def __init__(self, reference_image, spatial_shape=None, bilateral=True, theta_alpha=1.0, theta_beta=1.0,
+                 theta_gamma=1.0, max_channels=1, max_entries=0):
+        """reference_image [B, *S, R] (bilateral) — or None with spatial_shape = (B, *S) for a purely
+        spatial kernel.  max_channels: the widest input that will be applied."""
+        if bilateral:
+            _check_tensor(reference_image, "reference_image")
+            ref = reference_image.contiguous()
+            shape = tuple(ref.shape[:-1])
+            device = ref.device
+        else:
+            ref = None
+            shape = tuple(spatial_shape if spatial_shape is not None else reference_image.shape[:-1])
+            device = reference_image.device if reference_image is not None else torch.device(
+                "cuda", torch.cuda.current_device())
+        self.call = FilterCall(shape + (int(max_channels),), None if ref is None else tuple(ref.shape), bilateral,
+                               theta_alpha, theta_beta, theta_gamma)
+        self.max_entries = int(max_entries)
+        self.device = device
+        call = self.call
+        if not capi.lib().pl_supported(call.pd, call.vd):
+            raise capi.PlError(capi.PL_UNSUPPORTED_DIMS, "Lattice(pd=%d, vd=%d)" % (call.pd, call.vd))
+        self.workspace = None
+        if call.batch == 0 or call.n == 0:
+            return
+        with torch.cuda.device(device):
+            self.workspace = torch.empty(call.workspace_bytes(self.max_entries), dtype=torch.uint8, device=device)
+            capi.check(capi.lib().pl_lattice_build_f32(
+                0 if ref is None else ref.data_ptr(), call.batch, len(call.sdims), capi.int_array(call.sdims),
+                call.r, int(call.bilateral), call.theta[0], call.theta[1], call.theta[2], call.vd,
+                self.workspace.data_ptr(), self.workspace.numel(), self.max_entries, _stream_handle(device)),
+                "pl_lattice_build_f32")
+
+    def apply(self, input_image, reverse=False, mode="atomic", out=None):
+        """Filters input_image [B, *S, C] (C <= max_channels) through the lattice."""
+        _check_tensor(input_image, "input_image")
+        x = input_image.contiguous()
+        call = self.call
+        if tuple(x.shape[:-1]) != (call.batch,) + tuple(call.sdims):
+            raise ValueError("input_image does not have the lattice's batch and spatial shape")
+        if x.shape[-1] + 1 > call.vd:
+            raise ValueError("input_image has more channels than the lattice was built for")
+        if out is None:
+            out = torch.empty_like(x)
+        if self.workspace is None:
+            return out
+        with torch.cuda.device(self.device):
+            capi.check(capi.lib().pl_lattice_apply_f32(
+                out.data_ptr(), x.data_ptr(), x.shape[-1], int(bool(reverse)), capi.MODES[mode], call.batch,
+                call.n, call.pd, len(call.sdims), capi.int_array(call.sdims), self.workspace.data_ptr(),
+                self.workspace.numel(), self.max_entries, _stream_handle(self.device)), "pl_lattice_apply_f32")
+        return out
+
+    def stats(self):
+        return lattice_stats(self.workspace)
+
+
+class _LatticeFilterReuseFunction(torch.autograd.Function):
+    """forward builds the lattice and keeps it for backward, which only applies it (reverse=True)."""
+
+    @staticmethod
+    def forward(ctx, input_image, reference_image, bilateral, theta_alpha, theta_beta, theta_gamma, reverse,
+                mode):
+        lattice = Lattice(reference_image, tuple(input_image.shape[:-1]), bilateral, theta_alpha, theta_beta,
+                          theta_gamma, max_channels=input_image.shape[-1])
+        ctx.lattice, ctx.mode = lattice, mode
+        ctx.save_for_backward(reference_image)   # autograd's version check guards against in-place edits
+        return lattice.apply(input_image, reverse, mode)
+
+    @staticmethod
+    def backward(ctx, grad):
+        (reference_image,) = ctx.saved_tensors
+        g = ctx.lattice.apply(grad, True, ctx.mode)
+        ref_grad = torch.zeros_like(reference_image) if reference_image is not None else None
+        return g, ref_grad, None, None, None, None, None, None
+
+
 class _LatticeFilterFunction(torch.autograd.Function):
     @staticmethod
     def forward(ctx, input_image, reference_image, bilateral, theta_alpha, theta_beta, theta_gamma,
@@ -144,10 +228,13 @@ class _LatticeFilterFunction(torch.autograd.Function):
 
 
 def lattice_filter(input_image, reference_image, bilateral=True, theta_alpha=1.0, theta_beta=1.0,
-                   theta_gamma=1.0, reverse=False, mode="atomic"):
+                   theta_gamma=1.0, reverse=False, mode="atomic", reuse_lattice=False):
     """output[B, *S, C] = permutohedral-lattice filter of input_image[B, *S, C] guided by
-    reference_image[B, *S, R] (bilateral) or by position only (bilateral=False, theta_gamma)."""
-    return _LatticeFilterFunction.apply(input_image, reference_image, bool(bilateral),
+    reference_image[B, *S, R] (bilateral) or by position only (bilateral=False, theta_gamma).
+    reuse_lattice=True keeps the lattice built in forward for the backward pass instead of rebuilding
+    it there (same results; the reference always rebuilds)."""
+    fn = _LatticeFilterReuseFunction if reuse_lattice else _LatticeFilterFunction
+    return fn.apply(input_image, reference_image, bool(bilateral),
                                         float(theta_alpha), float(theta_beta), float(theta_gamma),
                                         bool(reverse), mode)
 

@@ -245,3 +245,39 @@ def test_host_pipeline_matches_device_call(gpu, oracle):
         got = pipe.filter(inp, ref, True, 5.0, 0.2, reverse=reverse).numpy()
         want = oracle.lattice_filter(inp.numpy(), ref.numpy(), True, 5.0, 0.2, 1.0, reverse)
         gpu.assert_outputs_close(got, want, "host pipeline")
+
+
+def test_lattice_built_once_applied_many_times(gpu, oracle):
+    import torch
+    import permutohedral_lattice_b200 as plb
+    from conftest import bits
+    rng = np.random.default_rng(41)
+    ref_n = rng.random((2, 30, 26, 3), dtype=np.float32)
+    ref = torch.from_numpy(ref_n).cuda()
+    lat = plb.Lattice(ref, bilateral=True, theta_alpha=5.0, theta_beta=0.2, max_channels=6)
+    for c, reverse in ((6, False), (2, True), (6, True), (1, False)):
+        x_n = rng.standard_normal((2, 30, 26, c)).astype(np.float32)
+        got = lat.apply(torch.from_numpy(x_n).cuda(), reverse=reverse).cpu().numpy()
+        want = oracle.lattice_filter(x_n, ref_n, True, 5.0, 0.2, 1.0, reverse)
+        gpu.assert_outputs_close(got, want, "apply c=%d reverse=%s" % (c, reverse))
+    # deterministic mode: build + apply is bit-for-bit the one-call filter
+    x = torch.from_numpy(rng.random((2, 30, 26, 6), dtype=np.float32)).cuda()
+    a = lat.apply(x, mode="deterministic").cpu().numpy()
+    b = plb.lattice_filter(x, ref, True, 5.0, 0.2, mode="deterministic").cpu().numpy()
+    assert np.array_equal(bits(a), bits(b))
+
+
+def test_autograd_with_lattice_reuse(gpu, oracle):
+    import torch
+    import permutohedral_lattice_b200 as plb
+    rng = np.random.default_rng(43)
+    ref_n = rng.random((1, 24, 20, 3), dtype=np.float32)
+    inp_n = rng.random((1, 24, 20, 4), dtype=np.float32)
+    grad_n = rng.standard_normal((1, 24, 20, 4)).astype(np.float32)
+    ref = torch.from_numpy(ref_n).cuda()
+    inp = torch.from_numpy(inp_n).cuda().requires_grad_(True)
+    out = plb.lattice_filter(inp, ref, True, 5.0, 0.2, reuse_lattice=True)
+    out.backward(torch.from_numpy(grad_n).cuda())
+    gpu.assert_outputs_close(out.detach().cpu().numpy(), oracle.lattice_filter(inp_n, ref_n, True, 5.0, 0.2), "fwd")
+    gpu.assert_outputs_close(inp.grad.cpu().numpy(), oracle.lattice_filter(grad_n, ref_n, True, 5.0, 0.2, 1.0, True),
+                             "bwd")
