@@ -48,6 +48,8 @@ struct Geom {
     int W, H, outer;        // n = outer * H * W (W fastest)
     int TX, TY;             // tile = TY rows of TX points, TX * TY = TP
     int tiles_x, tiles_y, tiles_per_item, num_tiles;
+    int tx_log2;            // TX is a power of two
+    int grid3;              // 1: tile kernels run on a (tiles_x, tiles_y, batch * outer) grid
     int n_sdims, R;         // op path: spatial dims and reference channels (pd = n_sdims + R)
     int sdims[MAX_SDIMS];
     float spatial_std, feature_std;
@@ -146,25 +148,53 @@ __device__ __forceinline__ u32 tile_hash(const Key<KW>& k) {
     return h ^ (h >> 13);
 }
 
-// Point handled by thread `tid` of tile `tile`: item, point index inside the item, validity; the
-// long form also gives the point's position (outer index, row, column).
-__device__ __forceinline__ bool tile_point(const Geom& g, int tile, int tid, int& item, int& pix, int& o,
+// Tile of this CTA.  Tile kernels run on a 3-D grid (tile column, tile row, item * outer + outer index)
+// whenever that fits the grid limits, so no thread divides to find its tile; else on a 1-D grid.
+struct TilePos {
+    int tile, item, o, ty, tx;
+};
+__device__ __forceinline__ TilePos this_tile(const Geom& g) {
+    TilePos t;
+    if (g.grid3) {
+        t.tx = blockIdx.x;
+        t.ty = blockIdx.y;
+        const int z = blockIdx.z;
+        if (g.outer == 1) {
+            t.item = z;
+            t.o = 0;
+        } else {
+            t.item = z / g.outer;
+            t.o = z - t.item * g.outer;
+        }
+        t.tile = (z * g.tiles_y + t.ty) * g.tiles_x + t.tx;
+    } else {
+        t.tile = blockIdx.x;
+        t.item = t.tile / g.tiles_per_item;
+        int r = t.tile - t.item * g.tiles_per_item;
+        const int per_plane = g.tiles_x * g.tiles_y;
+        t.o = r / per_plane;
+        r -= t.o * per_plane;
+        t.ty = r / g.tiles_x;
+        t.tx = r - t.ty * g.tiles_x;
+    }
+    return t;
+}
+
+// Point handled by thread `tid` of the tile: item, point index inside the item, validity; the long
+// form also gives the point's position (outer index, row, column).
+__device__ __forceinline__ bool tile_point(const Geom& g, const TilePos& t, int tid, int& item, int& pix, int& o,
                                            int& y, int& x) {
-    item = tile / g.tiles_per_item;
-    int t = tile - item * g.tiles_per_item;
-    int per_plane = g.tiles_x * g.tiles_y;
-    o = t / per_plane;
-    t -= o * per_plane;
-    int ty = t / g.tiles_x, tx = t - ty * g.tiles_x;
-    int ly = tid / g.TX, lx = tid - ly * g.TX;
-    y = ty * g.TY + ly;
-    x = tx * g.TX + lx;
+    item = t.item;
+    o = t.o;
+    const int ly = tid >> g.tx_log2, lx = tid & (g.TX - 1);
+    y = t.ty * g.TY + ly;
+    x = t.tx * g.TX + lx;
     pix = (o * g.H + y) * g.W + x;
     return (y < g.H) && (x < g.W);
 }
-__device__ __forceinline__ bool tile_point(const Geom& g, int tile, int tid, int& item, int& pix) {
+__device__ __forceinline__ bool tile_point(const Geom& g, const TilePos& t, int tid, int& item, int& pix) {
     int o, y, x;
-    return tile_point(g, tile, tid, item, pix, o, y, x);
+    return tile_point(g, t, tid, item, pix, o, y, x);
 }
 
 // Feature vector of a point.  Op path: src/PermutohedralLatticeCPU.h:464-473 (coordinate of each
@@ -234,12 +264,13 @@ build_tiles(Geom g, const float* __restrict__ positions, const float* __restrict
     u16* lidx_s = reinterpret_cast<u16*>(smem_raw + sizeof(Key<KW>) * SPLATS + sizeof(int) * LS);
     __shared__ int nloc_s, base_s;
 
-    const int tid = threadIdx.x, tile = blockIdx.x;
+    const TilePos tpos = this_tile(g);
+    const int tid = threadIdx.x, tile = tpos.tile;
     for (int i = tid; i < LS; i += TP) hslots[i] = -1;
     if (tid == 0) nloc_s = 0;
 
     int item, pix, po, py, px;
-    const bool valid = tile_point(g, tile, tid, item, pix, po, py, px);
+    const bool valid = tile_point(g, tpos, tid, item, pix, po, py, px);
     if (valid) {
         float f[PD];
         float w[PD + 1];
@@ -609,9 +640,9 @@ __device__ __forceinline__ void fence_async_proxy() {
 
 // First point and number of valid points of tile row `ly` (the run of points that is contiguous in
 // memory); returns false if the row lies outside the item.
-__device__ __forceinline__ bool tile_row(const Geom& g, int tile, int ly, int& first_row, int& count) {
+__device__ __forceinline__ bool tile_row(const Geom& g, const TilePos& tpos, int ly, int& first_row, int& count) {
     int item, pix;
-    if (!tile_point(g, tile, ly * g.TX, item, pix)) return false;
+    if (!tile_point(g, tpos, ly * g.TX, item, pix)) return false;
     const int x0 = pix % g.W;
     first_row = item * g.n + pix;
     count = min(g.TX, g.W - x0);
@@ -735,12 +766,13 @@ splat_tiles_fast(Geom g, const float* __restrict__ input, Header* hdr, const int
     __shared__ int wsum_s[32];
     __shared__ __align__(8) u64 bar;
     if (call_failed(hdr)) return;
-    const int tid = threadIdx.x, tile = blockIdx.x;
+    const TilePos tpos = this_tile(g);
+    const int tid = threadIdx.x, tile = tpos.tile;
     const int2 info = tile_info[tile];
     const int base = info.x, nloc = info.y;
 
     int item, pix;
-    const bool valid = tile_point(g, tile, tid, item, pix);
+    const bool valid = tile_point(g, tpos, tid, item, pix);
     prow_s[tid] = valid ? item * g.n + pix : -1;
     for (int i = tid; i < nloc; i += TP) {
         cur_s[i] = 0;
@@ -755,7 +787,7 @@ splat_tiles_fast(Geom g, const float* __restrict__ input, Header* hdr, const int
         if (tid == 0) mbar_expect_tx(&bar, (unsigned)nvalid * C * 4u);
         if (tid < g.TY) {
             int first, count;
-            if (tile_row(g, tile, tid, first, count))
+            if (tile_row(g, tpos, tid, first, count))
                 bulk_load(in_s + (size_t)tid * g.TX * C, input + (size_t)first * C, (unsigned)count * C * 4u, &bar);
         }
     } else {
@@ -830,12 +862,13 @@ splat_tiles_group(Geom g, const float* __restrict__ input, Header* hdr, const in
     __shared__ int wsum_s[32];
     __shared__ __align__(8) u64 bar;
     if (call_failed(hdr)) return;
-    const int tid = threadIdx.x, tile = blockIdx.x;
+    const TilePos tpos = this_tile(g);
+    const int tid = threadIdx.x, tile = tpos.tile;
     const int2 info = tile_info[tile];
     const int base = info.x, nloc = info.y;
 
     int item, pix;
-    const bool valid = tile_point(g, tile, tid, item, pix);
+    const bool valid = tile_point(g, tpos, tid, item, pix);
     prow_s[tid] = valid ? item * g.n + pix : -1;
     for (int i = tid; i < nloc; i += TP) cur_s[i] = 0;
     if (bulk_ok && tid == 0) mbar_init(&bar, 1);
@@ -847,7 +880,7 @@ splat_tiles_group(Geom g, const float* __restrict__ input, Header* hdr, const in
         if (tid == 0) mbar_expect_tx(&bar, (unsigned)nvalid * C * 4u);
         if (tid < g.TY) {
             int first, count;
-            if (tile_row(g, tile, tid, first, count))
+            if (tile_row(g, tpos, tid, first, count))
                 bulk_load(in_s + (size_t)tid * g.TX * C, input + (size_t)first * C, (unsigned)count * C * 4u, &bar);
         }
     } else {
@@ -963,12 +996,13 @@ splat_tiles_generic(Geom g, const float* __restrict__ input, Header* hdr, const 
     int* prow_s = off_s + SPLATS;                                           // [TP]
     __shared__ int wsum_s[32];
     if (call_failed(hdr)) return;
-    const int tid = threadIdx.x, tile = blockIdx.x, lane = tid & 31, warp = tid >> 5;
+    const TilePos tpos = this_tile(g);
+    const int tid = threadIdx.x, tile = tpos.tile, lane = tid & 31, warp = tid >> 5;
     const int2 info = tile_info[tile];
     const int base = info.x, nloc = info.y;
 
     int item, pix;
-    const bool valid = tile_point(g, tile, tid, item, pix);
+    const bool valid = tile_point(g, tpos, tid, item, pix);
     prow_s[tid] = valid ? item * g.n + pix : -1;
     for (int i = tid; i < nloc; i += TP) cur_s[i] = 0;
     in_s[tid * VP + C] = 1.f;   // homogeneous channel, then padding
@@ -1061,11 +1095,12 @@ splat_tiles_det(Geom g, const float* __restrict__ input, Header* hdr, const int2
     int* prow_s = cur_s + SPLATS;
     __shared__ int wsum_s[32];
     if (call_failed(hdr)) return;
-    const int tid = threadIdx.x, tile = blockIdx.x, lane = tid & 31, warp = tid >> 5;
+    const TilePos tpos = this_tile(g);
+    const int tid = threadIdx.x, tile = tpos.tile, lane = tid & 31, warp = tid >> 5;
     const int2 info = tile_info[tile];
     const int base = info.x, nloc = info.y;
     int item, pix;
-    const bool valid = tile_point(g, tile, tid, item, pix);
+    const bool valid = tile_point(g, tpos, tid, item, pix);
     prow_s[tid] = valid ? item * g.n + pix : -1;
     for (int i = tid; i < nloc; i += TP) cur_s[i] = 0;
     const int nvalid = __syncthreads_count(valid);
@@ -1209,7 +1244,8 @@ slice_tiles_fast(Geom g, float* __restrict__ output, const Header* hdr, const in
     float* out_s = reinterpret_cast<float*>(smem_raw);                                          // [TP][C], later
     int* prow_s = reinterpret_cast<int*>(smem_raw + SliceFast<PD, VD>::region(rows_cap));       // [TP]
     if (call_failed(hdr)) return;
-    const int tid = threadIdx.x, tile = blockIdx.x;
+    const TilePos tpos = this_tile(g);
+    const int tid = threadIdx.x, tile = tpos.tile;
     const int2 info = tile_info[tile];
     const int base = info.x, cnt = info.y;
     const int nrows = min(cnt, rows_cap);
@@ -1219,7 +1255,7 @@ slice_tiles_fast(Geom g, float* __restrict__ output, const Header* hdr, const in
         cp_async16(rows_s + lrow * RS + 4 * q, v4 + (size_t)list_ref[base + lrow] * QPR + q);
     }
     int item, pix;
-    const bool valid = tile_point(g, tile, tid, item, pix);
+    const bool valid = tile_point(g, tpos, tid, item, pix);
     prow_s[tid] = valid ? item * g.n + pix : -1;
     float w[PD + 1];
     int l[PD + 1];
@@ -1276,7 +1312,7 @@ slice_tiles_fast(Geom g, float* __restrict__ output, const Header* hdr, const in
         __syncthreads();
         if (tid < g.TY) {
             int first, count;
-            if (tile_row(g, tile, tid, first, count))
+            if (tile_row(g, this_tile(g), tid, first, count))   // recomputed: keeps registers free above
                 bulk_store(output + (size_t)first * C, out_s + (size_t)tid * g.TX * C, (unsigned)count * C * 4u);
             bulk_store_finish();
         }
@@ -1307,7 +1343,8 @@ slice_tiles_generic(Geom g, float* __restrict__ output, const Header* hdr, const
     float* prec_s = reinterpret_cast<float*>(rows4 + (size_t)rows_cap * QPR);       // [TP][PW]
     int* prow_s = reinterpret_cast<int*>(prec_s + (size_t)TP * PW);                 // [TP]
     if (call_failed(hdr)) return;
-    const int tid = threadIdx.x, tile = blockIdx.x, lane = tid & 31, warp = tid >> 5;
+    const TilePos tpos = this_tile(g);
+    const int tid = threadIdx.x, tile = tpos.tile, lane = tid & 31, warp = tid >> 5;
     const int2 info = tile_info[tile];
     const int base = info.x, cnt = info.y;
     const int nrows = min(cnt, rows_cap);
@@ -1317,7 +1354,7 @@ slice_tiles_generic(Geom g, float* __restrict__ output, const Header* hdr, const
         cp_async16(rows4 + i, v4 + (size_t)list_ref[base + lrow] * QPR + q);
     }
     int item, pix;
-    const bool valid = tile_point(g, tile, tid, item, pix);
+    const bool valid = tile_point(g, tpos, tid, item, pix);
     prow_s[tid] = valid ? item * g.n + pix : -1;
     float w[PD + 1];
     int l[PD + 1];
@@ -1413,9 +1450,10 @@ export_points(Geom g, const Header* hdr, const int2* __restrict__ tile_info, con
               int32_t* __restrict__ pixel_vertex, float* __restrict__ pixel_weight) {
     constexpr int TP = Cfg<PD>::TP, SPLATS = Cfg<PD>::SPLATS;
     if (hdr->status != 0) return;
-    const int tid = threadIdx.x, tile = blockIdx.x;
+    const TilePos tpos = this_tile(g);
+    const int tid = threadIdx.x, tile = tpos.tile;
     int item, pix;
-    if (!tile_point(g, tile, tid, item, pix)) return;
+    if (!tile_point(g, tpos, tid, item, pix)) return;
     const int base = tile_info[tile].x;
     const u16* rec_tile = rec + (size_t)tile * SPLATS;
     const float* recw_tile = rec_w + (size_t)tile * SPLATS;
@@ -1516,6 +1554,9 @@ static int make_geom(Geom& g, int batch, int n, int pd, int n_sdims, const int* 
     if (total > 0x7FFFFFFFll) return PL_INVALID_ARGUMENT;
     g.tiles_per_item = (int)per_item;
     g.num_tiles = (int)total;
+    g.tx_log2 = 0;
+    while ((1 << g.tx_log2) < g.TX) g.tx_log2++;
+    g.grid3 = (g.tiles_y <= 65535 && (long long)batch * g.outer <= 65535) ? 1 : 0;
     scale_factors(pd, g.scale);
     return PL_OK;
 }
@@ -1545,6 +1586,12 @@ static int make_layout(Layout& L, const Geom& g, int pd, int vd, int64_t max_ent
     L.v64 = off;       off += align_up(sizeof(long long) * (size_t)padded_vd(vd) * E);   // deterministic mode sums
     L.total = off;
     return PL_OK;
+}
+
+// Launch grid of the tile kernels (see this_tile).
+static dim3 tile_grid(const Geom& g) {
+    if (g.grid3) return dim3((unsigned)g.tiles_x, (unsigned)g.tiles_y, (unsigned)(g.batch * g.outer));
+    return dim3((unsigned)g.num_tiles, 1, 1);
 }
 
 static int g_num_sms = 0;
@@ -1587,18 +1634,18 @@ static int launch_splat(const Geom& g, const float* input, Header* hdr, const in
         // four lanes per window measured best for 24-float rows (two and eight lanes are within 10 %)
         PL_CUDA(cudaFuncSetAttribute(splat_tiles_group<PD, VD, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      (int)smem));
-        splat_tiles_group<PD, VD, 4><<<g.num_tiles, Cfg<PD>::TP, smem, st>>>(
+        splat_tiles_group<PD, VD, 4><<<tile_grid(g), Cfg<PD>::TP, smem, st>>>(
             g, input, hdr, tile_info, rec, rec_w, list_ref, v0, bulk_rows_ok(g, input, VD - 1) ? 1 : 0);
     } else if constexpr (VD > 0) {
         const size_t smem = SplatFast<PD, VD>::BYTES;
         PL_CUDA(cudaFuncSetAttribute(splat_tiles_fast<PD, VD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        splat_tiles_fast<PD, VD><<<g.num_tiles, Cfg<PD>::TP, smem, st>>>(
+        splat_tiles_fast<PD, VD><<<tile_grid(g), Cfg<PD>::TP, smem, st>>>(
             g, input, hdr, tile_info, rec, rec_w, list_ref, v0, bulk_rows_ok(g, input, VD - 1) ? 1 : 0);
     } else {
         const size_t smem = SplatGeneric<PD>::bytes(vd);
         if (smem > 200 * 1024) return PL_UNSUPPORTED_DIMS;
         PL_CUDA(cudaFuncSetAttribute(splat_tiles_generic<PD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        splat_tiles_generic<PD><<<g.num_tiles, Cfg<PD>::TP, smem, st>>>(g, input, hdr, tile_info, rec, rec_w,
+        splat_tiles_generic<PD><<<tile_grid(g), Cfg<PD>::TP, smem, st>>>(g, input, hdr, tile_info, rec, rec_w,
                                                                         list_ref, v0, vd);
     }
     return PL_OK;
@@ -1612,7 +1659,7 @@ static int launch_slice(const Geom& g, float* output, const Header* hdr, const i
         if (rows_cap > Cfg<PD>::SPLATS) rows_cap = Cfg<PD>::SPLATS;
         const size_t smem = SliceFast<PD, VD>::bytes(rows_cap);
         PL_CUDA(cudaFuncSetAttribute(slice_tiles_fast<PD, VD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        slice_tiles_fast<PD, VD><<<g.num_tiles, Cfg<PD>::TP, smem, st>>>(
+        slice_tiles_fast<PD, VD><<<tile_grid(g), Cfg<PD>::TP, smem, st>>>(
             g, output, hdr, tile_info, rec, rec_w, list_ref, vsrc, rows_cap, bulk_rows_ok(g, output, VD - 1) ? 1 : 0);
     } else {
         const int rows_cap = rows_cap_for(PD, vd);
@@ -1620,7 +1667,7 @@ static int launch_slice(const Geom& g, float* output, const Header* hdr, const i
         const size_t smem = sizeof(float) * (size_t)rows_cap * padded_vd(vd) + fixed;
         if (smem > 200 * 1024) return PL_UNSUPPORTED_DIMS;
         PL_CUDA(cudaFuncSetAttribute(slice_tiles_generic<PD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        slice_tiles_generic<PD><<<g.num_tiles, Cfg<PD>::TP, smem, st>>>(g, output, hdr, tile_info, rec, rec_w,
+        slice_tiles_generic<PD><<<tile_grid(g), Cfg<PD>::TP, smem, st>>>(g, output, hdr, tile_info, rec, rec_w,
                                                                         list_ref, vsrc, vd, rows_cap);
     }
     return PL_OK;
@@ -1670,7 +1717,7 @@ static int run_filter(const Geom& g, float* output, const float* input, const fl
     while ((1ull << table_log2) < L.table_slots) table_log2++;
 
     if (phases & PH_BUILD) {
-        build_tiles<PD><<<g.num_tiles, TP, Cfg<PD>::BUILD_SMEM, st>>>(
+        build_tiles<PD><<<tile_grid(g), TP, Cfg<PD>::BUILD_SMEM, st>>>(
             g, positions, reference, hdr, tile_info, rec, rec_w, list_keys, (u32)L.max_entries);
         if (ev) PL_CUDA(cudaEventRecord(ev[1], st));
         clear_table<<<wide, 256, 0, st>>>(hdr, table, (u32)table_log2);
@@ -1694,7 +1741,7 @@ static int run_filter(const Geom& g, float* output, const float* input, const fl
         if (smem > 200 * 1024) return PL_UNSUPPORTED_DIMS;
         PL_CUDA(cudaFuncSetAttribute(splat_tiles_det<PD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         absmax_kernel<<<wide, 256, 0, st>>>(input, (u64)g.batch * g.n * (vd - 1), hdr);
-        splat_tiles_det<PD><<<g.num_tiles, TP, smem, st>>>(g, input, hdr, tile_info, rec, rec_w, list_ref, v64, vd);
+        splat_tiles_det<PD><<<tile_grid(g), TP, smem, st>>>(g, input, hdr, tile_info, rec, rec_w, list_ref, v64, vd);
         convert_fixed<<<wide, 256, 0, st>>>(hdr, v64, v0, padded_vd(vd));
     } else {
         rc = PL_DISPATCH_VD(launch_splat, PD, vd, g, input, hdr, tile_info, rec, rec_w, list_ref, v0, vd, st);
@@ -1728,7 +1775,7 @@ static int run_export(const Geom& g, const float* positions, const float* refere
     const Header* hdr = reinterpret_cast<const Header*>(ws);
     if (g.num_tiles == 0) return PL_OK;
     if (pixel_vertex || pixel_weight)
-        export_points<PD><<<g.num_tiles, TP, 0, st>>>(
+        export_points<PD><<<tile_grid(g), TP, 0, st>>>(
             g, hdr, reinterpret_cast<const int2*>(ws + L.tile_info), reinterpret_cast<const u16*>(ws + L.rec),
             reinterpret_cast<const float*>(ws + L.rec_w), reinterpret_cast<const u32*>(ws + L.list_ref),
             pixel_vertex, pixel_weight);
