@@ -243,8 +243,10 @@ def run_reference(args, rank, world):
         "unit": "Mpixels/s", "n_gpus": args.gpus, "steps": len(times), "warmup": args.warmup,
         "ms_per_step": secs * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic",
-        "config": {"workload": w.name, "batch": w.batch, "pixels_per_item": w.pixels_per_item,
-                   "pd": w.pd, "vd": w.vd, "direction": "fwd+bwd" if w.backward else "fwd"},
+        "config": {"workload": w.name, "batch_per_gpu": w.batch, "global_batch": w.batch * max(1, world),
+                   "pixels_per_item": w.pixels_per_item, "pd": w.pd, "vd": w.vd,
+                   "direction": "fwd+bwd" if w.backward else "fwd",
+                   "parallelism": "batch-sharded x%d" % max(1, world), "mode": "cpu reference"},
         "cpu_baseline": {"value": value, "unit": "Mpixels/s", "cores": info["cores"],
                          "kind": info["kind"], "sample": info["sample"]},
         "e2e": {"value": value, "unit": "Mpixels/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
