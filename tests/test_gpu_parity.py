@@ -281,3 +281,17 @@ def test_autograd_with_lattice_reuse(gpu, oracle):
     gpu.assert_outputs_close(out.detach().cpu().numpy(), oracle.lattice_filter(inp_n, ref_n, True, 5.0, 0.2), "fwd")
     gpu.assert_outputs_close(inp.grad.cpu().numpy(), oracle.lattice_filter(grad_n, ref_n, True, 5.0, 0.2, 1.0, True),
                              "bwd")
+
+
+def test_cuda_graph_replay_matches_plain_call(gpu, oracle):
+    import torch
+    import permutohedral_lattice_b200 as plb
+    rng = np.random.default_rng(51)
+    ref_n = rng.random((2, 40, 36, 3), dtype=np.float32)
+    gf = plb.GraphedLatticeFilter((2, 40, 36, 5), (2, 40, 36, 3), True, 6.0, 0.2)
+    gf.reference.copy_(torch.from_numpy(ref_n))
+    for _ in range(3):      # replays with new contents of the static tensors
+        x_n = rng.standard_normal((2, 40, 36, 5)).astype(np.float32)
+        gf.input.copy_(torch.from_numpy(x_n))
+        got = gf.replay().cpu().numpy()
+        gpu.assert_outputs_close(got, oracle.lattice_filter(x_n, ref_n, True, 6.0, 0.2), "graph replay")
