@@ -14,7 +14,9 @@ ROOT = os.path.dirname(PKG)
 CSRC = os.path.join(PKG, "csrc")
 LIB = os.path.join(PKG, "libpl_lattice.so")
 SOURCES = [os.path.join(CSRC, "pl_lattice.cu")]
-HEADERS = [os.path.join(CSRC, "simplex.cuh"), os.path.join(ROOT, "include", "pl_lattice.h")]
+HEADERS = [os.path.join(CSRC, h) for h in ("simplex.cuh", "common.cuh", "lattice_build.cuh", "splat.cuh",
+                                             "blur_slice.cuh", "export.cuh")] + [
+    os.path.join(ROOT, "include", "pl_lattice.h")]
 
 
 def nvcc_path():

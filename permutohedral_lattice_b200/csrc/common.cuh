@@ -1,0 +1,331 @@
+// Shared definitions of the lattice kernels: geometry of a call, workspace header and layout, packed
+// vertex keys and their hashes, tile addressing, vector reductions and asynchronous-copy helpers.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include "../../include/pl_lattice.h"
+#include "simplex.cuh"
+
+namespace pl {
+
+typedef unsigned long long u64;
+typedef unsigned int u32;
+typedef unsigned short u16;
+
+constexpr u64 EMPTY_SLOT = ~0ull;
+constexpr int MAX_SDIMS = 8;
+constexpr int MAX_PD = 16;
+
+// ---------------------------------------------------------------------------------------------
+// Geometry of a call: how points map to tiles and how features are produced.
+// ---------------------------------------------------------------------------------------------
+struct Geom {
+    int batch, n;           // items, points per item
+    int W, H, outer;        // n = outer * H * W (W fastest)
+    int TX, TY;             // tile = TY rows of TX points, TX * TY = TP
+    int tiles_x, tiles_y, tiles_per_item, num_tiles;
+    int tx_log2;            // TX is a power of two
+    int grid3;              // 1: tile kernels run on a (tiles_x, tiles_y, batch * outer) grid
+    int n_sdims, R;         // op path: spatial dims and reference channels (pd = n_sdims + R)
+    int sdims[MAX_SDIMS];
+    float spatial_std, feature_std;
+    float spatial_rcp, feature_rcp;   // correctly rounded reciprocals of the two (host-computed)
+    int rcp_div;            // 1: divide through the reciprocals (exact for these operands), 0: IEEE divide
+    int from_positions;     // 1: features are read from a positions array
+    float scale[MAX_PD];    // host-computed scale factors (double arithmetic rounded to float)
+};
+
+struct Header {   // first 256 bytes of the workspace
+    u32 num_entries;
+    u32 num_vertices;
+    u32 status;
+    u32 table_log2;
+    u32 absmax_bits;   // deterministic mode: bit pattern of max |input| (non-negative floats order as integers)
+    u32 pad[59];
+};
+
+struct Layout {   // byte offsets into the workspace
+    size_t tile_info, rec, rec_w, list_keys, list_ref, vid, vowner, table, nbr, v0, v1, v64, total;
+    u64 max_entries;   // capacity of entry- and vertex-indexed arrays
+    u64 table_slots;   // allocated slots (power of two)
+};
+
+template <int KW>
+struct alignas((KW % 2 == 0) ? 16 : 8) Key {
+    u64 w[KW];
+};
+
+template <int PD>
+struct Cfg {
+    static constexpr int KW = (PD + 1 + 3) / 4;          // 16-bit fields: PD coordinates + item
+    static constexpr int TP = (PD <= 8) ? 256 : 128;     // points per tile = threads per CTA
+    static constexpr int SPLATS = TP * (PD + 1);
+    static constexpr int LS = (5 * SPLATS <= 4 * 1024)   ? 1024
+                              : (5 * SPLATS <= 4 * 2048) ? 2048
+                              : (5 * SPLATS <= 4 * 4096) ? 4096
+                              : (5 * SPLATS <= 4 * 8192) ? 8192
+                                                         : 16384;   // shared hash slots (>= 1.25 * SPLATS)
+    static constexpr size_t BUILD_SMEM = sizeof(Key<KW>) * SPLATS + sizeof(int) * LS + sizeof(u16) * SPLATS;
+};
+
+template <int KW>
+__device__ __forceinline__ u64 hash_key(const Key<KW>& k) {
+    u64 h = 0x9E3779B97F4A7C15ull;
+#pragma unroll
+    for (int j = 0; j < KW; j++) {
+        h ^= k.w[j];
+        h *= 0xFF51AFD7ED558CCDull;
+        h ^= h >> 32;
+    }
+    h *= 0xC4CEB9FE1A85EC53ull;
+    h ^= h >> 29;
+    return h;
+}
+
+template <int KW>
+__device__ __forceinline__ bool key_equal(const Key<KW>& a, const Key<KW>& b) {
+    bool eq = true;
+#pragma unroll
+    for (int j = 0; j < KW; j++) eq = eq && (a.w[j] == b.w[j]);
+    return eq;
+}
+
+// 16-bit field f of a key.  Fields 0..PD-1: lattice coordinates biased by 0x8000 (so that adding small
+// offsets to a packed word never carries between fields); field PD: batch item.
+template <int KW>
+__device__ __forceinline__ void key_set(Key<KW>& k, int f, u16 v) {
+    k.w[f >> 2] |= (u64)v << (16 * (f & 3));
+}
+template <int KW>
+__device__ __forceinline__ u16 key_get(const Key<KW>& k, int f) {
+    return (u16)(k.w[f >> 2] >> (16 * (f & 3)));
+}
+
+// 0x0001 in every coordinate field of key word j.
+template <int PD>
+__device__ __forceinline__ constexpr u64 coord_ones(int j) {
+    u64 m = 0;
+    for (int f = 4 * j; f < 4 * j + 4; f++)
+        if (f < PD) m |= 1ull << (16 * (f & 3));
+    return m;
+}
+
+// Cheap 32-bit hash for the per-tile shared-memory table (placement only).
+template <int KW>
+__device__ __forceinline__ u32 tile_hash(const Key<KW>& k) {
+    u32 h = 0;
+#pragma unroll
+    for (int j = 0; j < KW; j++) {
+        h = (h ^ (u32)k.w[j]) * 0x9E3779B1u;
+        h = (h ^ (u32)(k.w[j] >> 32)) * 0x85EBCA77u;
+    }
+    h ^= h >> 15;
+    h *= 0x2C1B3C6Du;
+    return h ^ (h >> 13);
+}
+
+// Tile of this CTA.  Tile kernels run on a 3-D grid (tile column, tile row, item * outer + outer index)
+// whenever that fits the grid limits, so no thread divides to find its tile; else on a 1-D grid.
+struct TilePos {
+    int tile, item, o, ty, tx;
+};
+__device__ __forceinline__ TilePos this_tile(const Geom& g) {
+    TilePos t;
+    if (g.grid3) {
+        t.tx = blockIdx.x;
+        t.ty = blockIdx.y;
+        const int z = blockIdx.z;
+        if (g.outer == 1) {
+            t.item = z;
+            t.o = 0;
+        } else {
+            t.item = z / g.outer;
+            t.o = z - t.item * g.outer;
+        }
+        t.tile = (z * g.tiles_y + t.ty) * g.tiles_x + t.tx;
+    } else {
+        t.tile = blockIdx.x;
+        t.item = t.tile / g.tiles_per_item;
+        int r = t.tile - t.item * g.tiles_per_item;
+        const int per_plane = g.tiles_x * g.tiles_y;
+        t.o = r / per_plane;
+        r -= t.o * per_plane;
+        t.ty = r / g.tiles_x;
+        t.tx = r - t.ty * g.tiles_x;
+    }
+    return t;
+}
+
+// Point handled by thread `tid` of the tile: item, point index inside the item, validity; the long
+// form also gives the point's position (outer index, row, column).
+__device__ __forceinline__ bool tile_point(const Geom& g, const TilePos& t, int tid, int& item, int& pix, int& o,
+                                           int& y, int& x) {
+    item = t.item;
+    o = t.o;
+    const int ly = tid >> g.tx_log2, lx = tid & (g.TX - 1);
+    y = t.ty * g.TY + ly;
+    x = t.tx * g.TX + lx;
+    pix = (o * g.H + y) * g.W + x;
+    return (y < g.H) && (x < g.W);
+}
+__device__ __forceinline__ bool tile_point(const Geom& g, const TilePos& t, int tid, int& item, int& pix) {
+    int o, y, x;
+    return tile_point(g, t, tid, item, pix, o, y, x);
+}
+
+// Feature vector of a point.  Op path: src/PermutohedralLatticeCPU.h:464-473 (coordinate of each
+// spatial dimension as float divided by spatial_std, reference channel divided by feature_std; IEEE
+// divisions, not reciprocal multiplies).  The last two spatial coordinates are the point's row and
+// column in its tile grid; only deeper dimensions need the reference's divide-and-modulo.
+// Positions path: a row of the positions array.
+template <int PD>
+__device__ __forceinline__ void load_features(const Geom& g, const float* __restrict__ positions,
+                                              const float* __restrict__ reference, int item, int pix, int o,
+                                              int y, int x, float* f) {
+    if (g.from_positions) {
+        const float* p = positions + ((size_t)item * g.n + pix) * PD;
+#pragma unroll
+        for (int i = 0; i < PD; i++) f[i] = __ldg(p + i);
+    } else {
+        const float* ref = reference + ((size_t)item * g.n + pix) * g.R;
+        int rest = o;
+#pragma unroll
+        for (int i = PD - 1; i >= 0; i--) {
+            if (i >= g.n_sdims) {
+                const float a = __ldg(ref + (i - g.n_sdims));
+                f[i] = g.rcp_div ? div_by_rcp(a, g.feature_std, g.feature_rcp) : PL_FDIV(a, g.feature_std);
+            } else {
+                int c;
+                if (i == g.n_sdims - 1 && g.n_sdims >= 2) {
+                    c = x;
+                } else if (i == g.n_sdims - 2) {
+                    c = y;
+                } else if (g.n_sdims == 1) {
+                    c = x;
+                } else {
+                    c = rest % g.sdims[i];
+                    rest /= g.sdims[i];
+                }
+                const float a = small_int_to_float(c);
+                f[i] = g.rcp_div ? div_by_rcp(a, g.spatial_std, g.spatial_rcp) : PL_FDIV(a, g.spatial_std);
+            }
+        }
+    }
+}
+
+// Floats of a vertex row: vd padded to a multiple of 4 (16-byte rows).
+__host__ __device__ __forceinline__ int padded_vd(int vd) { return (vd + 3) & ~3; }
+
+// Status word of the call, read once per CTA so that every thread takes the same branch even while
+// other CTAs of the same launch are setting error bits.
+__device__ __forceinline__ bool call_failed(const Header* hdr) {
+    __shared__ u32 status_s;
+    if (threadIdx.x == 0) status_s = hdr->status;
+    __syncthreads();
+    return status_s != 0;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Value rows.  A vertex row holds vd floats padded to VP = a multiple of 4, so that rows are 16-byte
+// aligned: every row access below is a float4, and a row of 22 channels covers exactly three
+// 32-byte sectors.  Pad channels stay zero through splat and blur and are never sliced.
+// ---------------------------------------------------------------------------------------------
+// Vector reduction into global memory (sm_90+): one L2 operation per 16 bytes.
+__device__ __forceinline__ void red_add_v4(float* addr, float4 v) {
+    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(v.x), "f"(v.y), "f"(v.z),
+                 "f"(v.w)
+                 : "memory");
+}
+__device__ __forceinline__ void red_add_v2(float* addr, float a, float b) {
+    asm volatile("red.global.add.v2.f32 [%0], {%1, %2};" ::"l"(addr), "f"(a), "f"(b) : "memory");
+}
+__device__ __forceinline__ void red_add_f32(float* addr, float a) {
+    asm volatile("red.global.add.f32 [%0], %1;" ::"l"(addr), "f"(a) : "memory");
+}
+__device__ __forceinline__ void cp_async4(void* smem, const void* gmem) {
+    const unsigned sa = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(sa), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
+    const unsigned sa = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(sa), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() {
+    asm volatile("cp.async.commit_group;\n\tcp.async.wait_group 0;" ::: "memory");
+}
+
+// How a warp's lanes are spread over value rows: GS lanes (one float4 each) per row, PPW rows per
+// warp instruction.  Rows wider than 32 quads are walked in chunks of 32 quads.
+struct LaneMap {
+    int gs, ppw, g, q0;
+    bool active;
+    __device__ __forceinline__ LaneMap(int qpr, int lane) {
+        gs = qpr < 32 ? qpr : 32;
+        ppw = 32 / gs;
+        g = lane / gs;
+        q0 = lane - g * gs;
+        active = g < ppw;
+    }
+};
+
+// ---------------------------------------------------------------------------------------------
+// Bulk asynchronous copies (TMA engine, untiled form) with an mbarrier; every wait is bounded.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ void mbar_init(u64* bar, unsigned count) {
+    const unsigned a = (unsigned)__cvta_generic_to_shared(bar);
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(a), "r"(count) : "memory");
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(u64* bar, unsigned bytes) {
+    const unsigned a = (unsigned)__cvta_generic_to_shared(bar);
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(a), "r"(bytes) : "memory");
+}
+// global -> shared, 16-byte aligned addresses, size a multiple of 16 bytes
+__device__ __forceinline__ void bulk_load(void* smem_dst, const void* gmem_src, unsigned bytes, u64* bar) {
+    const unsigned d = (unsigned)__cvta_generic_to_shared(smem_dst);
+    const unsigned a = (unsigned)__cvta_generic_to_shared(bar);
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(d),
+                 "l"(gmem_src), "r"(bytes), "r"(a)
+                 : "memory");
+}
+// Waits for phase `parity` of the barrier; gives up (returns false) after a bounded number of polls.
+__device__ __forceinline__ bool mbar_wait(u64* bar, unsigned parity) {
+    const unsigned a = (unsigned)__cvta_generic_to_shared(bar);
+    for (int it = 0; it < (1 << 20); it++) {
+        unsigned done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(done)
+            : "r"(a), "r"(parity)
+            : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+// shared -> global
+__device__ __forceinline__ void bulk_store(void* gmem_dst, const void* smem_src, unsigned bytes) {
+    const unsigned sa = (unsigned)__cvta_generic_to_shared(smem_src);
+    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gmem_dst), "r"(sa), "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ void bulk_store_finish() {
+    asm volatile("cp.async.bulk.commit_group;\n\tcp.async.bulk.wait_group.read 0;" ::: "memory");
+}
+__device__ __forceinline__ void fence_async_proxy() {
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
+// First point and number of valid points of tile row `ly` (the run of points that is contiguous in
+// memory); returns false if the row lies outside the item.
+__device__ __forceinline__ bool tile_row(const Geom& g, const TilePos& tpos, int ly, int& first_row, int& count) {
+    int item, pix;
+    if (!tile_point(g, tpos, ly * g.TX, item, pix)) return false;
+    const int x0 = pix % g.W;
+    first_row = item * g.n + pix;
+    count = min(g.TX, g.W - x0);
+    return true;
+}
+
+}  // namespace pl

@@ -1,0 +1,305 @@
+// Lattice construction: per-tile key generation and de-duplication (build_tiles), the global hash
+// table (clear_table, insert_entries) and the vertex / neighbour tables (link_vertices, link_neighbours).
+#pragma once
+#include "common.cuh"
+
+namespace pl {
+
+// ---------------------------------------------------------------------------------------------
+// build_tiles
+// ---------------------------------------------------------------------------------------------
+template <int PD>
+__global__ void __launch_bounds__(Cfg<PD>::TP)
+build_tiles(Geom g, const float* __restrict__ positions, const float* __restrict__ reference,
+            Header* hdr, int2* __restrict__ tile_info, u16* __restrict__ rec, float* __restrict__ rec_w,
+            Key<Cfg<PD>::KW>* __restrict__ list_keys, u32 max_entries) {
+    constexpr int KW = Cfg<PD>::KW, TP = Cfg<PD>::TP, SPLATS = Cfg<PD>::SPLATS, LS = Cfg<PD>::LS;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    Key<KW>* keys_s = reinterpret_cast<Key<KW>*>(smem_raw);
+    int* hslots = reinterpret_cast<int*>(smem_raw + sizeof(Key<KW>) * SPLATS);
+    u16* lidx_s = reinterpret_cast<u16*>(smem_raw + sizeof(Key<KW>) * SPLATS + sizeof(int) * LS);
+    __shared__ int nloc_s, base_s;
+
+    const TilePos tpos = this_tile(g);
+    const int tid = threadIdx.x, tile = tpos.tile;
+    for (int i = tid; i < LS; i += TP) hslots[i] = -1;
+    if (tid == 0) nloc_s = 0;
+
+    int item, pix, po, py, px;
+    const bool valid = tile_point(g, tpos, tid, item, pix, po, py, px);
+    if (valid) {
+        float f[PD];
+        float w[PD + 1];
+        load_features<PD>(g, positions, reference, item, pix, po, py, px, f);
+        Simplex<PD> s;
+        find_simplex<PD>(f, g.scale, s);
+        barycentric<PD>(s, w);
+        // the weights are final: store them now so the writes overlap the de-duplication below
+        float* recw_tile = rec_w + (size_t)tile * SPLATS;
+#pragma unroll
+        for (int r = 0; r <= PD; r++) recw_tile[r * TP + tid] = w[r];
+        // Remainder-r vertex: coordinate i = rem0_i + r - (PD+1) [rank_i > PD - r]
+        // (src/PermutohedralLatticeCPU.h:297-304).  In packed form: start from the remainder-0 key,
+        // then per step add one to every coordinate field and take PD+1 off the one coordinate whose
+        // rank is PD - r + 1.
+        Key<KW> k;
+#pragma unroll
+        for (int j = 0; j < KW; j++) k.w[j] = 0;
+#pragma unroll
+        for (int i = 0; i < PD; i++) key_set<KW>(k, i, (u16)(s.rem0[i] + 0x8000));
+        key_set<KW>(k, PD, (u16)item);
+        keys_s[tid] = k;
+#pragma unroll
+        for (int r = 1; r <= PD; r++) {
+#pragma unroll
+            for (int i = 0; i < PD; i++)
+                k.w[i >> 2] -= (s.rank[i] == PD - r + 1) ? ((u64)(PD + 1) << (16 * (i & 3))) : 0ull;
+#pragma unroll
+            for (int j = 0; j < KW; j++) k.w[j] += coord_ones<PD>(j);
+            keys_s[r * TP + tid] = k;
+        }
+    }
+    __syncthreads();
+
+    // de-duplicate: the first splat to claim a slot for a key represents it.  The first probes of all
+    // PD+1 keys are issued together (independent shared-memory accesses); most keys resolve there,
+    // the rest walk on one at a time.
+    int rep[PD + 1];
+    {
+        u32 slot[PD + 1];
+        int cand[PD + 1];
+#pragma unroll
+        for (int r = 0; r <= PD; r++) {
+            rep[r] = -1;
+            slot[r] = 0;
+            cand[r] = -1;
+            if (valid) {
+                slot[r] = tile_hash<KW>(keys_s[r * TP + tid]) & (LS - 1);
+                cand[r] = hslots[slot[r]];
+            }
+        }
+#pragma unroll
+        for (int r = 0; r <= PD; r++) {
+            if (valid && cand[r] < 0) {
+                cand[r] = atomicCAS(&hslots[slot[r]], -1, r * TP + tid);
+                if (cand[r] < 0) rep[r] = r * TP + tid;
+            }
+        }
+#pragma unroll
+        for (int r = 0; r <= PD; r++) {
+            if (valid && rep[r] < 0 && key_equal<KW>(keys_s[cand[r]], keys_s[r * TP + tid])) rep[r] = cand[r];
+        }
+#pragma unroll
+        for (int r = 0; r <= PD; r++) {
+            if (valid && rep[r] < 0) {
+                const int me = r * TP + tid;
+                const Key<KW> k = keys_s[me];
+                u32 s = (slot[r] + 1) & (LS - 1);
+                int found = -1;
+                for (int it = 0; it < LS; it++) {
+                    int o = hslots[s];
+                    if (o < 0) {
+                        o = atomicCAS(&hslots[s], -1, me);
+                        if (o < 0) { found = me; break; }
+                    }
+                    if (key_equal<KW>(keys_s[o], k)) { found = o; break; }
+                    s = (s + 1) & (LS - 1);
+                }
+                rep[r] = found;
+            }
+        }
+    }
+    __syncthreads();
+    // number the tile's entries: one shared-memory atomic per warp and remainder, not per owner
+#pragma unroll
+    for (int r = 0; r <= PD; r++) {
+        const bool own = valid && rep[r] == r * TP + tid;
+        const unsigned owners = __ballot_sync(0xFFFFFFFFu, own);
+        if (owners) {
+            const int lane = tid & 31, leader = __ffs(owners) - 1;
+            int first = 0;
+            if (lane == leader) first = atomicAdd(&nloc_s, __popc(owners));
+            first = __shfl_sync(0xFFFFFFFFu, first, leader);
+            if (own) lidx_s[r * TP + tid] = (u16)(first + __popc(owners & ((1u << lane) - 1u)));
+        }
+    }
+    __syncthreads();
+    if (tid == 0) {
+        int cnt = nloc_s;
+        u32 base = atomicAdd(&hdr->num_entries, (u32)cnt);
+        if ((u64)base + (u64)cnt > (u64)max_entries) {
+            atomicOr(&hdr->status, 1u << PL_CAPACITY_EXCEEDED);
+            base_s = -1;
+            tile_info[tile] = make_int2(0, 0);
+        } else {
+            base_s = (int)base;
+            tile_info[tile] = make_int2((int)base, cnt);
+        }
+    }
+    __syncthreads();
+    const int base = base_s;
+    u16* rec_tile = rec + (size_t)tile * SPLATS;
+#pragma unroll
+    for (int r = 0; r <= PD; r++) {
+        const int me = r * TP + tid;
+        u16 l = 0;
+        if (valid && rep[r] >= 0) {
+            l = lidx_s[rep[r]];
+            if (rep[r] == me && base >= 0) list_keys[(size_t)base + l] = keys_s[me];
+        }
+        rec_tile[me] = l;
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// clear_table: table capacity = power of two >= 2 * entries (at least 1024), chosen on the device.
+// ---------------------------------------------------------------------------------------------
+__global__ void clear_table(Header* hdr, u64* __restrict__ table, u32 max_log2) {
+    if (hdr->status != 0) return;
+    u32 need = 2u * hdr->num_entries;
+    u32 lg = 10;
+    while (lg < max_log2 && (1ull << lg) < (u64)need) lg++;
+    if (blockIdx.x == 0 && threadIdx.x == 0) hdr->table_log2 = lg;
+    const u64 cap = 1ull << lg;
+    for (u64 i = (u64)blockIdx.x * blockDim.x + threadIdx.x; i < cap; i += (u64)gridDim.x * blockDim.x)
+        table[i] = EMPTY_SLOT;
+}
+
+// ---------------------------------------------------------------------------------------------
+// insert_entries
+// ---------------------------------------------------------------------------------------------
+// Returns the index of the entry owning `k` in the table, or -1 if absent.
+template <int KW>
+__device__ __forceinline__ int table_find(const u64* __restrict__ table, u64 mask,
+                                          const Key<KW>* __restrict__ list_keys, const Key<KW>& k) {
+    const u64 h = hash_key<KW>(k);
+    const u32 tag = (u32)(h >> 32);
+    u64 s = h & mask;
+    for (u64 it = 0; it <= mask; it++) {
+        const u64 cur = table[s];
+        if (cur == EMPTY_SLOT) return -1;
+        if ((u32)(cur >> 32) == tag) {
+            const u32 o = (u32)cur;
+            if (key_equal<KW>(list_keys[o], k)) return (int)o;
+        }
+        s = (s + 1) & mask;
+    }
+    return -1;
+}
+
+template <int KW>
+__global__ void __launch_bounds__(256)
+insert_entries(Header* hdr, u64* __restrict__ table, const Key<KW>* __restrict__ list_keys,
+               u32* __restrict__ list_ref, u32* __restrict__ vid, u32* __restrict__ vowner) {
+    if (call_failed(hdr)) return;
+    const u32 T = hdr->num_entries;
+    const u64 mask = (1ull << hdr->table_log2) - 1;
+    __shared__ u32 warp_cnt[8];
+    __shared__ u32 block_base;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (u32 start = blockIdx.x * 256u; start < T; start += gridDim.x * 256u) {
+        const u32 t = start + threadIdx.x;
+        bool winner = false;
+        if (t < T) {
+            const Key<KW> k = list_keys[t];
+            const u64 h = hash_key<KW>(k);
+            const u32 tag = (u32)(h >> 32);
+            const u64 mine = ((u64)tag << 32) | (u64)t;
+            u64 s = h & mask;
+            u32 owner = 0xFFFFFFFFu;
+            for (u64 it = 0; it <= mask; it++) {
+                u64 cur = table[s];
+                if (cur == EMPTY_SLOT) {
+                    cur = atomicCAS(&table[s], EMPTY_SLOT, mine);
+                    if (cur == EMPTY_SLOT) { owner = t; winner = true; break; }
+                }
+                if ((u32)(cur >> 32) == tag) {
+                    const u32 o = (u32)cur;
+                    if (key_equal<KW>(list_keys[o], k)) { owner = o; break; }
+                }
+                s = (s + 1) & mask;
+            }
+            if (owner == 0xFFFFFFFFu) {
+                atomicOr(&hdr->status, 1u << PL_INTERNAL_ERROR);
+                owner = t;
+            }
+            list_ref[t] = owner;
+        }
+        // vertex indices: one atomic per CTA and chunk
+        const u32 ballot = __ballot_sync(0xFFFFFFFFu, winner);
+        if (lane == 0) warp_cnt[warp] = __popc(ballot);
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            u32 tot = 0;
+#pragma unroll
+            for (int w = 0; w < 8; w++) { u32 c = warp_cnt[w]; warp_cnt[w] = tot; tot += c; }
+            block_base = tot ? atomicAdd(&hdr->num_vertices, tot) : 0u;
+        }
+        __syncthreads();
+        if (winner) {
+            const u32 v = block_base + warp_cnt[warp] + __popc(ballot & ((1u << lane) - 1u));
+            vid[t] = v;
+            vowner[v] = t;
+        }
+        __syncthreads();
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// link_vertices: entry -> vertex, neighbour table preset to "missing", zeroed value rows.
+// link_neighbours: the +-1 neighbours of every vertex along each of the PD+1 lattice axes.
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+link_vertices(Header* hdr, u32* __restrict__ list_ref, const u32* __restrict__ vid, int* __restrict__ nbr,
+              float* __restrict__ v0, long long* __restrict__ v64, u64 max_entries, int pd, int vd) {
+    if (hdr->status != 0) return;
+    const u32 T = hdr->num_entries, M = hdr->num_vertices;
+    const u64 gtid = (u64)blockIdx.x * blockDim.x + threadIdx.x;
+    const u64 gsz = (u64)gridDim.x * blockDim.x;
+    for (u64 t = gtid; t < T; t += gsz) list_ref[t] = vid[list_ref[t]];
+    int2* nb = reinterpret_cast<int2*>(nbr);
+    for (int a = 0; a <= pd; a++)
+        for (u64 v = gtid; v < M; v += gsz) nb[(u64)a * max_entries + v] = make_int2(-1, -1);
+    if (vd == 0) return;   // lattice built ahead of its use: rows are zeroed by each apply
+    const u64 cells = (u64)M * padded_vd(vd);
+    if (v64) {
+        for (u64 e = gtid; e < cells; e += gsz) v64[e] = 0;
+    } else {
+        for (u64 e = gtid; e < cells; e += gsz) v0[e] = 0.f;
+    }
+}
+
+// One table lookup per (vertex v, axis a): the neighbour u whose key is v's key with every stored
+// coordinate +1, except coordinate a which moves by -PD (along axis PD no stored coordinate is
+// special; src/PermutohedralLatticeCPU.h:381-388).  Then u is v's "+" neighbour and v is u's "-"
+// neighbour, so the second lookup of the reference is not needed.
+template <int PD>
+__global__ void __launch_bounds__(256)
+link_neighbours(const Header* hdr, const u64* __restrict__ table,
+                const Key<Cfg<PD>::KW>* __restrict__ list_keys, const u32* __restrict__ vid,
+                const u32* __restrict__ vowner, int* __restrict__ nbr, u64 max_entries) {
+    constexpr int KW = Cfg<PD>::KW;
+    if (hdr->status != 0) return;
+    const u32 M = hdr->num_vertices;
+    const u64 mask = (1ull << hdr->table_log2) - 1;
+    const u64 items = (u64)M * (PD + 1);
+    for (u64 e = (u64)blockIdx.x * blockDim.x + threadIdx.x; e < items; e += (u64)gridDim.x * blockDim.x) {
+        const u32 v = (u32)(e / (PD + 1));
+        const int a = (int)(e - (u64)v * (PD + 1));
+        const Key<KW> k = list_keys[vowner[v]];
+        Key<KW> nk;
+#pragma unroll
+        for (int j = 0; j < KW; j++) nk.w[j] = 0;
+#pragma unroll
+        for (int i = 0; i < PD; i++) key_set<KW>(nk, i, (u16)(key_get<KW>(k, i) + ((i == a) ? -PD : 1)));
+        key_set<KW>(nk, PD, key_get<KW>(k, PD));
+        const int o = table_find<KW>(table, mask, list_keys, nk);
+        if (o >= 0) {
+            const u32 u = vid[o];
+            nbr[((u64)a * max_entries + v) * 2] = (int)u;
+            nbr[((u64)a * max_entries + u) * 2 + 1] = (int)v;
+        }
+    }
+}
+
+}  // namespace pl
