@@ -37,7 +37,7 @@ def _stale(target, sources):
 
 def build_oracle(force=False):
     src = os.path.join(HERE, "pl_oracle.c")
-    if force or _stale(ORACLE_SO, [src]):
+    if force or _stale(ORACLE_SO, [src, os.path.join(HERE, "pl_oracle_impl.h")]):
         cmd = ["gcc", "-O2", "-std=c99", "-D_POSIX_C_SOURCE=200809L", "-ffp-contract=off", "-fPIC",
                "-shared", "-o", ORACLE_SO, src, "-lm", "-lpthread"]
         subprocess.check_call(cmd)

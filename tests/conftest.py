@@ -9,7 +9,9 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 GOLDEN_DIR = os.path.join(ROOT, "tests", "golden")
-GOLDEN_CASES = sorted(f[:-4] for f in os.listdir(GOLDEN_DIR) if f.endswith(".npz"))
+_ALL_CASES = sorted(f[:-4] for f in os.listdir(GOLDEN_DIR) if f.endswith(".npz"))
+GOLDEN_CASES = [c for c in _ALL_CASES if not c.endswith("_f64")]       # T = float
+GOLDEN_CASES_F64 = [c for c in _ALL_CASES if c.endswith("_f64")]       # T = double
 
 
 def pytest_configure(config):
@@ -29,8 +31,9 @@ def golden_positions(g, oracle):
     if bool(g["bilateral"]):
         ref = g["reference"]
         return oracle.compute_positions(ref.reshape(-1, ref.shape[-1]), sdims,
-                                        float(g["theta_alpha"]), float(g["theta_beta"]))
-    return oracle.compute_positions(None, sdims, float(g["theta_gamma"]), -1.0)
+                                        float(g["theta_alpha"]), float(g["theta_beta"]),
+                                        dtype=inp.dtype)
+    return oracle.compute_positions(None, sdims, float(g["theta_gamma"]), -1.0, dtype=inp.dtype)
 
 
 def sorted_rows(keys):
@@ -39,6 +42,9 @@ def sorted_rows(keys):
 
 
 def bits(a):
+    a = np.asarray(a)
+    if a.dtype == np.float64:
+        return np.ascontiguousarray(a).view(np.uint64)
     return np.ascontiguousarray(a, np.float32).view(np.uint32)
 
 

@@ -2,7 +2,8 @@
 (oracle/_ref/libpl_ref.so, built by oracle/build.py from the reference tree, hash table pre-sized so
 it never grows).  Needs the reference tree; run from the repository root:
 
-    python tests/golden/make_golden.py
+    python tests/golden/make_golden.py          # the fp32 fixtures
+    python tests/golden/make_golden.py f64      # the fp64 fixtures (*_f64.npz)
 
 Each <case>.npz holds the inputs, the call arguments and what the reference produced: forward and
 reverse outputs, the vertex count, the vertex keys (sorted rows) and each pixel's enclosing-simplex
@@ -26,32 +27,35 @@ def sorted_rows(keys):
     return keys[order]
 
 
-def run_case(name, inp, ref=None, positions=None, bilateral=True, ta=1.0, tb=1.0, tg=1.0):
+def run_case(name, inp, ref=None, positions=None, bilateral=True, ta=1.0, tb=1.0, tg=1.0,
+             dtype=np.float32):
     """inp [*S, C]; ref [*S, R] or None; positions [n, pd] or None (positions-in path)."""
     sdims = list(inp.shape[:-1])
     n = int(np.prod(sdims))
     c = inp.shape[-1]
     if positions is None:
         if bilateral:
-            pos = O.compute_positions(ref.reshape(n, -1), sdims, ta, tb, impl="reference")
+            pos = O.compute_positions(ref.reshape(n, -1), sdims, ta, tb, impl="reference",
+                                      dtype=dtype)
         else:
-            pos = O.compute_positions(None, sdims, tg, -1.0, impl="reference")
+            pos = O.compute_positions(None, sdims, tg, -1.0, impl="reference", dtype=dtype)
     else:
         pos = positions
-    fwd = O.filter(inp.reshape(n, c), pos, reverse=False, impl="reference")
-    rev = O.filter(inp.reshape(n, c), pos, reverse=True, impl="reference", structure=False)
+    fwd = O.filter(inp.reshape(n, c), pos, reverse=False, impl="reference", dtype=dtype)
+    rev = O.filter(inp.reshape(n, c), pos, reverse=True, impl="reference", structure=False,
+                   dtype=dtype)
     data = dict(
-        input=inp.astype(np.float32),
-        bilateral=np.array(bilateral), theta_alpha=np.float32(ta), theta_beta=np.float32(tb),
-        theta_gamma=np.float32(tg),
+        input=inp.astype(dtype),
+        bilateral=np.array(bilateral), theta_alpha=dtype(ta), theta_beta=dtype(tb),
+        theta_gamma=dtype(tg),
         out_forward=fwd.out.reshape(inp.shape), out_reverse=rev.out.reshape(inp.shape),
         num_vertices=np.int64(fwd.num_vertices), keys_sorted=sorted_rows(fwd.keys),
         pixel_keys=fwd.pixel_keys(), pixel_weights=fwd.pix_weight,
     )
     if ref is not None:
-        data["reference"] = ref.astype(np.float32)
+        data["reference"] = ref.astype(dtype)
     if positions is not None:
-        data["positions"] = positions.astype(np.float32)
+        data["positions"] = positions.astype(dtype)
     np.savez_compressed(os.path.join(HERE, name + ".npz"), **data)
     print(name, "n", n, "pd", pos.shape[1], "vd", c + 1, "M", fwd.num_vertices)
 
@@ -98,5 +102,27 @@ def main():
     np.savez_compressed(os.path.join(HERE, "photo_crop.npz"), **d)
 
 
+def main_f64():
+    """T = double (the reference registers its op for double too, src/LatticeFilterKernel.cpp:193)."""
+    rng = np.random.default_rng(64064)
+    f64 = dict(dtype=np.float64)
+    img = rng.random((28, 30, 3))
+    img = 0.5 * img + 0.5 * np.round(img * 3) / 3
+    run_case("rgb_pd5_vd4_f64", img, ref=img, ta=8.0, tb=0.125, **f64)
+    logits = 3 * rng.standard_normal((20, 24, 21))
+    e = np.exp(logits - logits.max(-1, keepdims=True))
+    ref = np.repeat(np.repeat(rng.random((4, 4, 3)), 5, 0), 6, 1)
+    ref = np.clip(ref + rng.normal(0, 0.05, ref.shape), 0, 1)
+    run_case("crf_pd5_vd22_f64", e / e.sum(-1, keepdims=True), ref=ref, ta=10.0, tb=0.0625, **f64)
+    run_case("spatial_pd2_vd4_f64", rng.random((21, 17, 3)), bilateral=False, tg=3.0, **f64)
+    run_case("volume_pd4_vd3_f64", rng.standard_normal((8, 9, 7, 2)),
+             ref=np.round(rng.random((8, 9, 7, 1)) * 4) / 4, ta=5.0, tb=0.1, **f64)
+    run_case("patch_pd16_vd4_f64", rng.random((300, 3)),
+             positions=rng.standard_normal((300, 16)) * 1.5, **f64)
+
+
 if __name__ == "__main__":
-    main()
+    if sys.argv[1:] == ["f64"]:
+        main_f64()
+    else:
+        main()

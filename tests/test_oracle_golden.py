@@ -3,17 +3,20 @@ CPU implementation (tests/golden/make_golden.py): everything bit-exact."""
 import numpy as np
 import pytest
 
-from conftest import GOLDEN_CASES, bits, golden_positions, load_golden, sorted_rows
+from conftest import (GOLDEN_CASES, GOLDEN_CASES_F64, bits, golden_positions, load_golden,
+                      sorted_rows)
 
 
-@pytest.mark.parametrize("case", GOLDEN_CASES)
+@pytest.mark.parametrize("case", GOLDEN_CASES + GOLDEN_CASES_F64)
 def test_port_reproduces_reference_fixture(case, oracle):
     g = load_golden(case)
     inp = g["input"]
+    assert inp.dtype == (np.float64 if case.endswith("_f64") else np.float32)
     c = inp.shape[-1]
     pos = golden_positions(g, oracle)
-    fwd = oracle.filter(inp.reshape(-1, c), pos, reverse=False)
-    rev = oracle.filter(inp.reshape(-1, c), pos, reverse=True, structure=False)
+    fwd = oracle.filter(inp.reshape(-1, c), pos, reverse=False, dtype=inp.dtype)
+    rev = oracle.filter(inp.reshape(-1, c), pos, reverse=True, structure=False, dtype=inp.dtype)
+    assert fwd.out.dtype == inp.dtype and fwd.pix_weight.dtype == inp.dtype
     assert fwd.num_vertices == int(g["num_vertices"])
     assert np.array_equal(sorted_rows(fwd.keys), g["keys_sorted"])
     assert np.array_equal(fwd.pixel_keys(), g["pixel_keys"])

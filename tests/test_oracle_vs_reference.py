@@ -36,6 +36,33 @@ def test_port_bit_identical_to_presized_reference(shape, r, c, ta, tb, reverse):
 
 
 @needs_ref
+@pytest.mark.parametrize("shape,r,c,ta,tb", [
+    ((37, 41), 3, 3, 8.0, 0.125),
+    ((48, 40), 3, 21, 20.0, 0.0625),
+    ((12, 11, 10), 1, 2, 5.0, 0.1),
+])
+@pytest.mark.parametrize("reverse", [False, True])
+def test_port_bit_identical_to_presized_reference_in_double(shape, r, c, ta, tb, reverse):
+    """T = double, including the float product the reference keeps in its elevation step."""
+    rng = np.random.default_rng(17)
+    ref = rng.random((1,) + shape + (r,))
+    inp = rng.standard_normal((1,) + shape + (c,))
+    kw = dict(structure=True, dtype=np.float64)
+    o1, s1 = O.lattice_filter(inp, ref, True, ta, tb, 1.0, reverse, impl="port", **kw)
+    o2, s2 = O.lattice_filter(inp, ref, True, ta, tb, 1.0, reverse, impl="reference", **kw)
+    assert o1.dtype == np.float64
+    assert s1[0].num_vertices == s2[0].num_vertices
+    assert np.array_equal(s1[0].keys, s2[0].keys)
+    assert np.array_equal(s1[0].pix_vertex, s2[0].pix_vertex)
+    assert np.array_equal(bits(s1[0].pix_weight), bits(s2[0].pix_weight))
+    assert np.array_equal(bits(o1), bits(o2))
+    # close to the float result (a few points near a simplex face may land in the neighbour cell)
+    o3 = O.lattice_filter(inp, ref, True, ta, tb, 1.0, reverse, impl="port")
+    assert np.linalg.norm(o3 - o1) < 2e-2 * np.linalg.norm(o1)
+    assert not np.array_equal(o3.astype(np.float64), o1)
+
+
+@needs_ref
 def test_port_matches_reference_positions_in_pd16():
     rng = np.random.default_rng(3)
     pos = (rng.standard_normal((2000, 16)) * 2).astype(np.float32)
