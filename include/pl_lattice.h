@@ -141,6 +141,35 @@ int pl_lattice_filter_f32_noalloc(float* output, const float* input, const float
                                   float theta_beta, float theta_gamma, int reverse, int64_t max_entries,
                                   void* stream);
 
+/* T = double.  The reference registers its op and instantiates its functors for double as well as
+ * float (src/LatticeFilterKernel.cpp:196-197,207-208, src/LatticeFilterKernel.cu:107-108); these
+ * entry points are the double counterparts of pl_workspace_bytes, pl_compute_positions_f32,
+ * pl_filter_f32, pl_lattice_filter_f32 and pl_export_lattice, with the same argument meaning.  The
+ * geometry follows the reference's arithmetic for T = double operation by operation (including the
+ * one product of the elevation step that it keeps in a float, src/PermutohedralLatticeCPU.h:226), so
+ * vertex keys and barycentric weights equal the reference CPU path bit for bit; the splat sums are
+ * double-precision reductions whose order varies from run to run.  A workspace sized by
+ * pl_workspace_bytes_f64 serves the double calls only.  The build / apply split, the deterministic
+ * mode and the no-allocation entry exist for float only. */
+int pl_workspace_bytes_f64(int batch, int n, int pd, int vd, int n_spatial_dims, const int* spatial_dims,
+                           int64_t max_entries, size_t* bytes);
+int pl_compute_positions_f64(const double* reference, double* positions, int n, int n_reference_channels,
+                             int n_spatial_dims, const int* spatial_dims, double spatial_std,
+                             double feature_std, void* stream);
+int pl_filter_f64(double* output, const double* input, const double* positions, int batch, int n, int pd,
+                  int vd, int reverse, void* workspace, size_t workspace_bytes, int64_t max_entries,
+                  void* stream);
+int pl_lattice_filter_f64(double* output, const double* input, const double* reference, int batch,
+                          int n_spatial_dims, const int* spatial_dims, int n_input_channels,
+                          int n_reference_channels, int bilateral, double theta_alpha, double theta_beta,
+                          double theta_gamma, int reverse, void* workspace, size_t workspace_bytes,
+                          int64_t max_entries, void* stream);
+int pl_export_lattice_f64(const void* workspace, const double* positions, const double* reference, int batch,
+                          int n, int pd, int vd, int n_spatial_dims, const int* spatial_dims,
+                          int n_reference_channels, double spatial_std, double feature_std, int64_t max_entries,
+                          int64_t max_vertices, int16_t* vertex_keys, int32_t* vertex_item,
+                          int32_t* pixel_vertex, double* pixel_weight, void* stream);
+
 /* Profiling aid: the next pl_filter_f32 / pl_lattice_filter_f32 call made by this host thread records
  * the PL_NUM_STAGE_EVENTS cudaEvent_t handles of stage_events[] on its stream at the stage
  * boundaries (start, after build, after index, after splat, after blur, after slice), then forgets

@@ -24,6 +24,8 @@ EXPORTED_SYMBOLS = [
     "pl_compute_positions_f32", "pl_filter_f32", "pl_lattice_filter_f32", "pl_lattice_stats",
     "pl_export_lattice", "pl_profile_next_call", "pl_lattice_filter_f32_noalloc",
     "pl_lattice_build_f32", "pl_lattice_build_positions_f32", "pl_lattice_apply_f32",
+    "pl_workspace_bytes_f64", "pl_compute_positions_f64", "pl_filter_f64", "pl_lattice_filter_f64",
+    "pl_export_lattice_f64",
 ]
 STATIC_SCRATCH_BYTES = 64 << 20
 NUM_STAGE_EVENTS = 6
@@ -74,6 +76,14 @@ def lib():
         L.pl_lattice_build_f32.argtypes = [vp, i, i, ip, i, i, f, f, f, i, vp, ctypes.c_size_t, i64, vp]
         L.pl_lattice_build_positions_f32.argtypes = [vp, i, i, i, i, vp, ctypes.c_size_t, i64, vp]
         L.pl_lattice_apply_f32.argtypes = [vp, vp, i, i, i, i, i, i, i, ip, vp, ctypes.c_size_t, i64, vp]
+        d = ctypes.c_double
+        L.pl_workspace_bytes_f64.argtypes = L.pl_workspace_bytes.argtypes
+        L.pl_compute_positions_f64.argtypes = [vp, vp, i, i, i, ip, d, d, vp]
+        L.pl_filter_f64.argtypes = [vp, vp, vp, i, i, i, i, i, vp, ctypes.c_size_t, i64, vp]
+        L.pl_lattice_filter_f64.argtypes = [vp, vp, vp, i, i, ip, i, i, i, d, d, d, i, vp, ctypes.c_size_t,
+                                            i64, vp]
+        L.pl_export_lattice_f64.argtypes = [vp, vp, vp, i, i, i, i, i, ip, i, d, d, i64, i64, vp, vp, vp,
+                                            vp, vp]
         L.pl_profile_next_call.argtypes = [ctypes.POINTER(ctypes.c_void_p)]
         _lib = L
     return _lib

@@ -33,6 +33,9 @@ struct Geom {
     int rcp_div;            // 1: divide through the reciprocals (exact for these operands), 0: IEEE divide
     int from_positions;     // 1: features are read from a positions array
     float scale[MAX_PD];    // host-computed scale factors (double arithmetic rounded to float)
+    // T = double calls: the same three in double
+    double spatial_std_d, feature_std_d;
+    double scale_d[MAX_PD];
 };
 
 struct Header {   // first 256 bytes of the workspace
@@ -213,6 +216,40 @@ __device__ __forceinline__ void load_features(const Geom& g, const float* __rest
     }
 }
 
+// T = double: the reference's expressions as they stand (int converted to double, IEEE divisions).
+template <int PD>
+__device__ __forceinline__ void load_features(const Geom& g, const double* __restrict__ positions,
+                                              const double* __restrict__ reference, int item, int pix, int o,
+                                              int y, int x, double* f) {
+    if (g.from_positions) {
+        const double* p = positions + ((size_t)item * g.n + pix) * PD;
+#pragma unroll
+        for (int i = 0; i < PD; i++) f[i] = __ldg(p + i);
+    } else {
+        const double* ref = reference + ((size_t)item * g.n + pix) * g.R;
+        int rest = o;
+#pragma unroll
+        for (int i = PD - 1; i >= 0; i--) {
+            if (i >= g.n_sdims) {
+                f[i] = __ddiv_rn(__ldg(ref + (i - g.n_sdims)), g.feature_std_d);
+            } else {
+                int c;
+                if (i == g.n_sdims - 1 && g.n_sdims >= 2) {
+                    c = x;
+                } else if (i == g.n_sdims - 2) {
+                    c = y;
+                } else if (g.n_sdims == 1) {
+                    c = x;
+                } else {
+                    c = rest % g.sdims[i];
+                    rest /= g.sdims[i];
+                }
+                f[i] = __ddiv_rn((double)c, g.spatial_std_d);
+            }
+        }
+    }
+}
+
 // Floats of a vertex row: vd padded to a multiple of 4 (16-byte rows).
 __host__ __device__ __forceinline__ int padded_vd(int vd) { return (vd + 3) & ~3; }
 
@@ -238,6 +275,9 @@ __device__ __forceinline__ void red_add_v4(float* addr, float4 v) {
 }
 __device__ __forceinline__ void red_add_v2(float* addr, float a, float b) {
     asm volatile("red.global.add.v2.f32 [%0], {%1, %2};" ::"l"(addr), "f"(a), "f"(b) : "memory");
+}
+__device__ __forceinline__ void red_add_f64(double* addr, double a) {
+    asm volatile("red.global.add.f64 [%0], %1;" ::"l"(addr), "d"(a) : "memory");
 }
 __device__ __forceinline__ void red_add_f32(float* addr, float a) {
     asm volatile("red.global.add.f32 [%0], %1;" ::"l"(addr), "f"(a) : "memory");

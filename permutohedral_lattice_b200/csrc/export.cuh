@@ -7,6 +7,20 @@ namespace pl {
 // ---------------------------------------------------------------------------------------------
 // positions kernel (the standalone ComputeKernel functor) and lattice export
 // ---------------------------------------------------------------------------------------------
+__global__ void positions_kernel_f64(const double* __restrict__ reference, double* __restrict__ positions,
+                                     int n, int R, int n_sdims, Geom g) {
+    const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= n) return;
+    const int pd = n_sdims + R;
+    int divisor = 1;
+    for (int s = n_sdims - 1; s >= 0; s--) {
+        positions[(size_t)pd * idx + s] = __ddiv_rn((double)((idx / divisor) % g.sdims[s]), g.spatial_std_d);
+        divisor *= g.sdims[s];
+    }
+    for (int c = 0; c < R; c++)
+        positions[(size_t)pd * idx + n_sdims + c] = __ddiv_rn(reference[(size_t)idx * R + c], g.feature_std_d);
+}
+
 __global__ void positions_kernel(const float* __restrict__ reference, float* __restrict__ positions,
                                  int n, int R, int n_sdims, Geom g) {
     const int idx = blockIdx.x * blockDim.x + threadIdx.x;
@@ -21,11 +35,11 @@ __global__ void positions_kernel(const float* __restrict__ reference, float* __r
         positions[(size_t)pd * idx + n_sdims + c] = PL_FDIV(reference[(size_t)idx * R + c], g.feature_std);
 }
 
-template <int PD>
+template <int PD, typename R = float>
 __global__ void __launch_bounds__(Cfg<PD>::TP)
 export_points(Geom g, const Header* hdr, const int2* __restrict__ tile_info, const u16* __restrict__ rec,
-              const float* __restrict__ rec_w, const u32* __restrict__ list_ref,
-              int32_t* __restrict__ pixel_vertex, float* __restrict__ pixel_weight) {
+              const R* __restrict__ rec_w, const u32* __restrict__ list_ref,
+              int32_t* __restrict__ pixel_vertex, R* __restrict__ pixel_weight) {
     constexpr int TP = Cfg<PD>::TP, SPLATS = Cfg<PD>::SPLATS;
     if (hdr->status != 0) return;
     const TilePos tpos = this_tile(g);
@@ -34,7 +48,7 @@ export_points(Geom g, const Header* hdr, const int2* __restrict__ tile_info, con
     if (!tile_point(g, tpos, tid, item, pix)) return;
     const int base = tile_info[tile].x;
     const u16* rec_tile = rec + (size_t)tile * SPLATS;
-    const float* recw_tile = rec_w + (size_t)tile * SPLATS;
+    const R* recw_tile = rec_w + (size_t)tile * SPLATS;
     const size_t o = ((size_t)item * g.n + pix) * (PD + 1);
 #pragma unroll
     for (int r = 0; r <= PD; r++) {

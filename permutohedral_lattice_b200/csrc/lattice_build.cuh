@@ -1,6 +1,7 @@
 // Lattice construction: per-tile key generation and de-duplication (build_tiles), the global hash
 // table (clear_table, insert_entries) and the vertex / neighbour tables (link_vertices, link_neighbours).
 #pragma once
+#include <type_traits>
 #include "common.cuh"
 
 namespace pl {
@@ -8,10 +9,17 @@ namespace pl {
 // ---------------------------------------------------------------------------------------------
 // build_tiles
 // ---------------------------------------------------------------------------------------------
-template <int PD>
+// R: number type of the call (float or double); it decides the geometry arithmetic and the type of the
+// stored weights, nothing else.
+template <typename R>
+struct is_double { static constexpr bool value = false; };
+template <>
+struct is_double<double> { static constexpr bool value = true; };
+
+template <int PD, typename R = float>
 __global__ void __launch_bounds__(Cfg<PD>::TP)
-build_tiles(Geom g, const float* __restrict__ positions, const float* __restrict__ reference,
-            Header* hdr, int2* __restrict__ tile_info, u16* __restrict__ rec, float* __restrict__ rec_w,
+build_tiles(Geom g, const R* __restrict__ positions, const R* __restrict__ reference,
+            Header* hdr, int2* __restrict__ tile_info, u16* __restrict__ rec, R* __restrict__ rec_w,
             Key<Cfg<PD>::KW>* __restrict__ list_keys, u32 max_entries) {
     constexpr int KW = Cfg<PD>::KW, TP = Cfg<PD>::TP, SPLATS = Cfg<PD>::SPLATS, LS = Cfg<PD>::LS;
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -28,14 +36,19 @@ build_tiles(Geom g, const float* __restrict__ positions, const float* __restrict
     int item, pix, po, py, px;
     const bool valid = tile_point(g, tpos, tid, item, pix, po, py, px);
     if (valid) {
-        float f[PD];
-        float w[PD + 1];
+        R f[PD];
+        R w[PD + 1];
         load_features<PD>(g, positions, reference, item, pix, po, py, px, f);
-        Simplex<PD> s;
-        find_simplex<PD>(f, g.scale, s);
-        barycentric<PD>(s, w);
+        typename std::conditional<is_double<R>::value, Simplex64<PD>, Simplex<PD>>::type s;
+        if constexpr (is_double<R>::value) {
+            find_simplex_f64<PD>(f, g.scale_d, s);
+            barycentric_f64<PD>(s, w);
+        } else {
+            find_simplex<PD>(f, g.scale, s);
+            barycentric<PD>(s, w);
+        }
         // the weights are final: store them now so the writes overlap the de-duplication below
-        float* recw_tile = rec_w + (size_t)tile * SPLATS;
+        R* recw_tile = rec_w + (size_t)tile * SPLATS;
 #pragma unroll
         for (int r = 0; r <= PD; r++) recw_tile[r * TP + tid] = w[r];
         // Remainder-r vertex: coordinate i = rem0_i + r - (PD+1) [rank_i > PD - r]

@@ -35,6 +35,7 @@
 #include "splat.cuh"
 #include "blur_slice.cuh"
 #include "export.cuh"
+#include "fp64.cuh"
 
 namespace pl {
 
@@ -70,6 +71,14 @@ static void scale_factors(int pd, float* out) {
     float inv_std_dev = (float)((pd + 1) * sqrt(2.0 / 3));
     for (int i = 0; i < pd; i++)
         out[i] = (float)(1.0 / sqrt((double)((i + 1) * (i + 2))) * (double)inv_std_dev);
+}
+
+// T = double: standard deviations and scale factors (src/PermutohedralLatticeCPU.h:194-217) in double.
+static void set_geom_f64(Geom& g, int pd, double spatial_std, double feature_std) {
+    g.spatial_std_d = spatial_std;
+    g.feature_std_d = feature_std;
+    const double inv_std_dev = (pd + 1) * sqrt(2.0 / 3);
+    for (int i = 0; i < pd; i++) g.scale_d[i] = 1.0 / sqrt((double)((i + 1) * (i + 2))) * inv_std_dev;
 }
 
 static int make_geom(Geom& g, int batch, int n, int pd, int n_sdims, const int* sdims, int R,
@@ -116,7 +125,8 @@ static int make_geom(Geom& g, int batch, int n, int pd, int n_sdims, const int* 
     return PL_OK;
 }
 
-static int make_layout(Layout& L, const Geom& g, int pd, int vd, int64_t max_entries_arg) {
+// real_bytes: 4 for float calls, 8 for double calls (wider weights and value rows, no fixed-point sums).
+static int make_layout(Layout& L, const Geom& g, int pd, int vd, int64_t max_entries_arg, int real_bytes = 4) {
     const u64 S = (u64)g.batch * (u64)g.n * (u64)(pd + 1);
     if (S >= 0x7FFFFFF0ull) return PL_INVALID_ARGUMENT;
     u64 E = (max_entries_arg <= 0 || (u64)max_entries_arg > S) ? S : (u64)max_entries_arg;
@@ -129,16 +139,19 @@ static int make_layout(Layout& L, const Geom& g, int pd, int vd, int64_t max_ent
     size_t off = align_up(sizeof(Header));
     L.tile_info = off; off += align_up(sizeof(int2) * (size_t)g.num_tiles);
     L.rec = off;       off += align_up(sizeof(u16) * tile_splats * (size_t)g.num_tiles);
-    L.rec_w = off;     off += align_up(sizeof(float) * tile_splats * (size_t)g.num_tiles);
+    L.rec_w = off;     off += align_up((size_t)real_bytes * tile_splats * (size_t)g.num_tiles);
     L.list_keys = off; off += align_up(sizeof(u64) * kw_of(pd) * E);
     L.list_ref = off;  off += align_up(sizeof(u32) * E);
     L.vid = off;       off += align_up(sizeof(u32) * E);
     L.vowner = off;    off += align_up(sizeof(u32) * E);
     L.table = off;     off += align_up(sizeof(u64) * slots);
     L.nbr = off;       off += align_up(sizeof(int) * 2 * (size_t)(pd + 1) * E);
-    L.v0 = off;        off += align_up(sizeof(float) * (size_t)padded_vd(vd) * E);
-    L.v1 = off;        off += align_up(sizeof(float) * (size_t)padded_vd(vd) * E);
-    L.v64 = off;       off += align_up(sizeof(long long) * (size_t)padded_vd(vd) * E);   // deterministic mode sums
+    const size_t row_bytes = real_bytes == 8 ? sizeof(double) * (size_t)padded_vd_f64(vd)
+                                             : sizeof(float) * (size_t)padded_vd(vd);
+    L.v0 = off;        off += align_up(row_bytes * E);
+    L.v1 = off;        off += align_up(row_bytes * E);
+    L.v64 = off;       // deterministic mode sums (float calls only)
+    if (real_bytes == 4) off += align_up(sizeof(long long) * (size_t)padded_vd(vd) * E);
     L.total = off;
     return PL_OK;
 }
@@ -320,19 +333,73 @@ static int run_filter(const Geom& g, float* output, const float* input, const fl
     return PL_OK;
 }
 
+// T = double: the same structure kernels, then splat, blur and slice over rows of doubles.
 template <int PD>
-static int run_export(const Geom& g, const float* positions, const float* reference, const void* workspace,
+static int run_filter_f64(const Geom& g, double* output, const double* input, const double* positions,
+                          const double* reference, int vd, int reverse, void* workspace, const Layout& L,
+                          cudaStream_t st) {
+    constexpr int KW = Cfg<PD>::KW, TP = Cfg<PD>::TP;
+    unsigned char* ws = static_cast<unsigned char*>(workspace);
+    Header* hdr = reinterpret_cast<Header*>(ws);
+    int2* tile_info = reinterpret_cast<int2*>(ws + L.tile_info);
+    u16* rec = reinterpret_cast<u16*>(ws + L.rec);
+    double* rec_w = reinterpret_cast<double*>(ws + L.rec_w);
+    Key<KW>* list_keys = reinterpret_cast<Key<KW>*>(ws + L.list_keys);
+    u32* list_ref = reinterpret_cast<u32*>(ws + L.list_ref);
+    u32* vid = reinterpret_cast<u32*>(ws + L.vid);
+    u32* vowner = reinterpret_cast<u32*>(ws + L.vowner);
+    u64* table = reinterpret_cast<u64*>(ws + L.table);
+    int* nbr = reinterpret_cast<int*>(ws + L.nbr);
+    double* v0 = reinterpret_cast<double*>(ws + L.v0);
+    double* v1 = reinterpret_cast<double*>(ws + L.v1);
+
+    PL_CUDA(cudaMemsetAsync(hdr, 0, sizeof(Header), st));
+    if (g.num_tiles == 0) return PL_OK;
+    PL_CUDA(cudaFuncSetAttribute(build_tiles<PD, double>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)Cfg<PD>::BUILD_SMEM));
+    PL_CUDA(cudaFuncSetAttribute(splat_tiles_f64<PD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)Splat64<PD>::BYTES));
+    const int wide = num_sms() * 8;
+    int table_log2 = 0;
+    while ((1ull << table_log2) < L.table_slots) table_log2++;
+    const int vp = padded_vd_f64(vd);
+
+    build_tiles<PD, double><<<tile_grid(g), TP, Cfg<PD>::BUILD_SMEM, st>>>(
+        g, positions, reference, hdr, tile_info, rec, rec_w, list_keys, (u32)L.max_entries);
+    clear_table<<<wide, 256, 0, st>>>(hdr, table, (u32)table_log2);
+    insert_entries<KW><<<wide, 256, 0, st>>>(hdr, table, list_keys, list_ref, vid, vowner);
+    // rows of vp doubles are zeroed through the 64-bit branch (vp cells of 8 bytes per vertex)
+    link_vertices<<<wide, 256, 0, st>>>(hdr, list_ref, vid, nbr, nullptr, reinterpret_cast<long long*>(v0),
+                                        L.max_entries, PD, 0);
+    zero_rows<<<wide, 256, 0, st>>>(hdr, nullptr, reinterpret_cast<long long*>(v0), vp);
+    link_neighbours<PD><<<wide, 256, 0, st>>>(hdr, table, list_keys, vid, vowner, nbr, L.max_entries);
+    splat_tiles_f64<PD><<<tile_grid(g), TP, Splat64<PD>::BYTES, st>>>(g, input, hdr, tile_info, rec, rec_w,
+                                                                      list_ref, v0, vd);
+    double* src = v0;
+    double* dst = v1;
+    for (int step = 0; step <= PD; step++) {
+        const int axis = reverse ? PD - step : step;
+        blur_axis_f64<<<wide, 256, 0, st>>>(hdr, nbr + (size_t)axis * L.max_entries * 2, src, dst, vp / 2);
+        double* tmp = src; src = dst; dst = tmp;
+    }
+    slice_tiles_f64<PD><<<tile_grid(g), TP, 0, st>>>(g, output, hdr, tile_info, rec, rec_w, list_ref, src, vd);
+    PL_CUDA(cudaGetLastError());
+    return PL_OK;
+}
+
+template <int PD, typename R>
+static int run_export(const Geom& g, const R* positions, const R* reference, const void* workspace,
                       const Layout& L, long long max_vertices, int16_t* vertex_keys,
-                      int32_t* vertex_item, int32_t* pixel_vertex, float* pixel_weight,
+                      int32_t* vertex_item, int32_t* pixel_vertex, R* pixel_weight,
                       cudaStream_t st) {
     constexpr int KW = Cfg<PD>::KW, TP = Cfg<PD>::TP;
     const unsigned char* ws = static_cast<const unsigned char*>(workspace);
     const Header* hdr = reinterpret_cast<const Header*>(ws);
     if (g.num_tiles == 0) return PL_OK;
     if (pixel_vertex || pixel_weight)
-        export_points<PD><<<tile_grid(g), TP, 0, st>>>(
+        export_points<PD, R><<<tile_grid(g), TP, 0, st>>>(
             g, hdr, reinterpret_cast<const int2*>(ws + L.tile_info), reinterpret_cast<const u16*>(ws + L.rec),
-            reinterpret_cast<const float*>(ws + L.rec_w), reinterpret_cast<const u32*>(ws + L.list_ref),
+            reinterpret_cast<const R*>(ws + L.rec_w), reinterpret_cast<const u32*>(ws + L.list_ref),
             pixel_vertex, pixel_weight);
     if (vertex_keys || vertex_item)
         export_vertices<PD><<<num_sms() * 4, 256, 0, st>>>(
@@ -604,6 +671,133 @@ int pl_lattice_apply_f32(float* output, const float* input, int n_input_channels
                          max_entries, mode, (cudaStream_t)stream, PH_APPLY);
 }
 
+// ---------------------------------------------------------------------------------------------
+// T = double
+// ---------------------------------------------------------------------------------------------
+static int geom_for_workspace(Geom& g, int batch, int n, int pd, int n_spatial_dims, const int* spatial_dims) {
+    if (spatial_dims) {
+        if (n_spatial_dims < 1 || n_spatial_dims > MAX_SDIMS || n_spatial_dims > pd) return PL_INVALID_ARGUMENT;
+        long long prod = 1;
+        for (int i = 0; i < n_spatial_dims; i++) prod *= spatial_dims[i];
+        if (prod != n) return PL_INVALID_ARGUMENT;
+        return make_geom(g, batch, n, pd, n_spatial_dims, spatial_dims, pd - n_spatial_dims, 1.f, 1.f, false);
+    }
+    int one = n;
+    return make_geom(g, batch, n, pd, 1, &one, pd - 1, 1.f, 1.f, true);
+}
+
+int pl_workspace_bytes_f64(int batch, int n, int pd, int vd, int n_spatial_dims, const int* spatial_dims,
+                           int64_t max_entries, size_t* bytes) {
+    if (!bytes || batch < 0 || n < 0 || batch > 65535) return PL_INVALID_ARGUMENT;
+    if (!pl_supported(pd, vd)) return PL_UNSUPPORTED_DIMS;
+    Geom g;
+    int rc = geom_for_workspace(g, batch, n, pd, n_spatial_dims, spatial_dims);
+    if (rc != PL_OK) return rc;
+    Layout L;
+    rc = make_layout(L, g, pd, vd, max_entries, 8);
+    if (rc != PL_OK) return rc;
+    *bytes = L.total;
+    return PL_OK;
+}
+
+int pl_compute_positions_f64(const double* reference, double* positions, int n, int n_reference_channels,
+                             int n_spatial_dims, const int* spatial_dims, double spatial_std,
+                             double feature_std, void* stream) {
+    if (!positions || n < 0 || n_spatial_dims < 0 || n_spatial_dims > MAX_SDIMS ||
+        n_reference_channels < 0 || (n_reference_channels > 0 && !reference) ||
+        (n_spatial_dims > 0 && !spatial_dims))
+        return PL_INVALID_ARGUMENT;
+    if (n == 0) return PL_OK;
+    Geom g;
+    memset(&g, 0, sizeof(g));
+    for (int i = 0; i < n_spatial_dims; i++) g.sdims[i] = spatial_dims[i];
+    g.spatial_std_d = spatial_std;
+    g.feature_std_d = feature_std;
+    positions_kernel_f64<<<(n + 255) / 256, 256, 0, (cudaStream_t)stream>>>(
+        reference, positions, n, n_reference_channels, n_spatial_dims, g);
+    PL_CUDA(cudaGetLastError());
+    return PL_OK;
+}
+
+static int filter_common_f64(const Geom& g, double* output, const double* input, const double* positions,
+                             const double* reference, int pd, int vd, int reverse, void* workspace,
+                             size_t workspace_bytes, int64_t max_entries, cudaStream_t st) {
+    Layout L;
+    int rc = make_layout(L, g, pd, vd, max_entries, 8);
+    if (rc != PL_OK) return rc;
+    if (workspace_bytes < L.total) return PL_WORKSPACE_TOO_SMALL;
+#define CALL(P) run_filter_f64<P>(g, output, input, positions, reference, vd, reverse, workspace, L, st)
+    PL_DISPATCH_PD(pd, CALL)
+#undef CALL
+}
+
+int pl_filter_f64(double* output, const double* input, const double* positions, int batch, int n, int pd,
+                  int vd, int reverse, void* workspace, size_t workspace_bytes, int64_t max_entries,
+                  void* stream) {
+    if (batch < 0 || n < 0 || batch > 65535) return PL_INVALID_ARGUMENT;
+    if (!pl_supported(pd, vd)) return PL_UNSUPPORTED_DIMS;
+    if (batch == 0 || n == 0) return PL_OK;
+    if (!output || !input || !positions || !workspace) return PL_INVALID_ARGUMENT;
+    Geom g;
+    int one = n;
+    int rc = make_geom(g, batch, n, pd, 1, &one, pd - 1, 1.f, 1.f, true);
+    if (rc != PL_OK) return rc;
+    set_geom_f64(g, pd, 1.0, 1.0);
+    return filter_common_f64(g, output, input, positions, nullptr, pd, vd, reverse, workspace, workspace_bytes,
+                             max_entries, (cudaStream_t)stream);
+}
+
+int pl_lattice_filter_f64(double* output, const double* input, const double* reference, int batch,
+                          int n_spatial_dims, const int* spatial_dims, int n_input_channels,
+                          int n_reference_channels, int bilateral, double theta_alpha, double theta_beta,
+                          double theta_gamma, int reverse, void* workspace, size_t workspace_bytes,
+                          int64_t max_entries, void* stream) {
+    if (n_input_channels < 1) return PL_INVALID_ARGUMENT;
+    Geom g;
+    int pd = 0, n = 0;
+    int rc = op_geom(g, batch, n_spatial_dims, spatial_dims, n_reference_channels, bilateral, (float)theta_alpha,
+                     (float)theta_beta, (float)theta_gamma, &pd, &n);
+    if (rc != PL_OK) return rc;
+    set_geom_f64(g, pd, bilateral ? theta_alpha : theta_gamma, bilateral ? theta_beta : -1.0);
+    const int vd = n_input_channels + 1;
+    if (!pl_supported(pd, vd)) return PL_UNSUPPORTED_DIMS;
+    if (batch == 0 || n == 0) return PL_OK;
+    if (!output || !input || !workspace || (g.R > 0 && !reference)) return PL_INVALID_ARGUMENT;
+    return filter_common_f64(g, output, input, nullptr, reference, pd, vd, reverse, workspace, workspace_bytes,
+                             max_entries, (cudaStream_t)stream);
+}
+
+int pl_export_lattice_f64(const void* workspace, const double* positions, const double* reference, int batch,
+                          int n, int pd, int vd, int n_spatial_dims, const int* spatial_dims,
+                          int n_reference_channels, double spatial_std, double feature_std, int64_t max_entries,
+                          int64_t max_vertices, int16_t* vertex_keys, int32_t* vertex_item,
+                          int32_t* pixel_vertex, double* pixel_weight, void* stream) {
+    if (!workspace || batch < 0 || n < 0 || batch > 65535) return PL_INVALID_ARGUMENT;
+    if (!pl_supported(pd, vd)) return PL_UNSUPPORTED_DIMS;
+    if (batch == 0 || n == 0) return PL_OK;
+    Geom g;
+    int rc;
+    if (positions) {
+        int one = n;
+        rc = make_geom(g, batch, n, pd, 1, &one, pd - 1, 1.f, 1.f, true);
+    } else {
+        if (n_spatial_dims < 1 || n_spatial_dims > MAX_SDIMS || !spatial_dims ||
+            n_spatial_dims + n_reference_channels != pd || (n_reference_channels > 0 && !reference))
+            return PL_INVALID_ARGUMENT;
+        rc = make_geom(g, batch, n, pd, n_spatial_dims, spatial_dims, n_reference_channels, (float)spatial_std,
+                       (float)feature_std, false);
+    }
+    if (rc != PL_OK) return rc;
+    set_geom_f64(g, pd, spatial_std, feature_std);
+    Layout L;
+    rc = make_layout(L, g, pd, vd, max_entries, 8);
+    if (rc != PL_OK) return rc;
+#define CALL(P) run_export<P, double>(g, positions, reference, workspace, L, (long long)max_vertices, vertex_keys, \
+                                      vertex_item, pixel_vertex, pixel_weight, (cudaStream_t)stream)
+    PL_DISPATCH_PD(pd, CALL)
+#undef CALL
+}
+
 int pl_profile_next_call(void** stage_events) {
     g_stage_events = reinterpret_cast<cudaEvent_t*>(stage_events);
     return PL_OK;
@@ -649,8 +843,8 @@ int pl_export_lattice(const void* workspace, const float* positions, const float
     Layout L;
     rc = make_layout(L, g, pd, vd, max_entries);
     if (rc != PL_OK) return rc;
-#define CALL(P) run_export<P>(g, positions, reference, workspace, L, (long long)max_vertices, vertex_keys, \
-                              vertex_item, pixel_vertex, pixel_weight, (cudaStream_t)stream)
+#define CALL(P) run_export<P, float>(g, positions, reference, workspace, L, (long long)max_vertices, vertex_keys, \
+                                     vertex_item, pixel_vertex, pixel_weight, (cudaStream_t)stream)
     PL_DISPATCH_PD(pd, CALL)
 #undef CALL
 }

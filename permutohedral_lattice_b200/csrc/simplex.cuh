@@ -169,4 +169,86 @@ PL_HD int16_t vertex_coord(const Simplex<PD>& s, int i, int r) {
     return (int16_t)k;
 }
 
+// ---------------------------------------------------------------------------------------------
+// T = double (src/PermutohedralLatticeCPU.h:220-286 with T = double).  Written exactly as the
+// reference computes it: there is nothing to gain from avoiding conversions here.  One quirk is
+// kept: the elevation step holds position * scale in a float (:226), and multiplies it by the
+// loop index in float, whatever T is.
+// ---------------------------------------------------------------------------------------------
+template <int PD>
+struct Simplex64 {
+    int rem0[PD + 1];
+    int rank[PD + 1];
+    double el[PD + 1];
+};
+
+template <int PD>
+PL_HD void find_simplex_f64(const double* pos, const double* scale, Simplex64<PD>& s) {
+    double sm = 0.0;
+#pragma unroll
+    for (int i = PD; i > 0; i--) {
+        const float cf = (float)PL_DMUL(pos[i - 1], scale[i - 1]);
+        s.el[i] = PL_DADD(sm, -(double)PL_FMUL((float)i, cf));
+        sm = PL_DADD(sm, (double)cf);
+    }
+    s.el[0] = sm;
+    const double inv = 1.0 / (PD + 1);
+    int sum = 0;
+#pragma unroll
+    for (int i = 0; i <= PD; i++) {
+        const double v = PL_DMUL(s.el[i], inv);
+        const double up = PL_DMUL(ceil(v), (double)(PD + 1));
+        const double down = PL_DMUL(floor(v), (double)(PD + 1));
+        const double r0 = (PL_DADD(up, -s.el[i]) < PL_DADD(s.el[i], -down)) ? up : down;
+        s.rem0[i] = (int)(int16_t)r0;
+        sum += s.rem0[i];
+    }
+    sum /= (PD + 1);
+    double d[PD + 1];
+#pragma unroll
+    for (int i = 0; i <= PD; i++) {
+        d[i] = PL_DADD(s.el[i], -(double)s.rem0[i]);
+        s.rank[i] = 0;
+    }
+#pragma unroll
+    for (int i = 0; i < PD; i++) {
+#pragma unroll
+        for (int j = i + 1; j <= PD; j++) {
+            const int lt = d[i] < d[j] ? 1 : 0;
+            s.rank[i] += lt;
+            s.rank[j] += 1 - lt;
+        }
+    }
+#pragma unroll
+    for (int i = 0; i <= PD; i++) {
+        s.rank[i] += sum;
+        const int wrap = (s.rank[i] < 0 ? 1 : 0) - (s.rank[i] > PD ? 1 : 0);
+        s.rank[i] += wrap * (PD + 1);
+        s.rem0[i] += wrap * (PD + 1);
+    }
+}
+
+template <int PD>
+PL_HD void barycentric_f64(const Simplex64<PD>& s, double* bary /* PD+1 */) {
+    const double inv = 1.0 / (PD + 1);
+    double by_rank[PD + 1];
+#pragma unroll
+    for (int q = 0; q <= PD; q++) by_rank[q] = 0.0;
+#pragma unroll
+    for (int i = 0; i <= PD; i++) {
+        const double delta = PL_DMUL(PL_DADD(s.el[i], -(double)s.rem0[i]), inv);
+#pragma unroll
+        for (int q = 0; q <= PD; q++) by_rank[q] = (s.rank[i] == q) ? delta : by_rank[q];
+    }
+#pragma unroll
+    for (int k = 1; k <= PD; k++) bary[k] = PL_DADD(by_rank[PD - k], -by_rank[PD - k + 1]);
+    bary[0] = PL_DADD(by_rank[PD], PL_DADD(1.0, -by_rank[0]));
+}
+
+template <int PD>
+PL_HD int16_t vertex_coord(const Simplex64<PD>& s, int i, int r) {
+    const int k = s.rem0[i] + r - ((s.rank[i] > PD - r) ? PD + 1 : 0);
+    return (int16_t)k;
+}
+
 }  // namespace pl

@@ -31,11 +31,20 @@ def _stream_handle(device):
     return torch.cuda.current_stream(device).cuda_stream
 
 
-def _check_tensor(t, name):
+def _check_tensor(t, name, dtype=None):
+    """float32 or float64 (the two types the reference registers its op for,
+    src/LatticeFilterKernel.cpp:196-197,207-208); `dtype` pins it to another tensor's."""
     if not t.is_cuda:
         raise ValueError("%s must be a CUDA tensor (there is no CPU path in this package)" % name)
-    if t.dtype != torch.float32:
-        raise TypeError("%s must be float32" % name)
+    if t.dtype not in (torch.float32, torch.float64):
+        raise TypeError("%s must be float32 or float64" % name)
+    if dtype is not None and t.dtype != dtype:
+        raise TypeError("%s must have dtype %s like the other operand" % (name, dtype))
+
+
+def _float32_only(t, what):
+    if t is not None and t.dtype != torch.float32:
+        raise TypeError("%s is available for float32 only" % what)
 
 
 class FilterCall:
@@ -64,24 +73,27 @@ class FilterCall:
         self.vd = self.c + 1
         self.theta = (float(theta_alpha), float(theta_beta), float(theta_gamma))
 
-    def workspace_bytes(self, max_entries=0):
+    def workspace_bytes(self, max_entries=0, dtype=torch.float32):
         nbytes = ctypes.c_size_t(0)
-        capi.check(capi.lib().pl_workspace_bytes(self.batch, self.n, self.pd, self.vd,
-                                                 len(self.sdims), capi.int_array(self.sdims),
-                                                 int(max_entries), ctypes.byref(nbytes)),
-                   "pl_workspace_bytes")
+        fn = capi.lib().pl_workspace_bytes_f64 if dtype == torch.float64 else capi.lib().pl_workspace_bytes
+        capi.check(fn(self.batch, self.n, self.pd, self.vd, len(self.sdims), capi.int_array(self.sdims),
+                      int(max_entries), ctypes.byref(nbytes)), "pl_workspace_bytes")
         return nbytes.value
 
 
 def lattice_filter_raw(input_image, reference_image, bilateral=True, theta_alpha=1.0,
                        theta_beta=1.0, theta_gamma=1.0, reverse=False, mode="atomic",
                        max_entries=0, check=None, workspace=None, out=None):
-    """One call of pl_lattice_filter_f32 on the current stream.  Returns (output, workspace, call)."""
+    """One call of pl_lattice_filter_f32 (or _f64, by the tensors' dtype) on the current stream.
+    Returns (output, workspace, call)."""
     _check_tensor(input_image, "input_image")
     x = input_image.contiguous()
+    f64 = x.dtype == torch.float64
+    if f64 and mode != "atomic":
+        raise TypeError("mode=%r is available for float32 only" % mode)
     ref = None
     if bilateral:
-        _check_tensor(reference_image, "reference_image")
+        _check_tensor(reference_image, "reference_image", x.dtype)
         ref = reference_image.contiguous()
     call = FilterCall(tuple(x.shape), None if ref is None else tuple(ref.shape), bilateral,
                       theta_alpha, theta_beta, theta_gamma)
@@ -93,14 +105,17 @@ def lattice_filter_raw(input_image, reference_image, bilateral=True, theta_alpha
         return out, None, call
     stream = _stream_handle(x.device)
     with torch.cuda.device(x.device):
-        nbytes = call.workspace_bytes(max_entries)
+        nbytes = call.workspace_bytes(max_entries, x.dtype)
         ws = workspace if workspace is not None else _workspace(x.device, stream, nbytes)
-        rc = capi.lib().pl_lattice_filter_f32(
-            out.data_ptr(), x.data_ptr(), 0 if ref is None else ref.data_ptr(), call.batch,
-            len(call.sdims), capi.int_array(call.sdims), call.c, call.r, int(call.bilateral),
-            call.theta[0], call.theta[1], call.theta[2], int(bool(reverse)), ws.data_ptr(),
-            ws.numel(), int(max_entries), capi.MODES[mode], stream)
-        capi.check(rc, "pl_lattice_filter_f32")
+        head = (out.data_ptr(), x.data_ptr(), 0 if ref is None else ref.data_ptr(), call.batch,
+                len(call.sdims), capi.int_array(call.sdims), call.c, call.r, int(call.bilateral),
+                call.theta[0], call.theta[1], call.theta[2], int(bool(reverse)), ws.data_ptr(),
+                ws.numel(), int(max_entries))
+        if f64:
+            capi.check(capi.lib().pl_lattice_filter_f64(*head, stream), "pl_lattice_filter_f64")
+        else:
+            capi.check(capi.lib().pl_lattice_filter_f32(*head, capi.MODES[mode], stream),
+                       "pl_lattice_filter_f32")
         if check is None:
             check = max_entries > 0
         if check:
@@ -133,6 +148,7 @@ class Lattice:
                  theta_gamma=1.0, max_channels=1, max_entries=0):
         """reference_image [B, *S, R] (bilateral) — or None with spatial_shape = (B, *S) for a purely
         spatial kernel.  max_channels: the widest input that will be applied."""
+        _float32_only(reference_image, "Lattice (build once, apply many times)")
         if bilateral:
             _check_tensor(reference_image, "reference_image")
             ref = reference_image.contiguous()
@@ -164,6 +180,7 @@ class Lattice:
     def apply(self, input_image, reverse=False, mode="atomic", out=None):
         """Filters input_image [B, *S, C] (C <= max_channels) through the lattice."""
         _check_tensor(input_image, "input_image")
+        _float32_only(input_image, "Lattice (build once, apply many times)")
         x = input_image.contiguous()
         call = self.call
         if tuple(x.shape[:-1]) != (call.batch,) + tuple(call.sdims):
@@ -239,9 +256,10 @@ def lattice_filter(input_image, reference_image, bilateral=True, theta_alpha=1.0
                                         bool(reverse), mode)
 
 
-def compute_positions(reference_image, spatial_dims, spatial_std, feature_std):
+def compute_positions(reference_image, spatial_dims, spatial_std, feature_std, dtype=None):
     """positions[n, n_sdims + R] for one item: the ComputeKernel functor
-    (src/LatticeFilterKernel.h:40-54).  reference_image [n, R] or None."""
+    (src/LatticeFilterKernel.h:40-54).  reference_image [n, R] or None; dtype (default: the reference
+    image's, else float32) selects the float or double functor."""
     sdims = [int(s) for s in spatial_dims]
     n = 1
     for s in sdims:
@@ -250,14 +268,17 @@ def compute_positions(reference_image, spatial_dims, spatial_std, feature_std):
         _check_tensor(reference_image, "reference_image")
         ref = reference_image.contiguous().view(n, -1)
         r, device = ref.shape[1], ref.device
+        dtype = ref.dtype if dtype is None else dtype
+        _check_tensor(ref, "reference_image", dtype)
     else:
         ref, r, device = None, 0, torch.device("cuda", torch.cuda.current_device())
-    pos = torch.empty((n, len(sdims) + r), dtype=torch.float32, device=device)
+        dtype = torch.float32 if dtype is None else dtype
+    pos = torch.empty((n, len(sdims) + r), dtype=dtype, device=device)
+    fn = capi.lib().pl_compute_positions_f64 if dtype == torch.float64 else capi.lib().pl_compute_positions_f32
     with torch.cuda.device(device):
-        capi.check(capi.lib().pl_compute_positions_f32(
-            0 if ref is None else ref.data_ptr(), pos.data_ptr(), n, r, len(sdims),
-            capi.int_array(sdims), float(spatial_std), float(feature_std), _stream_handle(device)),
-            "pl_compute_positions_f32")
+        capi.check(fn(0 if ref is None else ref.data_ptr(), pos.data_ptr(), n, r, len(sdims),
+                      capi.int_array(sdims), float(spatial_std), float(feature_std), _stream_handle(device)),
+                   "pl_compute_positions")
     return pos
 
 
@@ -266,7 +287,10 @@ def filter_positions(input_values, positions, reverse=False, mode="atomic", max_
     """The LatticeFilter functor (src/LatticeFilterKernel.h:28-38) on [batch, n, C] values at
     [batch, n, pd] positions (2-D tensors are taken as batch 1).  Returns (output, workspace)."""
     _check_tensor(input_values, "input_values")
-    _check_tensor(positions, "positions")
+    _check_tensor(positions, "positions", input_values.dtype)
+    f64 = input_values.dtype == torch.float64
+    if f64 and mode != "atomic":
+        raise TypeError("mode=%r is available for float32 only" % mode)
     squeeze = input_values.dim() == 2
     x = input_values.contiguous().view((1,) + tuple(input_values.shape)) if squeeze else input_values.contiguous()
     p = positions.contiguous().view((1,) + tuple(positions.shape)) if squeeze else positions.contiguous()
@@ -281,13 +305,16 @@ def filter_positions(input_values, positions, reverse=False, mode="atomic", max_
         stream = _stream_handle(x.device)
         with torch.cuda.device(x.device):
             nbytes = ctypes.c_size_t(0)
-            capi.check(capi.lib().pl_workspace_bytes(batch, n, pd, vd, 0, None, int(max_entries),
-                                                     ctypes.byref(nbytes)), "pl_workspace_bytes")
+            size_fn = capi.lib().pl_workspace_bytes_f64 if f64 else capi.lib().pl_workspace_bytes
+            capi.check(size_fn(batch, n, pd, vd, 0, None, int(max_entries), ctypes.byref(nbytes)),
+                       "pl_workspace_bytes")
             ws = workspace if workspace is not None else _workspace(x.device, stream, nbytes.value)
-            capi.check(capi.lib().pl_filter_f32(out.data_ptr(), x.data_ptr(), p.data_ptr(), batch, n,
-                                                pd, vd, int(bool(reverse)), ws.data_ptr(), ws.numel(),
-                                                int(max_entries), capi.MODES[mode], stream),
-                       "pl_filter_f32")
+            head = (out.data_ptr(), x.data_ptr(), p.data_ptr(), batch, n, pd, vd, int(bool(reverse)),
+                    ws.data_ptr(), ws.numel(), int(max_entries))
+            if f64:
+                capi.check(capi.lib().pl_filter_f64(*head, stream), "pl_filter_f64")
+            else:
+                capi.check(capi.lib().pl_filter_f32(*head, capi.MODES[mode], stream), "pl_filter_f32")
             if check is None:
                 check = max_entries > 0
             if check:
@@ -298,29 +325,34 @@ def filter_positions(input_values, positions, reverse=False, mode="atomic", max_
 
 
 def export_lattice(workspace, stats, batch, n, pd, vd, positions=None, reference=None, sdims=None,
-                   spatial_std=1.0, feature_std=1.0, max_entries=0):
+                   spatial_std=1.0, feature_std=1.0, max_entries=0, dtype=None):
     """Lattice structure of the last call on `workspace` as torch tensors:
     (vertex_keys [M, pd] int16, vertex_item [M] int32, pixel_vertex [batch, n, pd+1] int32,
-    pixel_weight [batch, n, pd+1] float32)."""
+    pixel_weight [batch, n, pd+1] in the call's number type).  dtype: that call's number type; by
+    default the one of positions / reference, else float32."""
     device = workspace.device
+    if dtype is None:
+        given = positions if positions is not None else reference
+        dtype = given.dtype if given is not None else torch.float32
+    fn = capi.lib().pl_export_lattice_f64 if dtype == torch.float64 else capi.lib().pl_export_lattice
     m = int(stats.num_vertices)
     vkeys = torch.zeros((m, pd), dtype=torch.int16, device=device)
     vitem = torch.zeros((m,), dtype=torch.int32, device=device)
     pv = torch.zeros((batch, n, pd + 1), dtype=torch.int32, device=device)
-    pw = torch.zeros((batch, n, pd + 1), dtype=torch.float32, device=device)
+    pw = torch.zeros((batch, n, pd + 1), dtype=dtype, device=device)
     with torch.cuda.device(device):
         if positions is not None:
-            rc = capi.lib().pl_export_lattice(workspace.data_ptr(), positions.contiguous().data_ptr(), 0,
-                                              batch, n, pd, vd, 0, None, 0, 1.0, 1.0, int(max_entries),
-                                              m, vkeys.data_ptr(), vitem.data_ptr(), pv.data_ptr(),
-                                              pw.data_ptr(), _stream_handle(device))
+            rc = fn(workspace.data_ptr(), positions.contiguous().data_ptr(), 0,
+                    batch, n, pd, vd, 0, None, 0, 1.0, 1.0, int(max_entries),
+                    m, vkeys.data_ptr(), vitem.data_ptr(), pv.data_ptr(),
+                    pw.data_ptr(), _stream_handle(device))
         else:
             r = pd - len(sdims)
-            rc = capi.lib().pl_export_lattice(workspace.data_ptr(), 0,
-                                              0 if reference is None else reference.contiguous().data_ptr(),
-                                              batch, n, pd, vd, len(sdims), capi.int_array(sdims), r,
-                                              float(spatial_std), float(feature_std), int(max_entries),
-                                              m, vkeys.data_ptr(), vitem.data_ptr(), pv.data_ptr(),
-                                              pw.data_ptr(), _stream_handle(device))
+            rc = fn(workspace.data_ptr(), 0,
+                    0 if reference is None else reference.contiguous().data_ptr(),
+                    batch, n, pd, vd, len(sdims), capi.int_array(sdims), r,
+                    float(spatial_std), float(feature_std), int(max_entries),
+                    m, vkeys.data_ptr(), vitem.data_ptr(), pv.data_ptr(),
+                    pw.data_ptr(), _stream_handle(device))
         capi.check(rc, "pl_export_lattice")
     return vkeys, vitem, pv, pw

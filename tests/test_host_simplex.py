@@ -7,7 +7,7 @@ import subprocess
 import numpy as np
 import pytest
 
-from conftest import GOLDEN_CASES, ROOT, bits, golden_positions, load_golden
+from conftest import GOLDEN_CASES, GOLDEN_CASES_F64, ROOT, bits, golden_positions, load_golden
 
 
 @pytest.fixture(scope="module")
@@ -59,6 +59,38 @@ def test_keys_and_weights_match_oracle_random(pd, shim, oracle):
     res = oracle.filter(np.ones((len(pos), 1), np.float32), pos)
     assert np.array_equal(keys, res.pixel_keys())
     assert_weights_close(w, res.pix_weight)
+
+
+def run_shim_f64(shim, pos, scale):
+    n, pd = pos.shape
+    keys = np.zeros((n, pd + 1, pd), np.int16)
+    w = np.zeros((n, pd + 1), np.float64)
+    dp = ctypes.POINTER(ctypes.c_double)
+    rc = shim.simplex_host_f64(pos.ctypes.data_as(dp), scale.ctypes.data_as(dp), n, pd,
+                               keys.ctypes.data_as(ctypes.POINTER(ctypes.c_short)), w.ctypes.data_as(dp))
+    assert rc == 0
+    return keys, w
+
+
+@pytest.mark.parametrize("case", GOLDEN_CASES_F64)
+def test_double_keys_and_weights_match_golden_bit_for_bit(case, shim, oracle):
+    g = load_golden(case)
+    pos = np.ascontiguousarray(golden_positions(g, oracle), np.float64)
+    keys, w = run_shim_f64(shim, pos, oracle.scale_factors(pos.shape[1], np.float64))
+    assert np.array_equal(keys, g["pixel_keys"])
+    assert np.array_equal(bits(w), bits(g["pixel_weights"]))
+
+
+@pytest.mark.parametrize("pd", [2, 3, 4, 5, 16])
+def test_double_keys_and_weights_match_oracle_random(pd, shim, oracle):
+    rng = np.random.default_rng(100 + pd)
+    pos = rng.standard_normal((20000, pd)) * rng.choice([0.1, 1.0, 10.0, 50.0], (20000, 1))
+    pos[:100] = np.round(pos[:100])
+    pos[100:200] = 0.0
+    keys, w = run_shim_f64(shim, pos, oracle.scale_factors(pd, np.float64))
+    res = oracle.filter(np.ones((len(pos), 1)), pos, dtype=np.float64)
+    assert np.array_equal(keys, res.pixel_keys())
+    assert np.array_equal(bits(w), bits(res.pix_weight))
 
 
 def test_reciprocal_division_is_the_ieee_quotient(shim):
