@@ -249,11 +249,13 @@ def lattice_filter(input_image, reference_image, bilateral=True, theta_alpha=1.0
     """output[B, *S, C] = permutohedral-lattice filter of input_image[B, *S, C] guided by
     reference_image[B, *S, R] (bilateral) or by position only (bilateral=False, theta_gamma).
     reuse_lattice=True keeps the lattice built in forward for the backward pass instead of rebuilding
-    it there (same results; the reference always rebuilds)."""
+    it there (same results; the reference always rebuilds).
+    The thetas are float attributes of the op (src/LatticeFilterKernel.cpp:36-38): they are rounded to
+    float32 here and widened again for float64 tensors, as the reference does (:131-142)."""
     fn = _LatticeFilterReuseFunction if reuse_lattice else _LatticeFilterFunction
-    return fn.apply(input_image, reference_image, bool(bilateral),
-                                        float(theta_alpha), float(theta_beta), float(theta_gamma),
-                                        bool(reverse), mode)
+    as_attr = lambda v: ctypes.c_float(float(v)).value
+    return fn.apply(input_image, reference_image, bool(bilateral), as_attr(theta_alpha), as_attr(theta_beta),
+                    as_attr(theta_gamma), bool(reverse), mode)
 
 
 def compute_positions(reference_image, spatial_dims, spatial_std, feature_std, dtype=None):

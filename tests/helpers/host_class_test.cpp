@@ -2,11 +2,13 @@
 // both ways (whole batch, and the reference's per-item ComputeKernel + LatticeFilter structure) and
 // writes both outputs back.  File layout (little endian): int32 header
 // {batch, n_sdims, sdims[3], C, R, bilateral, reverse}, float32 {theta_alpha, theta_beta, theta_gamma},
-// then input [batch, n, C] and reference [batch, n, R] as float32.
+// then input [batch, n, C] and reference [batch, n, R] as float32, or as float64 when the program is
+// given "f64" as its third argument (the outputs then are float64 too).
 #include <cuda_runtime.h>
 
 #include <cstdio>
 #include <cstdlib>
+#include <cstring>
 #include <vector>
 
 #include "LatticeFilterKernel.hpp"
@@ -16,10 +18,8 @@ static void die(const char* what) {
     exit(2);
 }
 
-int main(int argc, char** argv) {
-    if (argc != 3) die("usage: host_class_test <in> <out>");
-    FILE* f = fopen(argv[1], "rb");
-    if (!f) die("cannot open input");
+template <typename T>
+static int run(FILE* f, const char* out_path) {
     int hdr[9];
     float theta[3];
     if (fread(hdr, 4, 9, f) != 9 || fread(theta, 4, 3, f) != 3) die("short header");
@@ -28,35 +28,35 @@ int main(int argc, char** argv) {
     size_t n = 1;
     for (int i = 0; i < n_sdims; i++) { shape.push_back(hdr[2 + i]); n *= hdr[2 + i]; }
     shape.push_back(C);
-    std::vector<float> in(batch * n * C), ref(batch * n * R), out(batch * n * C), out2(batch * n * C);
-    if (fread(in.data(), 4, in.size(), f) != in.size()) die("short input");
-    if (R && fread(ref.data(), 4, ref.size(), f) != ref.size()) die("short reference");
+    std::vector<T> in(batch * n * C), ref(batch * n * R), out(batch * n * C), out2(batch * n * C);
+    if (fread(in.data(), sizeof(T), in.size(), f) != in.size()) die("short input");
+    if (R && fread(ref.data(), sizeof(T), ref.size(), f) != ref.size()) die("short reference");
     fclose(f);
 
-    float *d_in, *d_ref = nullptr, *d_out, *d_pos;
+    T *d_in, *d_ref = nullptr, *d_out, *d_pos;
     cudaStream_t stream;
     if (cudaStreamCreate(&stream) != cudaSuccess) die("no CUDA device");
-    cudaMalloc(&d_in, in.size() * 4);
-    cudaMalloc(&d_out, out.size() * 4);
-    if (R) cudaMalloc(&d_ref, ref.size() * 4);
-    cudaMalloc(&d_pos, n * (n_sdims + R) * 4 + 16);
-    cudaMemcpyAsync(d_in, in.data(), in.size() * 4, cudaMemcpyHostToDevice, stream);
-    if (R) cudaMemcpyAsync(d_ref, ref.data(), ref.size() * 4, cudaMemcpyHostToDevice, stream);
+    cudaMalloc(&d_in, in.size() * sizeof(T));
+    cudaMalloc(&d_out, out.size() * sizeof(T));
+    if (R) cudaMalloc(&d_ref, ref.size() * sizeof(T));
+    cudaMalloc(&d_pos, n * (n_sdims + R) * sizeof(T) + 16);
+    cudaMemcpyAsync(d_in, in.data(), in.size() * sizeof(T), cudaMemcpyHostToDevice, stream);
+    if (R) cudaMemcpyAsync(d_ref, ref.data(), ref.size() * sizeof(T), cudaMemcpyHostToDevice, stream);
 
     int n_allocs = 0;
     pl::OpContext context([&](size_t bytes) { void* p = nullptr; cudaMalloc(&p, bytes); n_allocs++; return p; },
                           [](void* p) { cudaFree(p); });
     pl::GpuDevice device{stream};
     try {
-        pl::LatticeFilterOp op(reverse != 0, bilateral != 0, theta[0], theta[1], theta[2]);
+        pl::LatticeFilterOpT<T> op(reverse != 0, bilateral != 0, theta[0], theta[1], theta[2]);
         op.Compute(device, &context, d_in, shape, d_ref, R, d_out);
-        cudaMemcpyAsync(out.data(), d_out, out.size() * 4, cudaMemcpyDeviceToHost, stream);
+        cudaMemcpyAsync(out.data(), d_out, out.size() * sizeof(T), cudaMemcpyDeviceToHost, stream);
         op.ComputePerItem(device, &context, d_in, shape, d_ref, R, d_pos, d_out);
-        cudaMemcpyAsync(out2.data(), d_out, out2.size() * 4, cudaMemcpyDeviceToHost, stream);
+        cudaMemcpyAsync(out2.data(), d_out, out2.size() * sizeof(T), cudaMemcpyDeviceToHost, stream);
         // an unsupported position dimension must surface as an exception, not abort the process
         bool threw = false;
         try {
-            pl::LatticeFilter<pl::GpuDevice, float>()(device, &context, d_out, d_in, d_pos, 16, 11, 4, false);
+            pl::LatticeFilter<pl::GpuDevice, T>()(device, &context, d_out, d_in, d_pos, 16, 11, 4, false);
         } catch (const pl::Error& e) {
             threw = e.status == PL_UNSUPPORTED_DIMS;
         }
@@ -66,10 +66,18 @@ int main(int argc, char** argv) {
         return 3;
     }
     if (cudaStreamSynchronize(stream) != cudaSuccess) die("stream failed");
-    f = fopen(argv[2], "wb");
-    fwrite(out.data(), 4, out.size(), f);
-    fwrite(out2.data(), 4, out2.size(), f);
+    f = fopen(out_path, "wb");
+    fwrite(out.data(), sizeof(T), out.size(), f);
+    fwrite(out2.data(), sizeof(T), out2.size(), f);
     fclose(f);
     printf("ok allocs=%d\n", n_allocs);
     return 0;
+}
+
+int main(int argc, char** argv) {
+    if (argc != 3 && argc != 4) die("usage: host_class_test <in> <out> [f64]");
+    FILE* f = fopen(argv[1], "rb");
+    if (!f) die("cannot open input");
+    if (argc == 4 && strcmp(argv[3], "f64") == 0) return run<double>(f, argv[2]);
+    return run<float>(f, argv[2]);
 }

@@ -142,7 +142,8 @@ def test_autograd_f64_is_the_reverse_filter(gpu, oracle):
     r = torch.from_numpy(ref).cuda()
     out = plb.lattice_filter(x, r, True, 5.0, 0.3)
     out.backward(torch.from_numpy(grad).cuda())
-    want = oracle.lattice_filter(grad, ref, True, 5.0, 0.3, 1.0, True, dtype=np.float64)
+    # the op's thetas are float attributes, widened to double
+    want = oracle.lattice_filter(grad, ref, True, 5.0, float(np.float32(0.3)), 1.0, True, dtype=np.float64)
     assert x.grad.dtype == torch.float64
     close64(x.grad.cpu().numpy(), want, "f64 gradient")
 

@@ -20,13 +20,14 @@ BIN = os.path.join(ROOT, "tests", "helpers", "host_class_test.bin")
     ((2, 25, 30), 21, 3, True, False),
     ((1, 40, 28), 4, 3, False, False),
 ])
-def test_cpp_op_class_matches_oracle(shape, c, r, bilateral, reverse, tmp_path, oracle):
+@pytest.mark.parametrize("dtype", [np.float32, np.float64])
+def test_cpp_op_class_matches_oracle(shape, c, r, bilateral, reverse, dtype, tmp_path, oracle):
     if not os.path.exists(BIN):
         pytest.fail("tests/helpers/host_class_test.bin is not built (python -m permutohedral_lattice_b200.build)")
     rng = np.random.default_rng(17)
-    inp = rng.random(shape + (c,), dtype=np.float32)
-    ref = rng.random(shape + (r,), dtype=np.float32)
-    ta, tb, tg = 5.0, 0.2, 3.0
+    inp = rng.random(shape + (c,)).astype(dtype)
+    ref = rng.random(shape + (r,)).astype(dtype)
+    ta, tb, tg = 5.0, float(np.float32(0.2)), 3.0   # float attributes of the op class
     sd = list(shape[1:]) + [0] * (3 - len(shape[1:]))
     src, dst = tmp_path / "in.bin", tmp_path / "out.bin"
     with open(src, "wb") as f:
@@ -34,11 +35,13 @@ def test_cpp_op_class_matches_oracle(shape, c, r, bilateral, reverse, tmp_path, 
         f.write(struct.pack("<3f", ta, tb, tg))
         f.write(inp.tobytes())
         f.write(ref.tobytes())
-    res = subprocess.run([BIN, str(src), str(dst)], capture_output=True, text=True, timeout=300)
+    f64 = dtype == np.float64
+    res = subprocess.run([BIN, str(src), str(dst)] + (["f64"] if f64 else []), capture_output=True, text=True,
+                         timeout=300)
     assert res.returncode == 0, res.stderr
     assert res.stdout.startswith("ok")
-    got = np.fromfile(dst, np.float32).reshape((2,) + inp.shape)
-    want = oracle.lattice_filter(inp, ref, bilateral, ta, tb, tg, reverse)
+    got = np.fromfile(dst, dtype).reshape((2,) + inp.shape)
+    want = oracle.lattice_filter(inp, ref, bilateral, ta, tb, tg, reverse, dtype=dtype)
     for which, name in ((0, "whole batch"), (1, "per item")):
-        assert rel_l2(got[which], want) <= 1e-5, name
-        assert np.abs(got[which] - want).max() <= 1e-4, name
+        assert rel_l2(got[which], want) <= (1e-12 if f64 else 1e-5), name
+        assert np.abs(got[which] - want).max() <= (1e-11 if f64 else 1e-4), name
