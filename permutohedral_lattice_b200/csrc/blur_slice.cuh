@@ -72,6 +72,7 @@ slice_tiles_fast(Geom g, float* __restrict__ output, const Header* hdr, const in
     float* out_s = reinterpret_cast<float*>(smem_raw);                                          // [TP][C], later
     int* prow_s = reinterpret_cast<int*>(smem_raw + SliceFast<PD, VD>::region(rows_cap));       // [TP]
     if (call_failed(hdr)) return;
+    PhaseClock pc(2);
     const TilePos tpos = this_tile(g);
     const int tid = threadIdx.x, tile = tpos.tile;
     const int2 info = tile_info[tile];
@@ -96,6 +97,7 @@ slice_tiles_fast(Geom g, float* __restrict__ output, const Header* hdr, const in
     }
     cp_async_wait_all();
     __syncthreads();
+    pc.mark();
     float acc[VP];
 #pragma unroll
     for (int j = 0; j < VP; j++) acc[j] = 0.f;
@@ -130,6 +132,7 @@ slice_tiles_fast(Geom g, float* __restrict__ output, const Header* hdr, const in
         }
     }
     __syncthreads();   // every cached row has been read: the output block may overwrite them
+    pc.mark();
     if (valid) {
         const float inv = (float)(1.0 / (double)acc[C]);
 #pragma unroll
@@ -138,12 +141,14 @@ slice_tiles_fast(Geom g, float* __restrict__ output, const Header* hdr, const in
     if (bulk_ok) {
         fence_async_proxy();
         __syncthreads();
+        pc.mark();
         if (tid < g.TY) {
             int first, count;
             if (tile_row(g, this_tile(g), tid, first, count))   // recomputed: keeps registers free above
                 bulk_store(output + (size_t)first * C, out_s + (size_t)tid * g.TX * C, (unsigned)count * C * 4u);
             bulk_store_finish();
         }
+        pc.mark();
     } else {
         __syncthreads();
         for (int k = tid; k < TP * C; k += TP) {

@@ -357,6 +357,31 @@ __device__ __forceinline__ void fence_async_proxy() {
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
 
+// Developer aid, compiled only with -DPL_PHASE_CLOCKS: cycles that thread 0 of every CTA spends between
+// marks, summed per kernel and phase (read back with pl_debug_phase_cycles).  Off in the shipped build.
+#ifdef PL_PHASE_CLOCKS
+__device__ unsigned long long g_phase_cycles[8][16];
+struct PhaseClock {
+    long long t;
+    int k, i;
+    __device__ __forceinline__ PhaseClock(int kernel) : k(kernel), i(0) { t = clock64(); }
+    __device__ __forceinline__ void mark(bool sync = false) {
+        if (sync) __syncthreads();
+        if (threadIdx.x == 0) {
+            const long long n = clock64();
+            atomicAdd(&g_phase_cycles[k][i], (unsigned long long)(n - t));
+            t = n;
+        }
+        i++;
+    }
+};
+#else
+struct PhaseClock {
+    __device__ __forceinline__ PhaseClock(int) {}
+    __device__ __forceinline__ void mark(bool = false) {}
+};
+#endif
+
 // First point and number of valid points of tile row `ly` (the run of points that is contiguous in
 // memory); returns false if the row lies outside the item.
 __device__ __forceinline__ bool tile_row(const Geom& g, const TilePos& tpos, int ly, int& first_row, int& count) {

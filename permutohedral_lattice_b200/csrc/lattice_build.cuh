@@ -28,6 +28,7 @@ build_tiles(Geom g, const R* __restrict__ positions, const R* __restrict__ refer
     u16* lidx_s = reinterpret_cast<u16*>(smem_raw + sizeof(Key<KW>) * SPLATS + sizeof(int) * LS);
     __shared__ int nloc_s, base_s;
 
+    PhaseClock pc(0);
     const TilePos tpos = this_tile(g);
     const int tid = threadIdx.x, tile = tpos.tile;
     for (int i = tid; i < LS; i += TP) hslots[i] = -1;
@@ -73,6 +74,7 @@ build_tiles(Geom g, const R* __restrict__ positions, const R* __restrict__ refer
         }
     }
     __syncthreads();
+    pc.mark();
 
     // de-duplicate: the first splat to claim a slot for a key represents it.  The first probes of all
     // PD+1 keys are issued together (independent shared-memory accesses); most keys resolve there,
@@ -123,6 +125,7 @@ build_tiles(Geom g, const R* __restrict__ positions, const R* __restrict__ refer
         }
     }
     __syncthreads();
+    pc.mark();
     // number the tile's entries: one shared-memory atomic per warp and remainder, not per owner
 #pragma unroll
     for (int r = 0; r <= PD; r++) {
@@ -150,6 +153,7 @@ build_tiles(Geom g, const R* __restrict__ positions, const R* __restrict__ refer
         }
     }
     __syncthreads();
+    pc.mark();
     const int base = base_s;
     u16* rec_tile = rec + (size_t)tile * SPLATS;
 #pragma unroll
@@ -162,6 +166,7 @@ build_tiles(Geom g, const R* __restrict__ positions, const R* __restrict__ refer
         }
         rec_tile[me] = l;
     }
+    pc.mark(true);
 }
 
 // ---------------------------------------------------------------------------------------------

@@ -798,6 +798,17 @@ int pl_export_lattice_f64(const void* workspace, const double* positions, const 
 #undef CALL
 }
 
+#ifdef PL_PHASE_CLOCKS
+// Developer aid: copies (and clears) the per-kernel phase cycle counters, 8 x 16 values.  SYNCHRONISES.
+int pl_debug_phase_cycles(unsigned long long* out) {
+    PL_CUDA(cudaDeviceSynchronize());
+    PL_CUDA(cudaMemcpyFromSymbol(out, g_phase_cycles, sizeof(unsigned long long) * 8 * 16));
+    static unsigned long long zeros[8 * 16] = {0};
+    PL_CUDA(cudaMemcpyToSymbol(g_phase_cycles, zeros, sizeof(zeros)));
+    return PL_OK;
+}
+#endif
+
 int pl_profile_next_call(void** stage_events) {
     g_stage_events = reinterpret_cast<cudaEvent_t*>(stage_events);
     return PL_OK;

@@ -218,6 +218,7 @@ splat_tiles_group(Geom g, const float* __restrict__ input, Header* hdr, const in
     __shared__ int wsum_s[32];
     __shared__ __align__(8) u64 bar;
     if (call_failed(hdr)) return;
+    PhaseClock pc(1);
     const TilePos tpos = this_tile(g);
     const int tid = threadIdx.x, tile = tpos.tile;
     const int2 info = tile_info[tile];
@@ -229,6 +230,7 @@ splat_tiles_group(Geom g, const float* __restrict__ input, Header* hdr, const in
     for (int i = tid; i < nloc; i += TP) cur_s[i] = 0;
     if (bulk_ok && tid == 0) mbar_init(&bar, 1);
     const int nvalid = __syncthreads_count(valid);
+    pc.mark();
 
     // stage the tile's input rows in shared memory, [point][channel] without padding: one bulk copy
     // per tile row, each issued by its own thread; thread 0 announces the byte total (nvalid points)
@@ -257,6 +259,7 @@ splat_tiles_group(Geom g, const float* __restrict__ input, Header* hdr, const in
         w[r] = valid ? recw_tile[r * TP + tid] : 0.f;
     }
     SplatCommon<PD>::template sort_splats<GL * (PD + 1)>(valid, l, w, nloc, sorted_s, cur_s, nullptr, wsum_s);
+    pc.mark();
 
     if (bulk_ok) {
         if (!mbar_wait(&bar, 0)) {
@@ -267,6 +270,7 @@ splat_tiles_group(Geom g, const float* __restrict__ input, Header* hdr, const in
         cp_async_wait_all();
         __syncthreads();
     }
+    pc.mark();
 
     // GL lanes share a window of GL (PD+1) consecutive sorted splats.  A row is cut into pieces of
     // 32 / GL bytes; lane h of the group sums pieces h, h + GL, h + 2 GL, ...  Whenever the entry
@@ -279,7 +283,11 @@ splat_tiles_group(Geom g, const float* __restrict__ input, Header* hdr, const in
     using SC = SplatCommon<PD>;
     const int total = nvalid * (PD + 1);
     const int h = tid % GL, first = (tid / GL) * WL;
+#ifdef PL_PHASE_CLOCKS
+    if (first < total) {
+#else
     if (first >= total) return;
+#endif
     float acc[NPL * PF];
 #pragma unroll
     for (int j = 0; j < NPL * PF; j++) acc[j] = 0.f;
@@ -326,6 +334,10 @@ splat_tiles_group(Geom g, const float* __restrict__ input, Header* hdr, const in
         }
     }
     flush(cur);
+#ifdef PL_PHASE_CLOCKS
+    }
+    pc.mark(true);
+#endif
 }
 
 template <int PD>
