@@ -197,13 +197,15 @@ static bool bulk_rows_ok(const Geom& g, const void* ptr, int channels) {
 template <int PD, int VD>
 static int launch_splat(const Geom& g, const float* input, Header* hdr, const int2* tile_info, const u16* rec,
                         const float* rec_w, const u32* list_ref, float* v0, int vd, cudaStream_t st) {
-    if constexpr (VD > 8) {          // wide rows: a group of lanes per window, 32-byte reduction requests
-        const size_t smem = SplatFast<PD, VD>::BYTES - sizeof(int) * Cfg<PD>::SPLATS;   // no vertex-id cache
-        // four lanes per window measured best for 24-float rows (two and eight lanes are within 10 %)
-        PL_CUDA(cudaFuncSetAttribute(splat_tiles_group<PD, VD, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    if constexpr (VD > 8 && VD <= 32) {   // wide rows: a quarter warp per window, conflict-free row reads
+        const size_t smem = SplatRows<PD, VD>::BYTES;
+        PL_CUDA(cudaFuncSetAttribute(splat_tiles_rows<PD, VD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      (int)smem));
-        splat_tiles_group<PD, VD, 4><<<tile_grid(g), Cfg<PD>::TP, smem, st>>>(
-            g, input, hdr, tile_info, rec, rec_w, list_ref, v0, bulk_rows_ok(g, input, VD - 1) ? 1 : 0);
+        // five CTAs per SM need nearly all of the SM's shared memory: ask for the largest carve-out
+        PL_CUDA(cudaFuncSetAttribute(splat_tiles_rows<PD, VD>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                     cudaSharedmemCarveoutMaxShared));
+        splat_tiles_rows<PD, VD><<<tile_grid(g), Cfg<PD>::TP, smem, st>>>(g, input, hdr, tile_info, rec, rec_w,
+                                                                         list_ref, v0);
     } else if constexpr (VD > 0) {
         const size_t smem = SplatFast<PD, VD>::BYTES;
         PL_CUDA(cudaFuncSetAttribute(splat_tiles_fast<PD, VD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
@@ -799,6 +801,24 @@ int pl_export_lattice_f64(const void* workspace, const double* positions, const 
 }
 
 #ifdef PL_PHASE_CLOCKS
+// Developer aid: resident CTAs per SM of the config-2 tile kernels, as the runtime computes them.
+int pl_debug_occupancy(int* out) {
+    PL_CUDA(cudaFuncSetAttribute(build_tiles<5>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg<5>::BUILD_SMEM));
+    PL_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&out[0], build_tiles<5>, 256, Cfg<5>::BUILD_SMEM));
+    const size_t ss = SplatRows<5, 22>::BYTES;
+    PL_CUDA(cudaFuncSetAttribute(splat_tiles_rows<5, 22>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ss));
+    PL_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&out[1], splat_tiles_rows<5, 22>, 256, ss));
+    int rows_cap = (40 * 1024) / (SliceFast<5, 22>::RS * 4);
+    const size_t sl = SliceFast<5, 22>::bytes(rows_cap);
+    PL_CUDA(cudaFuncSetAttribute(slice_tiles_fast<5, 22>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sl));
+    PL_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&out[2], slice_tiles_fast<5, 22>, 256, sl));
+    out[3] = (int)Cfg<5>::BUILD_SMEM; out[4] = (int)ss; out[5] = (int)sl;
+    cudaFuncAttributes fa;
+    PL_CUDA(cudaFuncGetAttributes(&fa, splat_tiles_rows<5, 22>));
+    out[6] = fa.numRegs; out[7] = (int)fa.sharedSizeBytes;
+    return PL_OK;
+}
+
 // Developer aid: copies (and clears) the per-kernel phase cycle counters, 8 x 16 values.  SYNCHRONISES.
 int pl_debug_phase_cycles(unsigned long long* out) {
     PL_CUDA(cudaDeviceSynchronize());

@@ -11,44 +11,52 @@ namespace pl {
 // summed in registers, reading the tile's input rows from shared memory, and leaves the CTA as one
 // vector reduction per 16 bytes.  No floating-point atomics in shared memory.
 //
-// Fast form (VD known at compile time): one THREAD per entry holds the whole row in registers;
-// entries are handed to threads in order of run length so the lanes of a warp finish together; the
-// input block arrives by bulk asynchronous copies when its rows are 16-byte aligned.
+// Narrow rows (VD <= 8, splat_tiles_fast): one THREAD sums a window of PD+1 sorted splats with the whole
+// row in registers; the input block arrives by bulk asynchronous copies when its rows are 16-byte aligned.
+// Wide rows (8 < VD <= 32, splat_tiles_rows): a quarter warp per window, see there.
 // Generic form (any vd): a group of lanes per entry, one float4 of channels per lane.
 // ---------------------------------------------------------------------------------------------
 template <int PD>
 struct SplatCommon {
     static constexpr int TP = Cfg<PD>::TP, SPLATS = Cfg<PD>::SPLATS, NW = TP / 32;
+    // Words of the sorted list when it is cut into windows (one spare word per window, WL >= PD + 1).
+    static constexpr int SORTED = SPLATS + TP;
 
-    // Counting sort of the tile's splats by entry.  On return (after the trailing barrier)
-    // sorted_s[off_s[e] .. cur_s[e]) are entry e's splats as (point | entry << 16, weight bits);
-    // cur_s must be zero for e < nloc on entry.  off_s may be nullptr when run starts are not needed.
-    // WL > 0 stores sorted position pos at slot(pos): the list is cut into windows of WL splats and
-    // laid out step-major, so that threads walking neighbouring windows in step read neighbouring words.
+    // WL > 0 stores sorted position pos at slot(pos): the list is cut into windows of WL splats, each
+    // followed by one spare word.  Splats of one entry (written together by neighbouring lanes) land in
+    // neighbouring words, and lanes that walk neighbouring windows in step read words WL + 1 apart: an
+    // odd number of 8-byte words, so neither side collides on shared-memory banks.
     template <int WL>
     __device__ static __forceinline__ int slot(int pos) {
         if constexpr (WL == 0)
             return pos;
         else
-            return (pos % WL) * (SPLATS / WL) + pos / WL;
+            return pos + pos / WL;
     }
 
+    // Counting sort of the tile's splats by entry.  On return (after the trailing barrier) entry e's
+    // splats are sorted positions cur_s[e] .. cur_s[e] + count(e), each stored as
+    // (point | entry << 16, weight bits); off_s[e], when given, receives the end of the run.
+    // cur_s must be zero for e < nloc on entry.  One shared-memory atomic per splat: the value it
+    // returns is the splat's offset inside its entry's run, so no second atomic pass is needed once the
+    // run starts are known.  (Grouping equal entries of a warp with a match instruction first measured
+    // slower than letting the atomics collide.)
     template <int WL>
     __device__ static __forceinline__ void sort_splats(bool valid, const int* l, const float* w, int nloc,
                                                        uint2* sorted_s, int* cur_s, int* off_s, int* wsum_s) {
         const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-        if (valid) {
+        int off[PD + 1];
 #pragma unroll
-            for (int r = 0; r <= PD; r++) atomicAdd(&cur_s[l[r]], 1);
-        }
+        for (int r = 0; r <= PD; r++) off[r] = valid ? atomicAdd(&cur_s[l[r]], 1) : 0;
         __syncthreads();
-        int local[PD + 1];
+        int local[PD + 1], count[PD + 1];
         int sum = 0;
 #pragma unroll
         for (int r = 0; r <= PD; r++) {
             const int i = tid * (PD + 1) + r;
             local[r] = sum;
-            sum += (i < nloc) ? cur_s[i] : 0;
+            count[r] = (i < nloc) ? cur_s[i] : 0;
+            sum += count[r];
         }
         int incl = sum;
 #pragma unroll
@@ -74,15 +82,15 @@ struct SplatCommon {
         for (int r = 0; r <= PD; r++) {
             const int i = tid * (PD + 1) + r;
             if (i < nloc) {
-                if (off_s) off_s[i] = excl + local[r];
                 cur_s[i] = excl + local[r];
+                if (off_s) off_s[i] = excl + local[r] + count[r];
             }
         }
         __syncthreads();
         if (valid) {
 #pragma unroll
             for (int r = 0; r <= PD; r++) {
-                const int pos = atomicAdd(&cur_s[l[r]], 1);
+                const int pos = cur_s[l[r]] + off[r];
                 sorted_s[slot<WL>(pos)] = make_uint2((unsigned)tid | ((unsigned)l[r] << 16), __float_as_uint(w[r]));
             }
         }
@@ -94,7 +102,8 @@ template <int PD, int VD>
 struct SplatFast {
     static constexpr int TP = Cfg<PD>::TP, SPLATS = Cfg<PD>::SPLATS, C = VD - 1;
     static constexpr size_t IN_BYTES = ((sizeof(float) * TP * C + 15) / 16) * 16;
-    static constexpr size_t BYTES = IN_BYTES + sizeof(uint2) * SPLATS + 2 * sizeof(int) * SPLATS + sizeof(int) * TP;
+    static constexpr int SORTED = SplatCommon<PD>::SORTED;
+    static constexpr size_t BYTES = IN_BYTES + sizeof(uint2) * SORTED + 2 * sizeof(int) * SPLATS + sizeof(int) * TP;
 };
 
 // Adds a row held in registers to vertex row `vrow` (VP floats, 16-byte aligned).
@@ -115,8 +124,8 @@ splat_tiles_fast(Geom g, const float* __restrict__ input, Header* hdr, const int
     constexpr int TP = Cfg<PD>::TP, SPLATS = Cfg<PD>::SPLATS, C = VD - 1, VP = (VD + 3) & ~3;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     float* in_s = reinterpret_cast<float*>(smem_raw);                                       // [TP][C]
-    uint2* sorted_s = reinterpret_cast<uint2*>(smem_raw + SplatFast<PD, VD>::IN_BYTES);     // [SPLATS]
-    int* cur_s = reinterpret_cast<int*>(sorted_s + SPLATS);                                 // [SPLATS]
+    uint2* sorted_s = reinterpret_cast<uint2*>(smem_raw + SplatFast<PD, VD>::IN_BYTES);     // [SORTED]
+    int* cur_s = reinterpret_cast<int*>(sorted_s + SplatFast<PD, VD>::SORTED);              // [SPLATS]
     int* prow_s = cur_s + SPLATS;                                                           // [TP]
     u32* vid_s = reinterpret_cast<u32*>(prow_s + TP);                                       // [SPLATS] entry -> vertex
     __shared__ int wsum_s[32];
@@ -183,12 +192,13 @@ splat_tiles_fast(Geom g, const float* __restrict__ input, Header* hdr, const int
     float acc[VP];
 #pragma unroll
     for (int j = 0; j < VP; j++) acc[j] = 0.f;
-    using SC = SplatCommon<PD>;
-    int cur = (int)(sorted_s[SC::template slot<PD + 1>(first)].x >> 16);
+    // window tid holds sorted positions first .. first + PD in words tid (PD + 2) + i
+    const uint2* sp = sorted_s + tid * (PD + 2);
+    int cur = (int)(sp[0].x >> 16);
 #pragma unroll
     for (int i = 0; i <= PD; i++) {
         if (first + i < total) {
-            const uint2 pw = sorted_s[SC::template slot<PD + 1>(first + i)];
+            const uint2 pw = sp[i];
             const int e = (int)(pw.x >> 16);
             if (e != cur) {
                 flush_row<VP>(v0 + (size_t)vid_s[cur] * VP, acc);
@@ -197,26 +207,43 @@ splat_tiles_fast(Geom g, const float* __restrict__ input, Header* hdr, const int
             const float wt = __uint_as_float(pw.y);
             const float* x = in_s + (pw.x & 0xFFFFu) * C;
 #pragma unroll
-            for (int j = 0; j < C; j++) acc[j] = PL_FADD(acc[j], PL_FMUL(wt, x[j]));
+            for (int j = 0; j < C; j++) acc[j] = PL_FMA(wt, x[j], acc[j]);
             acc[C] = PL_FADD(acc[C], wt);
         }
     }
     flush_row<VP>(v0 + (size_t)vid_s[cur] * VP, acc);
 }
 
-template <int PD, int VD, int GL>
+// Wide rows (8 < VD <= 32): a QUARTER WARP per window.  The input block is staged with rows padded to VP
+// floats (16-byte aligned), so the 8 lanes of a quarter warp read one point's row as consecutive
+// float4 words: a 128-bit shared-memory load is served one quarter warp at a time, so every quarter
+// reads its own row without bank conflicts whatever rows the other quarters read.  Lane h keeps
+// channels 4h .. 4h+3 of the running sum; the row's channel C is staged as 1 (homogeneous), the padding
+// as 0, so the loop has no channel tests.  A flush is one 16-byte vector reduction per lane.
+template <int PD, int VD>
+struct SplatRows {
+    static constexpr int TP = Cfg<PD>::TP, SPLATS = Cfg<PD>::SPLATS, VP = (VD + 3) & ~3;
+    static constexpr int LR = VP / 4;                  // lanes that hold a piece of the row
+    static constexpr int WL = 8 * (PD + 1);            // splats per window: TP / 8 windows
+    static constexpr int SORTED = SPLATS + SPLATS / WL + 1;
+    static constexpr size_t BYTES = sizeof(float) * TP * VP + sizeof(uint2) * SORTED + sizeof(int) * SPLATS +
+                                    sizeof(int) * TP;
+};
+
+template <int PD, int VD>
 __global__ void __launch_bounds__(Cfg<PD>::TP)
-splat_tiles_group(Geom g, const float* __restrict__ input, Header* hdr, const int2* __restrict__ tile_info,
+splat_tiles_rows(Geom g, const float* __restrict__ input, Header* hdr, const int2* __restrict__ tile_info,
                  const u16* __restrict__ rec, const float* __restrict__ rec_w,
-                 const u32* __restrict__ list_ref, float* __restrict__ v0, int bulk_ok) {
-    constexpr int TP = Cfg<PD>::TP, SPLATS = Cfg<PD>::SPLATS, C = VD - 1, VP = (VD + 3) & ~3;
+                 const u32* __restrict__ list_ref, float* __restrict__ v0) {
+    using SR = SplatRows<PD, VD>;
+    constexpr int TP = SR::TP, SPLATS = SR::SPLATS, C = VD - 1, VP = SR::VP, LR = SR::LR, WL = SR::WL;
+    static_assert(LR <= 8, "a row must fit the 8 lanes of a quarter warp");
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    float* in_s = reinterpret_cast<float*>(smem_raw);                                       // [TP][C]
-    uint2* sorted_s = reinterpret_cast<uint2*>(smem_raw + SplatFast<PD, VD>::IN_BYTES);     // [SPLATS]
-    int* cur_s = reinterpret_cast<int*>(sorted_s + SPLATS);                                 // [SPLATS]
-    int* prow_s = cur_s + SPLATS;                                                           // [TP]
+    float* in_s = reinterpret_cast<float*>(smem_raw);                         // [TP][VP]
+    uint2* sorted_s = reinterpret_cast<uint2*>(in_s + TP * VP);               // [SORTED]
+    int* cur_s = reinterpret_cast<int*>(sorted_s + SR::SORTED);               // [SPLATS]
+    int* prow_s = cur_s + SPLATS;                                             // [TP]
     __shared__ int wsum_s[32];
-    __shared__ __align__(8) u64 bar;
     if (call_failed(hdr)) return;
     PhaseClock pc(1);
     const TilePos tpos = this_tile(g);
@@ -228,24 +255,26 @@ splat_tiles_group(Geom g, const float* __restrict__ input, Header* hdr, const in
     const bool valid = tile_point(g, tpos, tid, item, pix);
     prow_s[tid] = valid ? item * g.n + pix : -1;
     for (int i = tid; i < nloc; i += TP) cur_s[i] = 0;
-    if (bulk_ok && tid == 0) mbar_init(&bar, 1);
+    in_s[tid * VP + C] = 1.f;   // homogeneous channel, then padding
+#pragma unroll
+    for (int j = C + 1; j < VP; j++) in_s[tid * VP + j] = 0.f;
     const int nvalid = __syncthreads_count(valid);
     pc.mark();
-
-    // stage the tile's input rows in shared memory, [point][channel] without padding: one bulk copy
-    // per tile row, each issued by its own thread; thread 0 announces the byte total (nvalid points)
-    if (bulk_ok) {
-        if (tid == 0) mbar_expect_tx(&bar, (unsigned)nvalid * C * 4u);
-        if (tid < g.TY) {
-            int first, count;
-            if (tile_row(g, tpos, tid, first, count))
-                bulk_load(in_s + (size_t)tid * g.TX * C, input + (size_t)first * C, (unsigned)count * C * 4u, &bar);
-        }
-    } else {
-        for (int k = tid; k < TP * C; k += TP) {
-            const int p = k / C, j = k - p * C;
+    {
+        // element k = tid, tid + TP, ... of the tile's [point][channel] block; (point, channel) advance
+        // without a division: TP = DP * C + DJ
+        constexpr int DP = TP / C, DJ = TP % C;
+        int p = tid / C, j = tid - p * C;
+#pragma unroll 3
+        for (int it = 0; it < C; it++) {
             const int row = prow_s[p];
-            if (row >= 0) cp_async4(in_s + k, input + (size_t)row * C + j);
+            if (row >= 0) cp_async4(in_s + p * VP + j, input + (size_t)row * C + j);
+            p += DP;
+            j += DJ;
+            if (j >= C) {
+                j -= C;
+                p++;
+            }
         }
     }
 
@@ -258,86 +287,40 @@ splat_tiles_group(Geom g, const float* __restrict__ input, Header* hdr, const in
         l[r] = valid ? rec_tile[r * TP + tid] : 0;
         w[r] = valid ? recw_tile[r * TP + tid] : 0.f;
     }
-    SplatCommon<PD>::template sort_splats<GL * (PD + 1)>(valid, l, w, nloc, sorted_s, cur_s, nullptr, wsum_s);
+    SplatCommon<PD>::template sort_splats<WL>(valid, l, w, nloc, sorted_s, cur_s, nullptr, wsum_s);
+    pc.mark();
+    cp_async_wait_all();
+    __syncthreads();
     pc.mark();
 
-    if (bulk_ok) {
-        if (!mbar_wait(&bar, 0)) {
-            atomicOr(&hdr->status, 1u << PL_INTERNAL_ERROR);
-            return;
-        }
-    } else {
-        cp_async_wait_all();
-        __syncthreads();
-    }
-    pc.mark();
-
-    // GL lanes share a window of GL (PD+1) consecutive sorted splats.  A row is cut into pieces of
-    // 32 / GL bytes; lane h of the group sums pieces h, h + GL, h + 2 GL, ...  Whenever the entry
-    // changes, and at the end of the window, the partial row leaves as reductions: the GL lanes'
-    // pieces of one step are neighbours in memory, so each group issues one 32-byte request per step.
-    constexpr int PF = 8 / GL;                 // floats per piece: 4, 2 or 1
-    constexpr int NP = VP / PF;                // pieces per row
-    constexpr int NPL = (NP + GL - 1) / GL;    // pieces per lane
-    constexpr int WL = GL * (PD + 1);
-    using SC = SplatCommon<PD>;
     const int total = nvalid * (PD + 1);
-    const int h = tid % GL, first = (tid / GL) * WL;
-#ifdef PL_PHASE_CLOCKS
-    if (first < total) {
-#else
-    if (first >= total) return;
-#endif
-    float acc[NPL * PF];
-#pragma unroll
-    for (int j = 0; j < NPL * PF; j++) acc[j] = 0.f;
-    int cur = (int)(sorted_s[SC::template slot<WL>(first)].x >> 16);
-    auto flush = [&](int entry) {
-        float* vrow = v0 + (size_t)list_ref[base + entry] * VP + h * PF;
-#pragma unroll
-        for (int k = 0; k < NPL; k++) {
-            if (h + GL * k < NP) {
-                float* dst = vrow + GL * PF * k;
-                if constexpr (PF == 4)
-                    red_add_v4(dst, make_float4(acc[4 * k], acc[4 * k + 1], acc[4 * k + 2], acc[4 * k + 3]));
-                else if constexpr (PF == 2)
-                    red_add_v2(dst, acc[2 * k], acc[2 * k + 1]);
-                else
-                    red_add_f32(dst, acc[k]);
-            }
-        }
-#pragma unroll
-        for (int j = 0; j < NPL * PF; j++) acc[j] = 0.f;
-    };
+    const int h = tid & 7, wnd = tid >> 3, first = wnd * WL;
+    const bool active = (h < LR) && (first < total);
+    if (active) {
+        const int count = min(WL, total - first);
+        const uint2* sp = sorted_s + wnd * (WL + 1);   // this window's words (see SplatCommon::slot)
+        const float4* in4 = reinterpret_cast<const float4*>(in_s) + h;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        int cur = (int)(sp[0].x >> 16);
 #pragma unroll 4
-    for (int i = 0; i < WL; i++) {
-        if (first + i < total) {
-            const uint2 pw = sorted_s[SC::template slot<WL>(first + i)];
+        for (int i = 0; i < count; i++) {
+            const uint2 pw = sp[i];
             const int e = (int)(pw.x >> 16);
             if (e != cur) {
-                flush(cur);
+                red_add_v4(v0 + (size_t)list_ref[base + cur] * VP + 4 * h, acc);
+                acc = make_float4(0.f, 0.f, 0.f, 0.f);
                 cur = e;
             }
             const float wt = __uint_as_float(pw.y);
-            const float* x = in_s + (pw.x & 0xFFFFu) * C + h * PF;
-#pragma unroll
-            for (int k = 0; k < NPL; k++) {
-#pragma unroll
-                for (int c = 0; c < PF; c++) {
-                    const int j = (h + GL * k) * PF + c;      // channel of this lane's slot
-                    if (j < C)
-                        acc[PF * k + c] = PL_FADD(acc[PF * k + c], PL_FMUL(wt, x[GL * PF * k + c]));
-                    else if (j == C)
-                        acc[PF * k + c] = PL_FADD(acc[PF * k + c], wt);
-                }
-            }
+            const float4 x = in4[(pw.x & 0xFFFFu) * LR];
+            acc.x = PL_FMA(wt, x.x, acc.x);
+            acc.y = PL_FMA(wt, x.y, acc.y);
+            acc.z = PL_FMA(wt, x.z, acc.z);
+            acc.w = PL_FMA(wt, x.w, acc.w);
         }
-    }
-    flush(cur);
-#ifdef PL_PHASE_CLOCKS
+        red_add_v4(v0 + (size_t)list_ref[base + cur] * VP + 4 * h, acc);
     }
     pc.mark(true);
-#endif
 }
 
 template <int PD>
@@ -398,7 +381,7 @@ splat_tiles_generic(Geom g, const float* __restrict__ input, Header* hdr, const 
     if (!lm.active) return;
     const float4* in4 = reinterpret_cast<const float4*>(in_s);
     for (int e = warp * lm.ppw + lm.g; e < nloc; e += NW * lm.ppw) {
-        const int beg = off_s[e], end = cur_s[e];
+        const int beg = cur_s[e], end = off_s[e];
         float* vrow = v0 + (size_t)list_ref[base + e] * VP;
         for (int q = lm.q0; q < QPR; q += lm.gs) {
             float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
