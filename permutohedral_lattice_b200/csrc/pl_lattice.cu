@@ -204,8 +204,11 @@ static int launch_splat(const Geom& g, const float* input, Header* hdr, const in
         // five CTAs per SM need nearly all of the SM's shared memory: ask for the largest carve-out
         PL_CUDA(cudaFuncSetAttribute(splat_tiles_rows<PD, VD>, cudaFuncAttributePreferredSharedMemoryCarveout,
                                      cudaSharedmemCarveoutMaxShared));
+        // bulk staging also needs 16-byte aligned landing zones inside the padded tile rows
+        const bool bulk = bulk_rows_ok(g, input, VD - 1) && g.TX <= 16 &&
+                          (g.TX * (SplatRows<PD, VD>::VP - (VD - 1))) % 4 == 0;
         splat_tiles_rows<PD, VD><<<tile_grid(g), Cfg<PD>::TP, smem, st>>>(g, input, hdr, tile_info, rec, rec_w,
-                                                                         list_ref, v0);
+                                                                         list_ref, v0, bulk ? 1 : 0);
     } else if constexpr (VD > 0) {
         const size_t smem = SplatFast<PD, VD>::BYTES;
         PL_CUDA(cudaFuncSetAttribute(splat_tiles_fast<PD, VD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));

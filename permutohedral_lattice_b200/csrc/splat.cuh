@@ -234,7 +234,7 @@ template <int PD, int VD>
 __global__ void __launch_bounds__(Cfg<PD>::TP)
 splat_tiles_rows(Geom g, const float* __restrict__ input, Header* hdr, const int2* __restrict__ tile_info,
                  const u16* __restrict__ rec, const float* __restrict__ rec_w,
-                 const u32* __restrict__ list_ref, float* __restrict__ v0) {
+                 const u32* __restrict__ list_ref, float* __restrict__ v0, int bulk_ok) {
     using SR = SplatRows<PD, VD>;
     constexpr int TP = SR::TP, SPLATS = SR::SPLATS, C = VD - 1, VP = SR::VP, LR = SR::LR, WL = SR::WL;
     static_assert(LR <= 8, "a row must fit the 8 lanes of a quarter warp");
@@ -244,10 +244,11 @@ splat_tiles_rows(Geom g, const float* __restrict__ input, Header* hdr, const int
     int* cur_s = reinterpret_cast<int*>(sorted_s + SR::SORTED);               // [SPLATS]
     int* prow_s = cur_s + SPLATS;                                             // [TP]
     __shared__ int wsum_s[32];
+    __shared__ __align__(8) u64 bar;
     if (call_failed(hdr)) return;
     PhaseClock pc(1);
     const TilePos tpos = this_tile(g);
-    const int tid = threadIdx.x, tile = tpos.tile;
+    const int tid = threadIdx.x, tile = tpos.tile, lane = tid & 31, warp = tid >> 5;
     const int2 info = tile_info[tile];
     const int base = info.x, nloc = info.y;
 
@@ -255,12 +256,28 @@ splat_tiles_rows(Geom g, const float* __restrict__ input, Header* hdr, const int
     const bool valid = tile_point(g, tpos, tid, item, pix);
     prow_s[tid] = valid ? item * g.n + pix : -1;
     for (int i = tid; i < nloc; i += TP) cur_s[i] = 0;
-    in_s[tid * VP + C] = 1.f;   // homogeneous channel, then padding
-#pragma unroll
-    for (int j = C + 1; j < VP; j++) in_s[tid * VP + j] = 0.f;
+    if (bulk_ok && tid == 0) mbar_init(&bar, 1);
     const int nvalid = __syncthreads_count(valid);
     pc.mark();
-    {
+
+    // Staging.  Bulk form: every tile row's block (TX points x C floats, contiguous in memory) lands
+    // by one bulk asynchronous copy at the END of the tile row's padded region; after the sort a warp
+    // spreads it out in place to the padded rows (all reads of a tile row, then all writes: the
+    // landing zone overlaps the rows it feeds).  Otherwise: 4-byte asynchronous copies straight to
+    // the padded positions.
+    const int land = g.TX * (VP - C);   // floats between the start of a tile row's region and its landing zone
+    if (bulk_ok) {
+        if (tid == 0) mbar_expect_tx(&bar, (unsigned)nvalid * C * 4u);
+        if (tid < g.TY) {
+            int first, count;
+            if (tile_row(g, tpos, tid, first, count))
+                bulk_load(in_s + (size_t)tid * g.TX * VP + land, input + (size_t)first * C, (unsigned)count * C * 4u,
+                          &bar);
+        }
+    } else {
+        in_s[tid * VP + C] = 1.f;   // homogeneous channel, then padding
+#pragma unroll
+        for (int j = C + 1; j < VP; j++) in_s[tid * VP + j] = 0.f;
         // element k = tid, tid + TP, ... of the tile's [point][channel] block; (point, channel) advance
         // without a division: TP = DP * C + DJ
         constexpr int DP = TP / C, DJ = TP % C;
@@ -289,8 +306,53 @@ splat_tiles_rows(Geom g, const float* __restrict__ input, Header* hdr, const int
     }
     SplatCommon<PD>::template sort_splats<WL>(valid, l, w, nloc, sorted_s, cur_s, nullptr, wsum_s);
     pc.mark();
-    cp_async_wait_all();
-    __syncthreads();
+    if (bulk_ok) {
+        if (!mbar_wait(&bar, 0)) {
+            atomicOr(&hdr->status, 1u << PL_INTERNAL_ERROR);
+            return;
+        }
+        constexpr int MAXE = (16 * C + 31) / 32;   // elements per lane of a tile row (TX <= 16)
+        for (int ly = warp; ly < g.TY; ly += TP / 32) {
+            // valid points of this tile row: its first point's validity and the row's width
+            const int p0 = ly * g.TX;
+            const int row0 = prow_s[p0];
+            int count = 0;
+            if (row0 >= 0) {
+                const int x0 = (row0 % g.n) % g.W;
+                count = min(g.TX, g.W - x0);
+            }
+            float* region = in_s + (size_t)p0 * VP;
+            const int n = count * C;
+            float tmp[MAXE];
+            int dst[MAXE];
+            int pp = lane / C, jj = lane - pp * C;   // element e = lane + 32 m is channel jj of point pp
+#pragma unroll
+            for (int m = 0; m < MAXE; m++) {
+                const int e = lane + 32 * m;
+                tmp[m] = (e < n) ? region[land + e] : 0.f;
+                dst[m] = (e < n) ? pp * VP + jj : -1;
+                pp += 32 / C;
+                jj += 32 % C;
+                if (jj >= C) {
+                    jj -= C;
+                    pp++;
+                }
+            }
+            __syncwarp();
+#pragma unroll
+            for (int m = 0; m < MAXE; m++)
+                if (dst[m] >= 0) region[dst[m]] = tmp[m];
+            if (lane < g.TX) {
+                region[lane * VP + C] = 1.f;   // homogeneous channel, then padding
+#pragma unroll
+                for (int j = C + 1; j < VP; j++) region[lane * VP + j] = 0.f;
+            }
+        }
+        __syncthreads();
+    } else {
+        cp_async_wait_all();
+        __syncthreads();
+    }
     pc.mark();
 
     const int total = nvalid * (PD + 1);
