@@ -4,3 +4,4 @@ from .lattice_filter import (compute_positions, export_lattice, filter_positions
                              lattice_filter_raw, lattice_stats, release_workspaces, Lattice)
 from .host_pipeline import HostPipeline  # noqa: F401,E402
 from .graphed import GraphedLatticeFilter  # noqa: F401,E402
+from .crf import DenseCRF  # noqa: F401,E402

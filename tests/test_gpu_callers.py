@@ -1,0 +1,59 @@
+"""The callers either side of the op: the image-file demo with the reference program's command line, and
+dense-CRF mean-field inference built on lattices that are constructed once per image."""
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+
+from conftest import ROOT
+
+pytestmark = pytest.mark.gpu
+
+
+def test_bilateral_demo_command_line(tmp_path, oracle):
+    from PIL import Image
+    rng = np.random.default_rng(3)
+    blocks = rng.integers(0, 256, (6, 8, 3))
+    img = np.clip(np.kron(blocks, np.ones((8, 8, 1))) + rng.normal(0, 6, (48, 64, 3)), 0, 255).astype(np.uint8)
+    src, dst = tmp_path / "in.bmp", tmp_path / "out.bmp"
+    Image.fromarray(img).save(src)
+    res = subprocess.run([sys.executable, "-m", "permutohedral_lattice_b200.bilateral_demo", str(src), str(dst),
+                          "8", "0.125"], cwd=ROOT, capture_output=True, text=True, timeout=600)
+    assert res.returncode == 0, res.stderr
+    assert res.stdout.count("Measured from function call") == 2
+    got = np.array(Image.open(dst))
+    x = (img / 255.0).astype(np.float32)[None]
+    want = np.round(oracle.lattice_filter(x, x, True, 8.0, 0.125)[0] * 255).astype(np.uint8)
+    d = np.abs(got.astype(np.int32) - want.astype(np.int32))
+    assert d.max() <= 1 and (d != 0).mean() < 1e-3      # a value on a rounding boundary may tip over
+    res = subprocess.run([sys.executable, "-m", "permutohedral_lattice_b200.bilateral_demo"], cwd=ROOT,
+                         capture_output=True, text=True, timeout=600)
+    assert res.returncode == 1 and "Usage" in res.stdout
+
+
+def test_dense_crf_mean_field_matches_cpu_composition(oracle):
+    import torch
+    import permutohedral_lattice_b200 as plb
+    rng = np.random.default_rng(5)
+    b, h, w, labels = 2, 40, 36, 5
+    image = np.clip(np.kron(rng.random((b, 5, 6, 3)), np.ones((1, 8, 6, 1))) + rng.normal(0, 0.03, (b, h, w, 3)),
+                    0, 1).astype(np.float32)
+    unaries = (2.0 * rng.standard_normal((b, h, w, labels))).astype(np.float32)
+    ta, tb, tg, wb, ws = 10.0, 0.1, 2.0, 1.5, 0.75
+    crf = plb.DenseCRF(torch.from_numpy(image).cuda(), labels, ta, tb, tg, wb, ws)
+    got = crf.infer(torch.from_numpy(unaries).cuda(), iterations=3).cpu().numpy()
+
+    def softmax(z):
+        e = np.exp(z - z.max(-1, keepdims=True))
+        return e / e.sum(-1, keepdims=True)
+
+    compat = 1.0 - np.eye(labels, dtype=np.float32)
+    q = softmax(-unaries)
+    for _ in range(3):
+        qb = oracle.lattice_filter(q, image, True, ta, tb, 1.0)
+        qs = oracle.lattice_filter(q, None, False, 1.0, 1.0, tg)
+        q = softmax(-unaries - (wb * qb + ws * qs) @ compat).astype(np.float32)
+    assert np.abs(got - q).max() <= 1e-4
+    assert np.abs(got.sum(-1) - 1).max() <= 1e-5

@@ -103,6 +103,41 @@ def test_ragged_shapes(shape, r, c, gpu, oracle):
         gpu.assert_outputs_close(out.cpu().numpy(), want, str(shape))
 
 
+@pytest.mark.parametrize("shape,r,c,why", [
+    ((40, 48), 3, 21, "wide rows, tile rows arrive by bulk copies and are spread out in place"),
+    ((25, 30), 3, 21, "wide rows, row bytes x width not a multiple of 16: 4-byte copies to the padded rows"),
+    ((37, 20), 3, 21, "wide rows, ragged last tile column (4 points) on the bulk path"),
+    ((6, 9, 7), 1, 21, "wide rows in a volume (pd 4)"),
+    ((33, 18), 3, 8, "vd 9: no compiled instantiation, generic lane-group kernels"),
+    ((20, 24), 3, 31, "vd 32: generic kernels, eight float4 per row"),
+    ((18, 22), 3, 40, "vd 41: generic kernels, eleven float4 per row"),
+])
+def test_value_widths_and_staging_paths(shape, r, c, why, gpu, oracle):
+    rng = np.random.default_rng(23)
+    ref = rng.random((2,) + shape + (r,), dtype=np.float32)
+    inp = rng.standard_normal((2,) + shape + (c,)).astype(np.float32)
+    for reverse in (False, True):
+        want, items = oracle.lattice_filter(inp, ref, True, 4.0, 0.2, 1.0, reverse, structure=True)
+        out, ws, call, x, rt = gpu.run_op(inp, ref, True, 4.0, 0.2, 1.0, reverse)
+        st, (vk, vi, pv, pw) = gpu.export_op(ws, call, rt)
+        gpu.assert_structure_equal(vk, vi, pv, pw, items, why)
+        gpu.assert_outputs_close(out.cpu().numpy(), want, why)
+
+
+def test_wide_rows_on_the_positions_path(gpu, oracle):
+    """vd 22 with features given as positions (pd 16 and pd 5): tiles are runs of points, the input block
+    goes to the padded rows by 4-byte copies."""
+    import torch
+    import permutohedral_lattice_b200 as plb
+    rng = np.random.default_rng(29)
+    for pd, n in ((16, 700), (5, 1000)):
+        pos = (rng.standard_normal((2, n, pd)) * 1.2).astype(np.float32)
+        inp = rng.random((2, n, 21), dtype=np.float32)
+        out, ws = plb.filter_positions(torch.from_numpy(inp).cuda(), torch.from_numpy(pos).cuda())
+        want = np.stack([oracle.filter(inp[i], pos[i], structure=False).out for i in range(2)])
+        gpu.assert_outputs_close(out.cpu().numpy(), want, "positions pd %d vd 22" % pd)
+
+
 def test_empty_inputs(gpu):
     import torch
     import permutohedral_lattice_b200 as plb
