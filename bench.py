@@ -252,7 +252,7 @@ def run_reference(args, rank, world):
         "e2e": {"value": value, "unit": "Mpixels/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
-    print(json.dumps(line), flush=True)
+    emit_line(line)
 
 
 def main():
@@ -517,10 +517,44 @@ def main():
         info.pop("seconds", None)
         line["cpu_baseline"] = info
     if rank == 0:
-        print(json.dumps(line), flush=True)
+        emit_line(line)
     if world > 1:
         dist.destroy_process_group()
 
 
+class _StdoutToStderr:
+    """While the benchmark runs, file descriptor 1 points at stderr, so that nothing a native library
+    prints (NCCL announces its version on stdout) can precede the JSON line; `emit` writes to the real
+    stdout."""
+
+    def __enter__(self):
+        sys.stdout.flush()
+        self.saved = os.dup(1)
+        os.dup2(2, 1)
+        return self
+
+    def emit(self, text):
+        sys.stdout.flush()
+        os.write(self.saved, (text + "\n").encode())
+
+    def __exit__(self, *exc):
+        sys.stdout.flush()
+        os.dup2(self.saved, 1)
+        os.close(self.saved)
+        return False
+
+
+_OUT = None
+
+
+def emit_line(line):
+    text = json.dumps(line)
+    if _OUT is not None:
+        _OUT.emit(text)
+    else:
+        print(text, flush=True)
+
+
 if __name__ == "__main__":
-    main()
+    with _StdoutToStderr() as _OUT:
+        main()
