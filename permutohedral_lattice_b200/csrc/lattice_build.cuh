@@ -28,16 +28,19 @@ build_tiles(Geom g, const R* __restrict__ positions, const R* __restrict__ refer
     Key<KW>* keys_s = reinterpret_cast<Key<KW>*>(smem_raw);
     int* hslots = reinterpret_cast<int*>(smem_raw + sizeof(Key<KW>) * SPLATS);
     u16* lidx_s = reinterpret_cast<u16*>(smem_raw + sizeof(Key<KW>) * SPLATS + sizeof(int) * LS);
-    __shared__ int nloc_s, base_s;
+    __shared__ int cnt_s[PD + 1], base_s;   // entries per remainder; first global entry of the tile
 
     PhaseClock pc(0);
     const TilePos tpos = this_tile(g);
     const int tid = threadIdx.x, tile = tpos.tile;
     for (int i = tid; i < LS; i += TP) hslots[i] = -1;
-    if (tid == 0) nloc_s = 0;
+    if (tid <= PD) cnt_s[tid] = 0;
 
     int item, pix, po, py, px;
     const bool valid = tile_point(g, tpos, tid, item, pix, po, py, px);
+    u32 slot[PD + 1];   // home slot of each key in the tile's hash, computed while the key is in registers
+#pragma unroll
+    for (int r = 0; r <= PD; r++) slot[r] = 0;
     if (valid) {
         R f[PD];
         R w[PD + 1];
@@ -65,6 +68,7 @@ build_tiles(Geom g, const R* __restrict__ positions, const R* __restrict__ refer
         for (int i = 0; i < PD; i++) key_set<KW>(k, i, (u16)(s.rem0[i] + 0x8000));
         key_set<KW>(k, PD, (u16)item);
         keys_s[tid] = k;
+        slot[0] = tile_hash<KW>(k) & (LS - 1);
 #pragma unroll
         for (int r = 1; r <= PD; r++) {
 #pragma unroll
@@ -73,6 +77,7 @@ build_tiles(Geom g, const R* __restrict__ positions, const R* __restrict__ refer
 #pragma unroll
             for (int j = 0; j < KW; j++) k.w[j] += coord_ones<PD>(j);
             keys_s[r * TP + tid] = k;
+            slot[r] = tile_hash<KW>(k) & (LS - 1);
         }
     }
     __syncthreads();
@@ -83,17 +88,11 @@ build_tiles(Geom g, const R* __restrict__ positions, const R* __restrict__ refer
     // the rest walk on one at a time.
     int rep[PD + 1];
     {
-        u32 slot[PD + 1];
         int cand[PD + 1];
 #pragma unroll
         for (int r = 0; r <= PD; r++) {
             rep[r] = -1;
-            slot[r] = 0;
-            cand[r] = -1;
-            if (valid) {
-                slot[r] = tile_hash<KW>(keys_s[r * TP + tid]) & (LS - 1);
-                cand[r] = hslots[slot[r]];
-            }
+            cand[r] = valid ? hslots[slot[r]] : -1;
         }
 #pragma unroll
         for (int r = 0; r <= PD; r++) {
@@ -128,22 +127,38 @@ build_tiles(Geom g, const R* __restrict__ positions, const R* __restrict__ refer
     }
     __syncthreads();
     pc.mark();
-    // number the tile's entries: one shared-memory atomic per warp and remainder, not per owner
+    // Number the tile's entries remainder by remainder (all entries of remainder 0 first, ...: the splat
+    // stage, which walks the tile's splats in entry order, measured 4 % faster with this order than with
+    // entries grouped by warp).  Per warp ONE shared-memory atomic instruction: lane r adds the warp's
+    // number of new remainder-r entries to counter r.  The index stored now is relative to the
+    // remainder's segment; the segment starts are known after the barrier.
+    {
+        const int lane = tid & 31;
+        unsigned owners[PD + 1];
+        int mine = 0;
 #pragma unroll
-    for (int r = 0; r <= PD; r++) {
-        const bool own = valid && rep[r] == r * TP + tid;
-        const unsigned owners = __ballot_sync(0xFFFFFFFFu, own);
-        if (owners) {
-            const int lane = tid & 31, leader = __ffs(owners) - 1;
-            int first = 0;
-            if (lane == leader) first = atomicAdd(&nloc_s, __popc(owners));
-            first = __shfl_sync(0xFFFFFFFFu, first, leader);
-            if (own) lidx_s[r * TP + tid] = (u16)(first + __popc(owners & ((1u << lane) - 1u)));
+        for (int r = 0; r <= PD; r++) {
+            owners[r] = __ballot_sync(0xFFFFFFFFu, valid && rep[r] == r * TP + tid);
+            mine = (lane == r) ? __popc(owners[r]) : mine;
+        }
+        int first = 0;
+        if (lane <= PD && mine) first = atomicAdd(&cnt_s[lane], mine);
+#pragma unroll
+        for (int r = 0; r <= PD; r++) {
+            const int first_r = __shfl_sync(0xFFFFFFFFu, first, r);
+            if ((owners[r] >> lane) & 1u)
+                lidx_s[r * TP + tid] = (u16)(first_r + __popc(owners[r] & ((1u << lane) - 1u)));
         }
     }
     __syncthreads();
+    int seg[PD + 1];   // first entry of each remainder's segment
+    int cnt = 0;
+#pragma unroll
+    for (int r = 0; r <= PD; r++) {
+        seg[r] = cnt;
+        cnt += cnt_s[r];
+    }
     if (tid == 0) {
-        int cnt = nloc_s;
         u32 base = atomicAdd(&hdr->num_entries, (u32)cnt);
         if ((u64)base + (u64)cnt > (u64)max_entries) {
             atomicOr(&hdr->status, 1u << PL_CAPACITY_EXCEEDED);
@@ -163,7 +178,7 @@ build_tiles(Geom g, const R* __restrict__ positions, const R* __restrict__ refer
         const int me = r * TP + tid;
         u16 l = 0;
         if (valid && rep[r] >= 0) {
-            l = lidx_s[rep[r]];
+            l = (u16)(seg[r] + lidx_s[rep[r]]);   // the representative has the same remainder
             if (rep[r] == me && base >= 0) list_keys[(size_t)base + l] = keys_s[me];
         }
         rec_tile[me] = l;
