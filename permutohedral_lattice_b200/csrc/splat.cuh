@@ -364,14 +364,16 @@ splat_tiles_rows(Geom g, const float* __restrict__ input, Header* hdr, const int
         const float4* in4 = reinterpret_cast<const float4*>(in_s) + h;
         float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
         int cur = (int)(sp[0].x >> 16);
+        u32 vcur = list_ref[base + cur];   // vertex of the running entry, fetched when the run starts
 #pragma unroll 4
         for (int i = 0; i < count; i++) {
             const uint2 pw = sp[i];
             const int e = (int)(pw.x >> 16);
             if (e != cur) {
-                red_add_v4(v0 + (size_t)list_ref[base + cur] * VP + 4 * h, acc);
+                red_add_v4(v0 + (size_t)vcur * VP + 4 * h, acc);
                 acc = make_float4(0.f, 0.f, 0.f, 0.f);
                 cur = e;
+                vcur = list_ref[base + cur];
             }
             const float wt = __uint_as_float(pw.y);
             const float4 x = in4[(pw.x & 0xFFFFu) * LR];
@@ -380,7 +382,7 @@ splat_tiles_rows(Geom g, const float* __restrict__ input, Header* hdr, const int
             acc.z = PL_FMA(wt, x.z, acc.z);
             acc.w = PL_FMA(wt, x.w, acc.w);
         }
-        red_add_v4(v0 + (size_t)list_ref[base + cur] * VP + 4 * h, acc);
+        red_add_v4(v0 + (size_t)vcur * VP + 4 * h, acc);
     }
     pc.mark(true);
 }
