@@ -169,19 +169,24 @@ build_tiles(Geom g, const R* __restrict__ positions, const R* __restrict__ refer
             tile_info[tile] = make_int2((int)base, cnt);
         }
     }
-    __syncthreads();
-    pc.mark();
-    const int base = base_s;
+    // the per-splat records do not need the tile's first global entry: they are written while thread
+    // 0's atomic is in flight
+    u16 lfin[PD + 1];
     u16* rec_tile = rec + (size_t)tile * SPLATS;
 #pragma unroll
     for (int r = 0; r <= PD; r++) {
-        const int me = r * TP + tid;
-        u16 l = 0;
-        if (valid && rep[r] >= 0) {
-            l = (u16)(seg[r] + lidx_s[rep[r]]);   // the representative has the same remainder
-            if (rep[r] == me && base >= 0) list_keys[(size_t)base + l] = keys_s[me];
+        lfin[r] = (valid && rep[r] >= 0) ? (u16)(seg[r] + lidx_s[rep[r]]) : (u16)0;   // the representative has the same remainder
+        rec_tile[r * TP + tid] = lfin[r];
+    }
+    __syncthreads();
+    pc.mark();
+    const int base = base_s;
+    if (valid && base >= 0) {
+#pragma unroll
+        for (int r = 0; r <= PD; r++) {
+            const int me = r * TP + tid;
+            if (rep[r] == me) list_keys[(size_t)base + lfin[r]] = keys_s[me];
         }
-        rec_tile[me] = l;
     }
     pc.mark(true);
 }
