@@ -201,10 +201,6 @@ slice_tiles_generic(Geom g, float* __restrict__ output, const Header* hdr, const
     const int base = info.x, cnt = info.y;
     const int nrows = min(cnt, rows_cap);
     const float4* v4 = reinterpret_cast<const float4*>(vsrc);
-    for (int i = tid; i < nrows * QPR; i += TP) {
-        const int lrow = i / QPR, q = i - lrow * QPR;
-        cp_async16(rows4 + i, v4 + (size_t)list_ref[base + lrow] * QPR + q);
-    }
     int item, pix;
     const bool valid = tile_point(g, tpos, tid, item, pix);
     prow_s[tid] = valid ? item * g.n + pix : -1;
@@ -216,6 +212,23 @@ slice_tiles_generic(Geom g, float* __restrict__ output, const Header* hdr, const
     for (int r = 0; r <= PD; r++) {
         l[r] = valid ? rec_tile[r * TP + tid] : 0;
         w[r] = valid ? recw_tile[r * TP + tid] : 0.f;
+    }
+    {   // row staging: vertex numbers of CH rows first, then the copies that depend on them (see slice_tiles_fast)
+        constexpr int CH = 8;
+        const int total = nrows * QPR;
+        for (int i0 = tid; i0 < total; i0 += CH * TP) {
+            u32 vtx[CH];
+#pragma unroll
+            for (int c = 0; c < CH; c++) {
+                const int i = i0 + c * TP;
+                vtx[c] = (i < total) ? list_ref[base + i / QPR] : 0u;
+            }
+#pragma unroll
+            for (int c = 0; c < CH; c++) {
+                const int i = i0 + c * TP;
+                if (i < total) cp_async16(rows4 + i, v4 + (size_t)vtx[c] * QPR + (i - (i / QPR) * QPR));
+            }
+        }
     }
     cp_async_wait_all();
     __syncthreads();

@@ -255,6 +255,17 @@ splat_tiles_rows(Geom g, const float* __restrict__ input, Header* hdr, const int
     int item, pix;
     const bool valid = tile_point(g, tpos, tid, item, pix);
     prow_s[tid] = valid ? item * g.n + pix : -1;
+    // the splat records are loaded first: they depend on nothing but the tile number, so their latency
+    // overlaps that of the tile's entry range above
+    float w[PD + 1];
+    int l[PD + 1];
+    const u16* rec_tile = rec + (size_t)tile * SPLATS;
+    const float* recw_tile = rec_w + (size_t)tile * SPLATS;
+#pragma unroll
+    for (int r = 0; r <= PD; r++) {
+        l[r] = valid ? rec_tile[r * TP + tid] : 0;
+        w[r] = valid ? recw_tile[r * TP + tid] : 0.f;
+    }
     for (int i = tid; i < nloc; i += TP) cur_s[i] = 0;
     if (bulk_ok && tid == 0) mbar_init(&bar, 1);
     const int nvalid = __syncthreads_count(valid);
@@ -295,15 +306,6 @@ splat_tiles_rows(Geom g, const float* __restrict__ input, Header* hdr, const int
         }
     }
 
-    float w[PD + 1];
-    int l[PD + 1];
-    const u16* rec_tile = rec + (size_t)tile * SPLATS;
-    const float* recw_tile = rec_w + (size_t)tile * SPLATS;
-#pragma unroll
-    for (int r = 0; r <= PD; r++) {
-        l[r] = valid ? rec_tile[r * TP + tid] : 0;
-        w[r] = valid ? recw_tile[r * TP + tid] : 0.f;
-    }
     SplatCommon<PD>::template sort_splats<WL>(valid, l, w, nloc, sorted_s, cur_s, nullptr, wsum_s);
     pc.mark();
     if (bulk_ok) {
