@@ -66,18 +66,10 @@ struct SplatCommon {
         }
         if (lane == 31) wsum_s[warp] = incl;
         __syncthreads();
-        if (warp == 0) {
-            const int v = (lane < NW) ? wsum_s[lane] : 0;
-            int vi = v;
+        int before = 0;   // entries' splats counted by the warps below this one (NW broadcast reads, no second barrier)
 #pragma unroll
-            for (int d = 1; d < 32; d <<= 1) {
-                const int t = __shfl_up_sync(0xFFFFFFFFu, vi, d);
-                if (lane >= d) vi += t;
-            }
-            wsum_s[lane] = vi - v;
-        }
-        __syncthreads();
-        const int excl = incl - sum + wsum_s[warp];
+        for (int q = 0; q < NW; q++) before += (q < warp) ? wsum_s[q] : 0;
+        const int excl = incl - sum + before;
 #pragma unroll
         for (int r = 0; r <= PD; r++) {
             const int i = tid * (PD + 1) + r;
