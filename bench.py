@@ -34,7 +34,7 @@ METRIC = "Mpixels/s fwd+bwd (pd=5, vd=22 CRF)"
 # DRAM bytes per point and launch (dram__bytes_read.sum + dram__bytes_write.sum) of the kernels of configuration 2,
 # from the one-pass ncu capture of the full-size workload summarised in
 # profiles/dram_traffic_c2_dense_crf_16x512.txt; traffic is proportional to the number of points.
-NCU_DRAM_BYTES_PER_POINT_C2 = {"build_tiles": 49.1, "splat_tiles": 149.7, "slice_tiles": 125.6, "blur_axis": 20.5}
+NCU_DRAM_BYTES_PER_POINT_C2 = {"build_tiles": 49.2, "splat_tiles": 149.7, "slice_tiles": 125.4, "blur_axis": 20.4}
 FALLBACK_HBM_GBS = 6650.0
 
 
