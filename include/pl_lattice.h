@@ -39,9 +39,10 @@ typedef enum pl_mode {
 typedef struct pl_stats {
     int64_t num_vertices;  /* distinct lattice vertices over the whole batch */
     int64_t num_entries;   /* tile-local vertex entries (>= num_vertices) */
-    int64_t table_slots;   /* hash table capacity chosen on the device for this call */
+    int64_t table_slots;   /* hash table capacity chosen on the device for this call (direct indexing: the
+                              dense index's slot count rounded up to a power of two) */
     int32_t device_status; /* pl_status recorded by the kernels (PL_OK, PL_CAPACITY_EXCEEDED, ...) */
-    int32_t reserved;
+    int32_t direct_index;  /* 1: vertices were located by direct indexing (spatial-only call), 0: hash table */
 } pl_stats;
 
 /* 1 if position dimension pd and value dimension vd (= input channels + 1) can be filtered.
@@ -177,6 +178,15 @@ int pl_export_lattice_f64(const void* workspace, const double* positions, const 
  * The reference only times whole calls with std::clock (Tests/test_bilateral_gpu.cpp:32-36). */
 #define PL_NUM_STAGE_EVENTS 6
 int pl_profile_next_call(void** stage_events);
+
+/* Spatial-only calls (bilateral == 0: the features are the grid coordinates divided by theta_gamma,
+ * src/LatticeFilterKernel.cpp:137-142, compute_spatial_kernel_gpu in Tests/PermutohedralLatticeGPU.cu:33-42)
+ * locate their vertices by direct indexing instead of hashing whenever the dense index fits the
+ * workspace's table region: the region of the lattice such a call can touch is known from the grid's
+ * size alone.  Results are identical either way.  This process-wide developer switch turns that path
+ * off (enable == 0) or back on, for A/B timing and tests; it returns the previous setting.  The
+ * reference hashes always (src/PermutohedralLatticeGPU.cuh:76-143). */
+int pl_debug_direct_index(int enable);
 
 /* Copies the counters of the last call that used `workspace` to the host.  SYNCHRONISES `stream`.
  * Returns PL_OK when read; the call's own outcome is stats->device_status.

@@ -44,7 +44,8 @@ struct Header {   // first 256 bytes of the workspace
     u32 status;
     u32 table_log2;
     u32 absmax_bits;   // deterministic mode: bit pattern of max |input| (non-negative floats order as integers)
-    u32 pad[59];
+    u32 direct;        // 1: vertices were found by direct indexing (spatial-only call), 0: through the hash table
+    u32 pad[58];
 };
 
 struct Layout {   // byte offsets into the workspace

@@ -32,6 +32,7 @@
 
 #include "common.cuh"
 #include "lattice_build.cuh"
+#include "direct_index.cuh"
 #include "splat.cuh"
 #include "blur_slice.cuh"
 #include "export.cuh"
@@ -154,6 +155,51 @@ static int make_layout(Layout& L, const Geom& g, int pd, int vd, int64_t max_ent
     if (real_bytes == 4) off += align_up(sizeof(long long) * (size_t)padded_vd(vd) * E);
     L.total = off;
     return PL_OK;
+}
+
+// Developer switch (pl_debug_direct_index): 0 sends spatial-only calls through the hash table too.
+static int g_direct_index_enabled = 1;
+
+// Bounds of the vertex keys a spatial-only call can create, and the dense index built on them.
+// Feature j of a point is c_j / spatial_std with 0 <= c_j < sdims[j]; the elevated coordinates
+// (src/PermutohedralLatticeCPU.h:220-231) are el_0 = sum_j cf_j and el_i = sum_{j>=i} cf_j - i cf_{i-1}
+// with cf_j = feature_j * scale_j >= 0, so each lies in an interval known from the grid's size.  A
+// vertex of the enclosing simplex is within 2 (pd+1) of the point in every coordinate; the margin below
+// is wider than that and also covers the rounding of the float arithmetic.
+static bool make_direct(Direct& d, const Geom& g, int pd, const Layout& L) {
+    memset(&d, 0, sizeof(d));
+    if (!g_direct_index_enabled || g.from_positions || g.R != 0 || pd != g.n_sdims || pd > MAX_SDIMS) return false;
+    if (!(g.spatial_std > 0.f) || !std::isfinite(g.spatial_std)) return false;
+    double cf[MAX_SDIMS];
+    for (int j = 0; j < pd; j++) {
+        if (g.sdims[j] < 1) return false;
+        cf[j] = (double)(g.sdims[j] - 1) / (double)g.spatial_std * (double)g.scale[j];
+        if (!(cf[j] < 30000.0)) return false;
+    }
+    const double margin = 3.0 * (pd + 1) + 2.0;
+    double sum_all = 0;
+    for (int j = 0; j < pd; j++) sum_all += cf[j];
+    if (sum_all + margin > 30000.0) return false;   // coordinates are 16-bit, as in the reference
+    d.lo0 = (int)std::floor(-margin);
+    d.ext[0] = (u32)((int)std::ceil(sum_all + margin) - d.lo0 + 1);
+    u64 cells = d.ext[0];
+    for (int i = 1; i < pd; i++) {
+        // k_i - k_0 follows el_i - el_0 = -(i cf_{i-1} + sum_{j<i} cf_j)
+        double span = i * cf[i - 1];
+        for (int j = 0; j < i; j++) span += cf[j];
+        const int lo = (int)std::floor((-span - 2 * margin) / (pd + 1));
+        const int hi = (int)std::ceil((2 * margin) / (pd + 1));
+        d.dlo[i] = lo;
+        d.ext[i] = (u32)(hi - lo + 1);
+        cells *= d.ext[i];
+        if (cells > (1ull << 32)) return false;
+    }
+    d.cells = cells;
+    d.slots = cells * (u64)g.batch;
+    // 32-bit slots in the memory of the hash table (64-bit slots); entry numbers must fit a slot
+    if (d.slots > 2 * L.table_slots || d.slots >= 0xFFFFFFFFull) return false;
+    d.on = 1;
+    return true;
 }
 
 // Launch grid of the tile kernels (see this_tile).
@@ -293,11 +339,27 @@ static int run_filter(const Geom& g, float* output, const float* input, const fl
         build_tiles<PD><<<tile_grid(g), TP, Cfg<PD>::BUILD_SMEM, st>>>(
             g, positions, reference, hdr, tile_info, rec, rec_w, list_keys, (u32)L.max_entries);
         if (ev) PL_CUDA(cudaEventRecord(ev[1], st));
-        clear_table<<<wide, 256, 0, st>>>(hdr, table, (u32)table_log2);
-        insert_entries<KW><<<wide, 256, 0, st>>>(hdr, table, list_keys, list_ref, vid, vowner);
-        link_vertices<<<wide, 256, 0, st>>>(hdr, list_ref, vid, nbr, v0, v64, L.max_entries, PD,
-                                            (phases & PH_APPLY) ? vd : 0);
-        link_neighbours<PD><<<wide, 256, 0, st>>>(hdr, table, list_keys, vid, vowner, nbr, L.max_entries);
+        Direct direct;
+        bool use_direct = false;
+        if constexpr (PD <= MAX_SDIMS) use_direct = make_direct(direct, g, PD, L);
+        if constexpr (PD <= MAX_SDIMS) {
+            if (use_direct) {
+                u32* table32 = reinterpret_cast<u32*>(table);
+                clear_direct<<<wide, 256, 0, st>>>(hdr, table32, direct.slots);
+                insert_direct<PD><<<wide, 256, 0, st>>>(hdr, direct, table32, list_keys, list_ref, vid, vowner);
+                link_vertices<<<wide, 256, 0, st>>>(hdr, list_ref, vid, nbr, v0, v64, L.max_entries, PD,
+                                                    (phases & PH_APPLY) ? vd : 0);
+                link_neighbours_direct<PD><<<wide, 256, 0, st>>>(hdr, direct, table32, list_keys, vid, vowner, nbr,
+                                                                 L.max_entries);
+            }
+        }
+        if (!use_direct) {
+            clear_table<<<wide, 256, 0, st>>>(hdr, table, (u32)table_log2);
+            insert_entries<KW><<<wide, 256, 0, st>>>(hdr, table, list_keys, list_ref, vid, vowner);
+            link_vertices<<<wide, 256, 0, st>>>(hdr, list_ref, vid, nbr, v0, v64, L.max_entries, PD,
+                                                (phases & PH_APPLY) ? vd : 0);
+            link_neighbours<PD><<<wide, 256, 0, st>>>(hdr, table, list_keys, vid, vowner, nbr, L.max_entries);
+        }
         if (ev) PL_CUDA(cudaEventRecord(ev[2], st));
     } else {
         if (ev) { PL_CUDA(cudaEventRecord(ev[1], st)); }
@@ -832,6 +894,12 @@ int pl_debug_phase_cycles(unsigned long long* out) {
 }
 #endif
 
+int pl_debug_direct_index(int enable) {
+    const int was = g_direct_index_enabled;
+    g_direct_index_enabled = enable ? 1 : 0;
+    return was;
+}
+
 int pl_profile_next_call(void** stage_events) {
     g_stage_events = reinterpret_cast<cudaEvent_t*>(stage_events);
     return PL_OK;
@@ -848,7 +916,7 @@ int pl_lattice_stats(const void* workspace, pl_stats* stats, void* stream) {
     stats->device_status = PL_OK;
     for (int code = PL_INVALID_ARGUMENT; code <= PL_INTERNAL_ERROR; code++)
         if (h.status & (1u << code)) stats->device_status = code;
-    stats->reserved = 0;
+    stats->direct_index = (int32_t)h.direct;
     return PL_OK;
 }
 
