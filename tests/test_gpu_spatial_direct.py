@@ -26,27 +26,31 @@ def hashed_path():
     capi.lib().pl_debug_direct_index(was)
 
 
+# (spatial shape, channels, theta_gamma, direct indexing expected).  The last three are so small or so
+# sparse that the dense index (whose bounds carry a fixed margin) outgrows the table region of the
+# workspace: the call then hashes, and must give the same results.
 CASES = [
-    ((64, 48), 4, 3.0),        # 2-D image, the CRF smoothness kernel
-    ((33, 17), 21, 1.0),       # theta_gamma 1: nearly one vertex per point, wide rows
-    ((40, 56), 2, 8.0),        # coarse lattice
-    ((9, 10, 11), 2, 2.0),     # volume, pd 3
-    ((300,), 1, 5.0),          # 1-D signal, pd 1
-    ((1, 1), 3, 3.0),          # a single point
-    ((3, 4, 5, 6), 2, 1.5),    # four spatial dimensions
-    ((50, 70), 3, 0.37),       # theta_gamma below one: vertices sparser than the dense index
+    ((64, 48), 4, 3.0, True),        # 2-D image, the CRF smoothness kernel
+    ((33, 17), 21, 1.0, True),       # theta_gamma 1: nearly one vertex per point, wide rows
+    ((40, 56), 2, 8.0, True),        # coarse lattice
+    ((24, 20, 22), 2, 2.0, True),    # volume, pd 3
+    ((300,), 1, 5.0, True),          # 1-D signal, pd 1
+    ((1, 1), 3, 3.0, True),          # a single point
+    ((9, 10, 11), 2, 2.0, False),    # tiny volume
+    ((3, 4, 5, 6), 2, 1.5, False),   # four spatial dimensions, a few points each
+    ((50, 70), 3, 0.37, False),      # theta_gamma below one: vertices far sparser than the index
 ]
 
 
-@pytest.mark.parametrize("shape,c,tg", CASES)
-def test_spatial_only_matches_oracle_with_direct_indexing(shape, c, tg, gpu, oracle):
+@pytest.mark.parametrize("shape,c,tg,direct", CASES)
+def test_spatial_only_matches_oracle(shape, c, tg, direct, gpu, oracle):
     rng = np.random.default_rng(5)
     inp = rng.standard_normal((2,) + shape + (c,)).astype(np.float32)
     for reverse in (False, True):
         want, items = oracle.lattice_filter(inp, None, False, 1.0, 1.0, tg, reverse, structure=True)
         out, ws, call, x, r = gpu.run_op(inp, None, False, 1.0, 1.0, tg, reverse)
         st, (vk, vi, pv, pw) = gpu.export_op(ws, call, r)
-        assert st.direct_index == 1, "spatial-only call did not use direct indexing"
+        assert st.direct_index == int(direct)
         gpu.assert_structure_equal(vk, vi, pv, pw, items, str(shape))
         gpu.assert_outputs_close(out.cpu().numpy(), want, str(shape))
 
@@ -84,12 +88,13 @@ def test_small_table_falls_back_to_hashing(gpu, oracle):
     """max_entries shrinks the workspace's table region; when the dense index no longer fits, the call
     hashes, with the same results."""
     rng = np.random.default_rng(8)
-    inp = rng.standard_normal((1, 64, 64, 2)).astype(np.float32)
+    inp = rng.standard_normal((8, 16, 16, 2)).astype(np.float32)
     want = oracle.lattice_filter(inp, None, False, 1.0, 1.0, 16.0, False)
-    out, ws, call, x, r = gpu.run_op(inp, None, False, 1.0, 1.0, 16.0, False, max_entries=1500)
-    st, _ = gpu.export_op(ws, call, r, max_entries=1500)
-    assert st.direct_index == 0
-    gpu.assert_outputs_close(out.cpu().numpy(), want, "hashed fallback")
+    for max_entries, direct in ((0, 1), (200, 0)):
+        out, ws, call, x, r = gpu.run_op(inp, None, False, 1.0, 1.0, 16.0, False, max_entries=max_entries)
+        st, _ = gpu.export_op(ws, call, r, max_entries=max_entries)
+        assert st.direct_index == direct
+        gpu.assert_outputs_close(out.cpu().numpy(), want, "max_entries %d" % max_entries)
 
 
 def test_spatial_only_lattice_reuse(gpu, oracle):
