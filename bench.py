@@ -467,7 +467,8 @@ def main():
             gf.reference.copy_(ref)
         if gb is not None:
             gb.input.copy_(grad)
-            gb.reference.copy_(ref)
+            if ref is not None:
+                gb.reference.copy_(ref)
         for _ in range(3):
             gf.replay()
             if gb is not None:

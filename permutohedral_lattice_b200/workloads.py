@@ -8,6 +8,9 @@ configuration is generated: numpy PCG64 (`default_rng(seed)`), seed = 100 * conf
   c2  16 x 512x512 dense-CRF message passing, 21 channels, theta 80 / 0.0625, pd 5, vd 22, fwd + bwd
   c3  8 x 128^3 volume, 2 channels guided by the clean phantom, theta 5 / 0.1, pd 4, vd 3, fwd + bwd
   c4  8 x 1024x1024, 16-D patch features given as positions, pd 16, vd 4, forward
+  c5  c2's input and gradient through the CRF's smoothness kernel: spatial-only (bilateral=False),
+      theta_gamma 3, pd 2, vd 22, fwd + bwd (not a BASELINE.json configuration; it exercises the
+      direct-indexing path)
 """
 from dataclasses import dataclass, field
 from typing import Optional
@@ -145,7 +148,13 @@ def config4(batch=8, size=1024, pd=16):
                     positions=np.stack(positions))
 
 
-CONFIGS = {0: config0, 1: config1, 2: config2, 3: config3, 4: config4}
+def config5(batch=16, size=512, channels=21):
+    w = config2(batch, size, channels)
+    return Workload("c5_crf_smoothness_%dx%d" % (batch, size), input=w.input, grad=w.grad, bilateral=False,
+                    theta_gamma=3.0, backward=True)
+
+
+CONFIGS = {0: config0, 1: config1, 2: config2, 3: config3, 4: config4, 5: config5}
 
 
 def small(config):
@@ -164,6 +173,8 @@ def small(config):
         w.theta_alpha = 2.0
     elif config == 4:
         w = config4(batch=2, size=48)
+    elif config == 5:
+        w = config5(batch=3, size=64)
     else:
         raise KeyError(config)
     w.name += "_small"
