@@ -6,20 +6,11 @@
 // insert_entries and link_neighbours; everything before and after them is unchanged.
 #pragma once
 #include "common.cuh"
+#include "direct_bounds.h"
 
 namespace pl {
 
-// A lattice point has all its coordinates congruent modulo PD+1, so with k_0 the first stored
-// coordinate, (k_i - k_0) / (PD+1) is an integer.  The dense index of a key is
-//   (((k_0 - lo0) * ext[1] + (k_1 - k_0)/(PD+1) - dlo[1]) * ext[2] + ...) + item * cells.
-struct Direct {
-    int on;
-    int lo0;               // smallest first coordinate
-    int dlo[MAX_SDIMS];    // i >= 1: smallest (k_i - k_0) / (PD+1)
-    u32 ext[MAX_SDIMS];    // extent of each index coordinate
-    u64 cells;             // slots per batch item
-    u64 slots;             // batch * cells
-};
+static_assert(DIRECT_MAX_DIMS == MAX_SDIMS, "the index has one coordinate per spatial dimension");
 
 constexpr u32 DIRECT_EMPTY = 0xFFFFFFFFu;
 

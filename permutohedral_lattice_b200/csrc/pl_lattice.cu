@@ -160,46 +160,12 @@ static int make_layout(Layout& L, const Geom& g, int pd, int vd, int64_t max_ent
 // Developer switch (pl_debug_direct_index): 0 sends spatial-only calls through the hash table too.
 static int g_direct_index_enabled = 1;
 
-// Bounds of the vertex keys a spatial-only call can create, and the dense index built on them.
-// Feature j of a point is c_j / spatial_std with 0 <= c_j < sdims[j]; the elevated coordinates
-// (src/PermutohedralLatticeCPU.h:220-231) are el_0 = sum_j cf_j and el_i = sum_{j>=i} cf_j - i cf_{i-1}
-// with cf_j = feature_j * scale_j >= 0, so each lies in an interval known from the grid's size.  A
-// vertex of the enclosing simplex is within 2 (pd+1) of the point in every coordinate; the margin below
-// is wider than that and also covers the rounding of the float arithmetic.
+// The dense index of a spatial-only call (direct_bounds.h), if the call qualifies and the index fits the
+// table region of the workspace (32-bit slots in the memory of the 64-bit hash slots).
 static bool make_direct(Direct& d, const Geom& g, int pd, const Layout& L) {
     memset(&d, 0, sizeof(d));
-    if (!g_direct_index_enabled || g.from_positions || g.R != 0 || pd != g.n_sdims || pd > MAX_SDIMS) return false;
-    if (!(g.spatial_std > 0.f) || !std::isfinite(g.spatial_std)) return false;
-    double cf[MAX_SDIMS];
-    for (int j = 0; j < pd; j++) {
-        if (g.sdims[j] < 1) return false;
-        cf[j] = (double)(g.sdims[j] - 1) / (double)g.spatial_std * (double)g.scale[j];
-        if (!(cf[j] < 30000.0)) return false;
-    }
-    const double margin = 3.0 * (pd + 1) + 2.0;
-    double sum_all = 0;
-    for (int j = 0; j < pd; j++) sum_all += cf[j];
-    if (sum_all + margin > 30000.0) return false;   // coordinates are 16-bit, as in the reference
-    d.lo0 = (int)std::floor(-margin);
-    d.ext[0] = (u32)((int)std::ceil(sum_all + margin) - d.lo0 + 1);
-    u64 cells = d.ext[0];
-    for (int i = 1; i < pd; i++) {
-        // k_i - k_0 follows el_i - el_0 = -(i cf_{i-1} + sum_{j<i} cf_j)
-        double span = i * cf[i - 1];
-        for (int j = 0; j < i; j++) span += cf[j];
-        const int lo = (int)std::floor((-span - 2 * margin) / (pd + 1));
-        const int hi = (int)std::ceil((2 * margin) / (pd + 1));
-        d.dlo[i] = lo;
-        d.ext[i] = (u32)(hi - lo + 1);
-        cells *= d.ext[i];
-        if (cells > (1ull << 32)) return false;
-    }
-    d.cells = cells;
-    d.slots = cells * (u64)g.batch;
-    // 32-bit slots in the memory of the hash table (64-bit slots); entry numbers must fit a slot
-    if (d.slots > 2 * L.table_slots || d.slots >= 0xFFFFFFFFull) return false;
-    d.on = 1;
-    return true;
+    if (!g_direct_index_enabled || g.from_positions || g.R != 0 || pd != g.n_sdims) return false;
+    return direct_bounds(d, pd, g.sdims, g.spatial_std, g.scale, g.batch, 2 * L.table_slots);
 }
 
 // Launch grid of the tile kernels (see this_tile).
