@@ -399,13 +399,33 @@ static int run_filter_f64(const Geom& g, double* output, const double* input, co
 
     build_tiles<PD, double><<<tile_grid(g), TP, Cfg<PD>::BUILD_SMEM, st>>>(
         g, positions, reference, hdr, tile_info, rec, rec_w, list_keys, (u32)L.max_entries);
-    clear_table<<<wide, 256, 0, st>>>(hdr, table, (u32)table_log2);
-    insert_entries<KW><<<wide, 256, 0, st>>>(hdr, table, list_keys, list_ref, vid, vowner);
+    // spatial-only calls index their vertices directly, as the float calls do (the key bounds hold for
+    // either arithmetic: the margin is far wider than any rounding)
+    Direct direct;
+    bool use_direct = false;
+    if constexpr (PD <= MAX_SDIMS) use_direct = make_direct(direct, g, PD, L);
+    u32* table32 = reinterpret_cast<u32*>(table);
+    if constexpr (PD <= MAX_SDIMS) {
+        if (use_direct) {
+            clear_direct<<<wide, 256, 0, st>>>(hdr, table32, direct.slots);
+            insert_direct<PD><<<wide, 256, 0, st>>>(hdr, direct, table32, list_keys, list_ref, vid, vowner);
+        }
+    }
+    if (!use_direct) {
+        clear_table<<<wide, 256, 0, st>>>(hdr, table, (u32)table_log2);
+        insert_entries<KW><<<wide, 256, 0, st>>>(hdr, table, list_keys, list_ref, vid, vowner);
+    }
     // rows of vp doubles are zeroed through the 64-bit branch (vp cells of 8 bytes per vertex)
     link_vertices<<<wide, 256, 0, st>>>(hdr, list_ref, vid, nbr, nullptr, reinterpret_cast<long long*>(v0),
                                         L.max_entries, PD, 0);
     zero_rows<<<wide, 256, 0, st>>>(hdr, nullptr, reinterpret_cast<long long*>(v0), vp);
-    link_neighbours<PD><<<wide, 256, 0, st>>>(hdr, table, list_keys, vid, vowner, nbr, L.max_entries);
+    if constexpr (PD <= MAX_SDIMS) {
+        if (use_direct)
+            link_neighbours_direct<PD><<<wide, 256, 0, st>>>(hdr, direct, table32, list_keys, vid, vowner, nbr,
+                                                             L.max_entries);
+    }
+    if (!use_direct)
+        link_neighbours<PD><<<wide, 256, 0, st>>>(hdr, table, list_keys, vid, vowner, nbr, L.max_entries);
     splat_tiles_f64<PD><<<tile_grid(g), TP, Splat64<PD>::BYTES, st>>>(g, input, hdr, tile_info, rec, rec_w,
                                                                       list_ref, v0, vd);
     double* src = v0;

@@ -96,12 +96,24 @@ def test_op_path_f64_matches_oracle(shape, r, c, gpu, oracle):
         close64(out.cpu().numpy(), want, "f64 " + str(shape))
 
 
-def test_spatial_only_f64(gpu, oracle):
+@pytest.mark.parametrize("shape,tg", [((30, 41), 2.5), ((12, 14, 16), 1.5)])
+def test_spatial_only_f64(shape, tg, gpu, oracle):
+    """bilateral=False in double: vertices located by direct indexing, as in float."""
+    import torch
+    import permutohedral_lattice_b200 as plb
     rng = np.random.default_rng(5)
-    inp = rng.random((2, 30, 41, 3))
-    want = oracle.lattice_filter(inp, None, False, 1.0, 1.0, 2.5, False, dtype=np.float64)
-    out = gpu.run_op(inp, None, False, 1.0, 1.0, 2.5, False)[0]
-    close64(out.cpu().numpy(), want, "spatial f64")
+    inp = rng.random((2,) + shape + (3,))
+    for reverse in (False, True):
+        want, items = oracle.lattice_filter(inp, None, False, 1.0, 1.0, tg, reverse, structure=True,
+                                            dtype=np.float64)
+        out, ws, call, x, rt = gpu.run_op(inp, None, False, 1.0, 1.0, tg, reverse)
+        st = plb.lattice_stats(ws)
+        assert st.device_status == 0 and st.direct_index == 1
+        vk, vi, pv, pw = plb.export_lattice(ws, st, call.batch, call.n, call.pd, call.vd, reference=rt,
+                                            sdims=call.sdims, spatial_std=call.spatial_std,
+                                            feature_std=call.feature_std, dtype=torch.float64)
+        gpu.assert_structure_equal(vk, vi, pv, pw, items, "spatial f64 " + str(shape))
+        close64(out.cpu().numpy(), want, "spatial f64 " + str(shape))
 
 
 def test_positions_path_f64_pd16(gpu, oracle):
