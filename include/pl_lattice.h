@@ -179,6 +179,19 @@ int pl_export_lattice_f64(const void* workspace, const double* positions, const 
 #define PL_NUM_STAGE_EVENTS 6
 int pl_profile_next_call(void** stage_events);
 
+/* The pointwise half of one dense-CRF mean-field update, in one pass over memory (all pointers device,
+ * [n_points][n_labels] floats, channels last as everywhere else):
+ *   q_out = softmax over labels ( -unaries - (bilateral_weight * q_bilateral + spatial_weight * q_spatial) @ compatibility )
+ * q_bilateral / q_spatial are the current label distributions filtered through the appearance and the
+ * smoothness kernel (pl_lattice_apply_f32 on two lattices built once per image); compatibility is
+ * [n_labels][n_labels] row-major, or NULL for the Potts model (1 - identity).  n_labels <= 128.
+ * q_out must not overlap the inputs.  No counterpart in the reference: it ships no CRF code, its README
+ * (README.md:15-16) names CRF-as-RNN as the user the filter was written for; this is the step either
+ * side of the filter in that user. */
+int pl_crf_update_f32(float* q_out, const float* unaries, const float* q_bilateral, const float* q_spatial,
+                      const float* compatibility, float bilateral_weight, float spatial_weight,
+                      int64_t n_points, int n_labels, void* stream);
+
 /* Spatial-only calls (bilateral == 0: the features are the grid coordinates divided by theta_gamma,
  * src/LatticeFilterKernel.cpp:137-142, compute_spatial_kernel_gpu in Tests/PermutohedralLatticeGPU.cu:33-42)
  * locate their vertices by direct indexing instead of hashing whenever the dense index fits the

@@ -15,7 +15,7 @@ CSRC = os.path.join(PKG, "csrc")
 LIB = os.path.join(PKG, "libpl_lattice.so")
 SOURCES = [os.path.join(CSRC, "pl_lattice.cu")]
 HEADERS = [os.path.join(CSRC, h) for h in ("simplex.cuh", "common.cuh", "lattice_build.cuh", "splat.cuh",
-                                             "blur_slice.cuh", "export.cuh", "fp64.cuh", "direct_index.cuh", "direct_bounds.h")] + [
+                                             "blur_slice.cuh", "export.cuh", "fp64.cuh", "direct_index.cuh", "direct_bounds.h", "crf.cuh")] + [
     os.path.join(ROOT, "include", "pl_lattice.h")]
 
 

@@ -25,7 +25,7 @@ EXPORTED_SYMBOLS = [
     "pl_export_lattice", "pl_profile_next_call", "pl_lattice_filter_f32_noalloc",
     "pl_lattice_build_f32", "pl_lattice_build_positions_f32", "pl_lattice_apply_f32",
     "pl_workspace_bytes_f64", "pl_compute_positions_f64", "pl_filter_f64", "pl_lattice_filter_f64",
-    "pl_export_lattice_f64", "pl_debug_direct_index",
+    "pl_export_lattice_f64", "pl_debug_direct_index", "pl_crf_update_f32",
 ]
 STATIC_SCRATCH_BYTES = 64 << 20
 NUM_STAGE_EVENTS = 6
@@ -85,6 +85,7 @@ def lib():
         L.pl_export_lattice_f64.argtypes = [vp, vp, vp, i, i, i, i, i, ip, i, d, d, i64, i64, vp, vp, vp,
                                             vp, vp]
         L.pl_debug_direct_index.argtypes = [i]
+        L.pl_crf_update_f32.argtypes = [vp, vp, vp, vp, vp, f, f, i64, i, vp]
         L.pl_profile_next_call.argtypes = [ctypes.POINTER(ctypes.c_void_p)]
         _lib = L
     return _lib

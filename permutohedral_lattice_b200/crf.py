@@ -12,11 +12,13 @@ guide image I[B, *S, R]:
     Q        = softmax(-U - pairwise)
 
 Both lattices depend on the image only: they are built once (`Lattice`) and applied in every iteration.
-The softmax and the small matrix product run as torch operations on the same stream.
+Everything after the two filters (weights, compatibility product, unaries, softmax) is one fused kernel,
+pl_crf_update_f32: one read of Qb, Qs and U and one write of Q per iteration.
 """
 import torch
 
-from .lattice_filter import Lattice
+from . import capi
+from .lattice_filter import Lattice, _stream_handle
 
 
 class DenseCRF:
@@ -29,13 +31,28 @@ class DenseCRF:
         self.spatial = Lattice(None, shape, False, 1.0, 1.0, theta_gamma, max_channels=n_labels)
         self.bilateral_weight = float(bilateral_weight)
         self.spatial_weight = float(spatial_weight)
-        if compatibility is None:
-            compatibility = 1.0 - torch.eye(n_labels, dtype=torch.float32, device=image.device)
-        self.compatibility = compatibility.to(device=image.device, dtype=torch.float32)
+        # None: Potts model (1 - identity), which the kernel evaluates without the L x L product
+        self.compatibility = None if compatibility is None else compatibility.to(
+            device=image.device, dtype=torch.float32).contiguous()
+        if self.compatibility is not None and tuple(self.compatibility.shape) != (self.n_labels, self.n_labels):
+            raise ValueError("compatibility must be [n_labels, n_labels]")
 
     def step(self, q, unaries):
-        message = self.bilateral_weight * self.bilateral.apply(q) + self.spatial_weight * self.spatial.apply(q)
-        return torch.softmax(-unaries - message @ self.compatibility, dim=-1)
+        if q.shape[-1] != self.n_labels or unaries.shape != q.shape:
+            raise ValueError("q and unaries must be [B, *S, n_labels]")
+        if unaries.dtype != torch.float32 or not unaries.is_cuda:
+            raise TypeError("unaries must be a float32 CUDA tensor")
+        unaries = unaries.contiguous()
+        qb = self.bilateral.apply(q)
+        qs = self.spatial.apply(q)
+        out = torch.empty_like(qb)
+        n_points = out.numel() // self.n_labels
+        with torch.cuda.device(out.device):
+            capi.check(capi.lib().pl_crf_update_f32(
+                out.data_ptr(), unaries.data_ptr(), qb.data_ptr(), qs.data_ptr(),
+                0 if self.compatibility is None else self.compatibility.data_ptr(), self.bilateral_weight,
+                self.spatial_weight, n_points, self.n_labels, _stream_handle(out.device)), "pl_crf_update_f32")
+        return out
 
     def infer(self, unaries, iterations=5):
         """Q after `iterations` mean-field updates, starting from softmax(-unaries)."""

@@ -37,6 +37,7 @@
 #include "blur_slice.cuh"
 #include "export.cuh"
 #include "fp64.cuh"
+#include "crf.cuh"
 
 namespace pl {
 
@@ -879,6 +880,35 @@ int pl_debug_phase_cycles(unsigned long long* out) {
     return PL_OK;
 }
 #endif
+
+int pl_crf_update_f32(float* q_out, const float* unaries, const float* q_bilateral, const float* q_spatial,
+                      const float* compatibility, float bilateral_weight, float spatial_weight,
+                      int64_t n_points, int n_labels, void* stream) {
+    if (n_points < 0 || n_labels < 1) return PL_INVALID_ARGUMENT;
+    if (n_labels > 128) return PL_UNSUPPORTED_DIMS;
+    if (n_points == 0) return PL_OK;
+    if (!q_out || !unaries || !q_bilateral || !q_spatial) return PL_INVALID_ARGUMENT;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (n_labels <= 32) {
+        constexpr int TPB = 256;
+        const size_t smem = crf_smem_bytes(TPB, n_labels);
+        const long long blocks = (n_points + TPB - 1) / TPB;
+        if (blocks > 0x7FFFFFFFll) return PL_INVALID_ARGUMENT;
+        PL_CUDA(cudaFuncSetAttribute(crf_update<TPB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        crf_update<TPB><<<(unsigned)blocks, TPB, smem, st>>>(q_out, unaries, q_bilateral, q_spatial, compatibility,
+                                                            bilateral_weight, spatial_weight, n_points, n_labels);
+    } else {
+        constexpr int TPB = 128;
+        const size_t smem = crf_smem_bytes(TPB, n_labels);
+        const long long blocks = (n_points + TPB - 1) / TPB;
+        if (blocks > 0x7FFFFFFFll) return PL_INVALID_ARGUMENT;
+        PL_CUDA(cudaFuncSetAttribute(crf_update<TPB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        crf_update<TPB><<<(unsigned)blocks, TPB, smem, st>>>(q_out, unaries, q_bilateral, q_spatial, compatibility,
+                                                            bilateral_weight, spatial_weight, n_points, n_labels);
+    }
+    PL_CUDA(cudaGetLastError());
+    return PL_OK;
+}
 
 int pl_debug_direct_index(int enable) {
     const int was = g_direct_index_enabled;

@@ -57,3 +57,49 @@ def test_dense_crf_mean_field_matches_cpu_composition(oracle):
         q = softmax(-unaries - (wb * qb + ws * qs) @ compat).astype(np.float32)
     assert np.abs(got - q).max() <= 1e-4
     assert np.abs(got.sum(-1) - 1).max() <= 1e-5
+
+
+@pytest.mark.parametrize("n_points,labels,potts", [
+    (1000, 21, True),        # ragged last block, Potts model
+    (777, 21, False),        # general compatibility matrix
+    (256, 5, False),         # exactly one block
+    (300, 40, False),        # more than 32 labels: the 128-thread form
+    (1, 2, True),            # a single point
+])
+def test_crf_update_kernel_matches_torch(n_points, labels, potts):
+    """pl_crf_update_f32 (through the C ABI) against the same update written with torch operations:
+    softmax(-U - (wb Qb + ws Qs) @ compat), fp32, max-abs 1e-5."""
+    import torch
+    from permutohedral_lattice_b200 import capi
+    g = torch.Generator(device="cpu").manual_seed(n_points + labels)
+    qb = torch.rand((n_points, labels), generator=g).cuda()
+    qs = torch.rand((n_points, labels), generator=g).cuda()
+    u = (3.0 * torch.randn((n_points, labels), generator=g)).cuda()
+    compat = None if potts else torch.randn((labels, labels), generator=g).cuda()
+    wb, ws = 1.5, 0.75
+    out = torch.full((n_points + 3, labels), 7.0, device="cuda")     # guard rows after the end
+    capi.check(capi.lib().pl_crf_update_f32(
+        out.data_ptr(), u.data_ptr(), qb.data_ptr(), qs.data_ptr(), 0 if potts else compat.data_ptr(), wb, ws,
+        n_points, labels, torch.cuda.current_stream().cuda_stream), "pl_crf_update_f32")
+    torch.cuda.synchronize()
+    cm = (1.0 - torch.eye(labels, device="cuda")) if potts else compat
+    msg = (wb * qb + ws * qs).double() @ cm.double()
+    want = torch.softmax(-u.double() - msg, dim=-1).float()
+    assert torch.all(out[n_points:] == 7.0), "wrote past the last point"
+    assert float((out[:n_points] - want).abs().max()) <= 1e-5
+    assert float((out[:n_points].sum(-1) - 1).abs().max()) <= 1e-5
+
+
+def test_crf_update_rejects_bad_arguments():
+    import torch
+    from permutohedral_lattice_b200 import capi
+    t = torch.zeros((4, 3), device="cuda")
+    L = capi.lib()
+    s = torch.cuda.current_stream().cuda_stream
+    assert L.pl_crf_update_f32(t.data_ptr(), t.data_ptr(), t.data_ptr(), t.data_ptr(), 0, 1.0, 1.0, 4, 0, s) \
+        == capi.PL_INVALID_ARGUMENT
+    assert L.pl_crf_update_f32(t.data_ptr(), t.data_ptr(), t.data_ptr(), t.data_ptr(), 0, 1.0, 1.0, 4, 129, s) \
+        == capi.PL_UNSUPPORTED_DIMS
+    assert L.pl_crf_update_f32(0, t.data_ptr(), t.data_ptr(), t.data_ptr(), 0, 1.0, 1.0, 4, 3, s) \
+        == capi.PL_INVALID_ARGUMENT
+    assert L.pl_crf_update_f32(0, 0, 0, 0, 0, 1.0, 1.0, 0, 3, s) == capi.PL_OK      # nothing to do
