@@ -60,3 +60,40 @@ class DenseCRF:
         for _ in range(int(iterations)):
             q = self.step(q, unaries)
         return q
+
+
+def _main():
+    """python -m permutohedral_lattice_b200.crf [--batch B] [--size S] [--labels L] [--iterations K]
+    Times mean-field iterations on the synthetic dense-CRF workload (seeded; no dataset belongs to this path)."""
+    import argparse
+
+    from . import workloads
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--batch", type=int, default=16)
+    ap.add_argument("--size", type=int, default=512)
+    ap.add_argument("--labels", type=int, default=21)
+    ap.add_argument("--iterations", type=int, default=10)
+    args = ap.parse_args()
+    w = workloads.config2(batch=args.batch, size=args.size, channels=args.labels)
+    image = torch.from_numpy(w.reference).cuda()
+    q0 = torch.from_numpy(w.input).cuda()
+    unaries = -torch.log(q0 + 1e-6)
+    crf = DenseCRF(image, args.labels, w.theta_alpha, w.theta_beta, 3.0)
+    q = q0
+    for _ in range(3):
+        q = crf.step(q, unaries)
+    torch.cuda.synchronize()
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    for _ in range(args.iterations):
+        q = crf.step(q, unaries)
+    t1.record()
+    torch.cuda.synchronize()
+    ms = t0.elapsed_time(t1) / args.iterations
+    print("%d x %dx%d, %d labels: %.3f ms per mean-field iteration (two lattice applications + fused update), "
+          "%.1f Mpixels/s" % (args.batch, args.size, args.size, args.labels, ms,
+                             args.batch * args.size * args.size / ms / 1e3))
+
+
+if __name__ == "__main__":
+    _main()

@@ -20,7 +20,10 @@ __host__ __forceinline__ size_t crf_smem_bytes(int tpb, int L) {
 // loaded with coalesced accesses (message and negated unaries formed on the way), then one thread per
 // point does the L x L product, the softmax, and the block leaves the same way it came.
 // compat == nullptr: Potts model (1 - identity): pairwise_k = sum_j m_j - m_k.
-template <int TPB>
+// LT > 0: Potts model with the label count fixed at compile time (a point's rows then live in registers:
+// one shared-memory read and one write per value); LT == 0: any count, any compatibility (rows stay in
+// shared memory).
+template <int TPB, int LT>
 __global__ void __launch_bounds__(TPB)
 crf_update(float* __restrict__ q_out, const float* __restrict__ unaries, const float* __restrict__ qb,
            const float* __restrict__ qs, const float* __restrict__ compat, float wb, float ws,
@@ -56,32 +59,58 @@ crf_update(float* __restrict__ q_out, const float* __restrict__ unaries, const f
     if (tid < np) {
         float* m = m_s + tid * LS;
         float* z = z_s + tid * LS;
-        float mx = -INFINITY;
-        if (compat) {
-            for (int k = 0; k < L; k++) {
-                float pair = 0.f;
-                for (int j = 0; j < L; j++) pair = PL_FMA(m[j], c_s[j * L + k], pair);
-                const float zk = PL_FADD(z[k], -pair);
-                z[k] = zk;
-                mx = fmaxf(mx, zk);
-            }
-        } else {
+        if constexpr (LT > 0) {
+            float mr[LT], zr[LT];
             float sum = 0.f;
-            for (int j = 0; j < L; j++) sum = PL_FADD(sum, m[j]);
-            for (int k = 0; k < L; k++) {
-                const float zk = PL_FADD(z[k], -PL_FADD(sum, -m[k]));
-                z[k] = zk;
-                mx = fmaxf(mx, zk);
+#pragma unroll
+            for (int j = 0; j < LT; j++) {
+                mr[j] = m[j];
+                zr[j] = z[j];
+                sum = PL_FADD(sum, mr[j]);
             }
+            float mx = -INFINITY;
+#pragma unroll
+            for (int k = 0; k < LT; k++) {
+                zr[k] = PL_FADD(zr[k], -PL_FADD(sum, -mr[k]));
+                mx = fmaxf(mx, zr[k]);
+            }
+            float den = 0.f;
+#pragma unroll
+            for (int k = 0; k < LT; k++) {
+                zr[k] = expf(PL_FADD(zr[k], -mx));
+                den = PL_FADD(den, zr[k]);
+            }
+            const float inv = PL_FDIV(1.f, den);
+#pragma unroll
+            for (int k = 0; k < LT; k++) m[k] = PL_FMUL(zr[k], inv);
+        } else {
+            float mx = -INFINITY;
+            if (compat) {
+                for (int k = 0; k < L; k++) {
+                    float pair = 0.f;
+                    for (int j = 0; j < L; j++) pair = PL_FMA(m[j], c_s[j * L + k], pair);
+                    const float zk = PL_FADD(z[k], -pair);
+                    z[k] = zk;
+                    mx = fmaxf(mx, zk);
+                }
+            } else {
+                float sum = 0.f;
+                for (int j = 0; j < L; j++) sum = PL_FADD(sum, m[j]);
+                for (int k = 0; k < L; k++) {
+                    const float zk = PL_FADD(z[k], -PL_FADD(sum, -m[k]));
+                    z[k] = zk;
+                    mx = fmaxf(mx, zk);
+                }
+            }
+            float den = 0.f;
+            for (int k = 0; k < L; k++) {
+                const float ex = expf(PL_FADD(z[k], -mx));
+                m[k] = ex;
+                den = PL_FADD(den, ex);
+            }
+            const float inv = PL_FDIV(1.f, den);
+            for (int k = 0; k < L; k++) m[k] = PL_FMUL(m[k], inv);
         }
-        float den = 0.f;
-        for (int k = 0; k < L; k++) {
-            const float ex = expf(PL_FADD(z[k], -mx));
-            m[k] = ex;
-            den = PL_FADD(den, ex);
-        }
-        const float inv = PL_FDIV(1.f, den);
-        for (int k = 0; k < L; k++) m[k] = PL_FMUL(m[k], inv);
     }
     __syncthreads();
     {

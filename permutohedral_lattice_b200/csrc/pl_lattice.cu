@@ -889,23 +889,22 @@ int pl_crf_update_f32(float* q_out, const float* unaries, const float* q_bilater
     if (n_points == 0) return PL_OK;
     if (!q_out || !unaries || !q_bilateral || !q_spatial) return PL_INVALID_ARGUMENT;
     cudaStream_t st = (cudaStream_t)stream;
-    if (n_labels <= 32) {
-        constexpr int TPB = 256;
-        const size_t smem = crf_smem_bytes(TPB, n_labels);
-        const long long blocks = (n_points + TPB - 1) / TPB;
-        if (blocks > 0x7FFFFFFFll) return PL_INVALID_ARGUMENT;
-        PL_CUDA(cudaFuncSetAttribute(crf_update<TPB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        crf_update<TPB><<<(unsigned)blocks, TPB, smem, st>>>(q_out, unaries, q_bilateral, q_spatial, compatibility,
-                                                            bilateral_weight, spatial_weight, n_points, n_labels);
-    } else {
-        constexpr int TPB = 128;
-        const size_t smem = crf_smem_bytes(TPB, n_labels);
-        const long long blocks = (n_points + TPB - 1) / TPB;
-        if (blocks > 0x7FFFFFFFll) return PL_INVALID_ARGUMENT;
-        PL_CUDA(cudaFuncSetAttribute(crf_update<TPB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        crf_update<TPB><<<(unsigned)blocks, TPB, smem, st>>>(q_out, unaries, q_bilateral, q_spatial, compatibility,
-                                                            bilateral_weight, spatial_weight, n_points, n_labels);
-    }
+    const int tpb = n_labels <= 32 ? 256 : 128;
+    const size_t smem = crf_smem_bytes(tpb, n_labels);
+    const long long blocks = (n_points + tpb - 1) / tpb;
+    if (blocks > 0x7FFFFFFFll) return PL_INVALID_ARGUMENT;
+#define PL_CRF_LAUNCH(TPB, LT)                                                                                   \
+    do {                                                                                                         \
+        PL_CUDA(cudaFuncSetAttribute(crf_update<TPB, LT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+        crf_update<TPB, LT><<<(unsigned)blocks, TPB, smem, st>>>(q_out, unaries, q_bilateral, q_spatial,         \
+                                                                 compatibility, bilateral_weight, spatial_weight, \
+                                                                 n_points, n_labels);                            \
+    } while (0)
+    // Potts model at the label count of the benchmark's CRF (20 classes + background): rows in registers
+    if (n_labels == 21 && !compatibility) PL_CRF_LAUNCH(256, 21);
+    else if (n_labels <= 32) PL_CRF_LAUNCH(256, 0);
+    else PL_CRF_LAUNCH(128, 0);
+#undef PL_CRF_LAUNCH
     PL_CUDA(cudaGetLastError());
     return PL_OK;
 }
