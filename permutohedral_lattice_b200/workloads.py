@@ -9,7 +9,7 @@ configuration is generated: numpy PCG64 (`default_rng(seed)`), seed = 100 * conf
   c3  8 x 128^3 volume, 2 channels guided by the clean phantom, theta 5 / 0.1, pd 4, vd 3, fwd + bwd
   c4  8 x 1024x1024, 16-D patch features given as positions, pd 16, vd 4, forward
   c5  c2's input and gradient through the CRF's smoothness kernel: spatial-only (bilateral=False),
-      theta_gamma 3, pd 2, vd 22, fwd + bwd (not a BASELINE.json configuration; it exercises the
+      theta_gamma 3, pd 2, vd 22, fwd + bwd (not one of the five benchmark configurations; it exercises the
       direct-indexing path)
 """
 from dataclasses import dataclass, field
