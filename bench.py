@@ -5,14 +5,21 @@
 One step = one forward + one backward (reverse=True on an upstream gradient) lattice filter over the
 whole batch of the configuration (forward only for configurations 0 and 4).  Default workload:
 configuration 2, dense-CRF message passing, 16 x 512x512, 21 channels guided by RGB + xy
-(pd 5, vd 22).  Metric: Mpixels/s.  Under torchrun every rank filters its own batch on its own GPU
-(weak scaling, no collective in the data path); time is the maximum over ranks.
+(pd 5, vd 22).  Metric: Mpixels/s.
+
+Under torchrun the ONE batch of the configuration is sharded over the ranks (contiguous slices, each
+item an independent lattice, no collective in the data path): strong scaling, `value` = pixels of the
+whole batch / time of the slowest rank.  Single-item configurations are replicated instead.  Blocks of
+K steps, each bracketed by barrier + synchronize, are repeated until they fill half a second of
+device time; `ms_per_step` is the median block / K.
 
 The line also carries: `roofline` for the slowest kernel (algorithmic bytes / CUDA-event time, against
-the measured HBM copy bandwidth in MEASURED_PEAKS.json), `roofline_call` for the whole step,
-`stages_ms` (per-call stage times from events recorded inside the timed steps), `e2e` (the same
+the measured HBM copy bandwidth in MEASURED_PEAKS.json), `roofline_call` for the whole call,
+`stages_ms` (per-call stage times from events recorded inside the last timed block), `e2e` (the same
 step through the public host-buffer API, `HostPipeline.filter`, from pinned host memory: copies in
-both directions inside the timed region, overlapped with the filter chunk by chunk) and `cpu_baseline` (the CPU
+both directions inside the timed region, overlapped with the filter item by item; beside it the time of
+the copies alone), `gather` (N > 1: the step with the ranks' outputs gathered on rank 0 by NCCL),
+`weak_scaling` (N > 1: every rank filters a whole batch of its own) and `cpu_baseline` (the CPU
 oracle on this box's host cores, bounded sample).  `--impl reference` times the reference CPU
 implementation alone.
 """
@@ -31,10 +38,6 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 METRIC = "Mpixels/s fwd+bwd (pd=5, vd=22 CRF)"
-# DRAM bytes per point and launch (dram__bytes_read.sum + dram__bytes_write.sum) of the kernels of configuration 2,
-# from the one-pass ncu capture of the full-size workload summarised in
-# profiles/dram_traffic_c2_dense_crf_16x512.txt; traffic is proportional to the number of points.
-NCU_DRAM_BYTES_PER_POINT_C2 = {"build_tiles": 49.2, "splat_tiles": 149.7, "slice_tiles": 125.4, "blur_axis": 20.4}
 FALLBACK_HBM_GBS = 6650.0
 
 
@@ -45,7 +48,10 @@ def parse_args():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--config", type=int, default=2)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--e2e-steps", type=int, default=3)
+    ap.add_argument("--e2e-steps", type=int, default=8)
+    ap.add_argument("--min-ms", type=float, default=500.0,
+                    help="the timed blocks of --steps steps are repeated until they fill this much device time")
+    ap.add_argument("--no-weak", action="store_true", help="skip the extra weak-scaling measurement at N > 1")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-threads", type=int, default=0)
     ap.add_argument("--batch", type=int, default=0,
@@ -73,6 +79,16 @@ def make_workload(cfg, rank, batch=0):
         if w.grad is not None:
             w.grad = np.ascontiguousarray(w.grad[perm])
     return w
+
+
+def config_of(w, world):
+    """The `config` object of the JSON line: the same for both arms of the comparison."""
+    sharded = w.batch >= 2
+    return {"workload": w.name, "global_batch": w.batch * (1 if sharded else max(1, world)),
+            "batch_per_gpu": -(-w.batch // max(1, world)) if sharded else w.batch,
+            "pixels_per_item": w.pixels_per_item, "pd": w.pd, "vd": w.vd,
+            "direction": "fwd+bwd" if w.backward else "fwd",
+            "l2_policy": "inputs larger than L2, no flush between iterations"}
 
 
 def peaks():
@@ -241,18 +257,53 @@ def run_reference(args, rank, world):
     line = {
         "impl": "reference", "metric": metric_name(args.config, w), "value": value,
         "unit": "Mpixels/s", "n_gpus": args.gpus, "steps": len(times), "warmup": args.warmup,
-        "ms_per_step": secs * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "f32", "data": "synthetic",
-        "config": {"workload": w.name, "batch_per_gpu": w.batch, "global_batch": w.batch * max(1, world),
-                   "pixels_per_item": w.pixels_per_item, "pd": w.pd, "vd": w.vd,
-                   "direction": "fwd+bwd" if w.backward else "fwd",
-                   "parallelism": "batch-sharded x%d" % max(1, world), "mode": "cpu reference"},
+        "ms_per_step": secs * 1e3, "higher_is_better": True, "scaling": "strong" if w.batch >= 2 else "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": config_of(w, world),
+        "details": {"mode": "cpu reference: the whole batch on rank 0's host cores, whatever --gpus says"},
         "cpu_baseline": {"value": value, "unit": "Mpixels/s", "cores": info["cores"],
                          "kind": info["kind"], "sample": info["sample"]},
         "e2e": {"value": value, "unit": "Mpixels/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
     emit_line(line)
+
+
+class Arm:
+    """One arm of the measurement: a set of device-resident tensors (a rank's slice of the batch, or a whole
+    batch) and the forward (+ backward) step over them."""
+
+    def __init__(self, plb, capi, w, lo, hi, dev):
+        import torch
+        self.plb, self.capi, self.w = plb, capi, w
+        self.b, self.n, self.c = hi - lo, w.pixels_per_item, w.vd - 1
+        self.use_positions = w.positions is not None
+        self.x = torch.from_numpy(w.input[lo:hi]).to(dev)
+        self.ref = None if w.reference is None else torch.from_numpy(w.reference[lo:hi]).to(dev)
+        self.pos = None if not self.use_positions else torch.from_numpy(w.positions[lo:hi]).to(dev)
+        self.grad = None if w.grad is None else torch.from_numpy(w.grad[lo:hi]).to(dev)
+        self.out_f = torch.empty_like(self.x)
+        self.out_b = torch.empty_like(self.x)
+        self.ws = None
+
+    def call(self, inp, out, reverse, events=None):
+        w = self.w
+        if self.b == 0:
+            return
+        if events is not None:
+            arr = (ctypes.c_void_p * self.capi.NUM_STAGE_EVENTS)(*[e.cuda_event for e in events])
+            self.capi.lib().pl_profile_next_call(arr)
+        if self.use_positions:
+            _, self.ws = self.plb.filter_positions(inp.view(self.b, self.n, self.c), self.pos, reverse=reverse,
+                                                   out=out.view(self.b, self.n, self.c))
+        else:
+            _, self.ws, _ = self.plb.lattice_filter_raw(inp, self.ref, w.bilateral, w.theta_alpha, w.theta_beta,
+                                                        w.theta_gamma, reverse, out=out)
+
+    def step(self, events_f=None, events_b=None):
+        self.call(self.x, self.out_f, False, events_f)
+        if self.w.backward:
+            self.call(self.grad, self.out_b, True, events_b)
 
 
 def main():
@@ -268,6 +319,7 @@ def main():
     import torch.distributed as dist
     import permutohedral_lattice_b200 as plb
     from permutohedral_lattice_b200 import capi
+    from permutohedral_lattice_b200.sharding import OutputGather, shard_range
 
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: the product has no CPU path")
@@ -276,105 +328,121 @@ def main():
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
 
-    w = make_workload(args.config, rank, args.batch)
-    b, n, c = w.batch, w.pixels_per_item, w.vd - 1
-    use_positions = w.positions is not None
-
-    x = torch.from_numpy(w.input).to(dev)
-    ref = None if w.reference is None else torch.from_numpy(w.reference).to(dev)
-    pos = None if not use_positions else torch.from_numpy(w.positions).to(dev)
-    grad = None if w.grad is None else torch.from_numpy(w.grad).to(dev)
-    out_f = torch.empty_like(x)
-    out_b = torch.empty_like(x)
-    xf = x.view(b, n, c)
-
-    def one_call(inp, out, reverse, events=None):
-        if events is not None:
-            arr = (ctypes.c_void_p * capi.NUM_STAGE_EVENTS)(*[e.cuda_event for e in events])
-            capi.lib().pl_profile_next_call(arr)
-        if use_positions:
-            o, ws = plb.filter_positions(inp.view(b, n, c), pos, reverse=reverse)
-            return o, ws
-        o, ws, _ = plb.lattice_filter_raw(inp, ref, w.bilateral, w.theta_alpha, w.theta_beta,
-                                          w.theta_gamma, reverse, out=out)
-        return o, ws
-
-    def step(events_f=None, events_b=None):
-        _, ws = one_call(x, out_f, False, events_f)
-        if w.backward:
-            one_call(grad, out_b, True, events_b)
-        return ws
-
     def barrier():
         torch.cuda.synchronize()
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
-    # warm-up (also creates the workspace and every stage event before the timed region)
-    for _ in range(max(args.warmup, 3)):
-        ws = step()
+    def max_over_ranks(values):
+        if world == 1:
+            return [float(v) for v in values]
+        t = torch.tensor(list(values), device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return [float(v) for v in t.tolist()]
+
+    def timed_blocks(step, steps, min_total_ms, last_block_step=None):
+        """Blocks of exactly `steps` steps, each bracketed by barrier + synchronize on both sides and timed
+        with CUDA events on the launching stream; as many blocks as it takes to fill min_total_ms (3 at
+        least).  Returns the blocks' times, each the maximum over ranks."""
+        e0 = torch.cuda.Event(enable_timing=True)
+        e1 = torch.cuda.Event(enable_timing=True)
+
+        def block(fn):
+            barrier()
+            e0.record()
+            for k in range(steps):
+                fn(k)
+            e1.record()
+            barrier()
+            return e0.elapsed_time(e1)
+
+        first = block(step)
+        (first_max,) = max_over_ranks([first])
+        nblocks = int(min(max(-(-min_total_ms // max(first_max, 1e-3)), 3), 400))
+        times = [first] + [block(step) for _ in range(nblocks - 2)] + [block(last_block_step or step)]
+        return max_over_ranks(times)
+
+    # ---- the workload and this rank's share of it -------------------------------------------------
+    # The same seeded batch on every rank; a batch of several items is SHARDED over the ranks (strong
+    # scaling: total work fixed), a single-item configuration is replicated (every rank filters it).
+    full = make_workload(args.config, 0, args.batch)
+    B, n, c = full.batch, full.pixels_per_item, full.vd - 1
+    sharded = B >= 2
+    lo, hi = shard_range(B, world, rank) if sharded else (0, B)
+    arm = Arm(plb, capi, full, lo, hi, dev)
+    calls_per_step = 2 if full.backward else 1
+    total_pixels = B * n * (1 if sharded else world)
+
+    warm = max(args.warmup, 3)
+    for _ in range(warm):
+        arm.step()
     torch.cuda.synchronize()
-    st = plb.lattice_stats(ws)
-    if st.device_status != 0:
-        raise SystemExit("device status %d" % st.device_status)
-    calls_per_step = 2 if w.backward else 1
+    if arm.ws is not None:
+        st = plb.lattice_stats(arm.ws)
+        if st.device_status != 0:
+            raise SystemExit("device status %d" % st.device_status)
+        counts = [int(st.num_vertices), int(st.num_entries)]
+    else:
+        counts = [0, 0]
+    if world > 1:   # whole-batch counts: sum over the ranks' slices
+        t = torch.tensor(counts, device=dev, dtype=torch.int64)
+        if sharded:
+            dist.all_reduce(t)
+        counts = [int(v) for v in t.tolist()]
+    num_vertices, num_entries = counts
+
+    # stage events of every call of the last timed block
     ev = [[[torch.cuda.Event(enable_timing=True) for _ in range(capi.NUM_STAGE_EVENTS)]
            for _ in range(calls_per_step)] for _ in range(args.steps)]
-    for s in ev:
-        for call in s:
+    for s_ in ev:
+        for call in s_:
             for e in call:
                 e.record()
-    t_begin = torch.cuda.Event(enable_timing=True)
-    t_end = torch.cuda.Event(enable_timing=True)
 
     sampler = ClockSampler(local_rank)
     sampler.start()
-    barrier()
+    launches0 = capi.lib().pl_launch_count()
     sampler.mark_begin()
-    t_begin.record()
-    for k in range(args.steps):
-        step(ev[k][0], ev[k][1] if w.backward else None)
-    t_end.record()
-    barrier()
+    block_ms = timed_blocks(lambda k: arm.step(), args.steps, args.min_ms,
+                            lambda k: arm.step(ev[k][0], ev[k][1] if full.backward else None))
     sampler.mark_end()
+    launches = capi.lib().pl_launch_count() - launches0
     clocks = sampler.stop()
-    elapsed_ms = t_begin.elapsed_time(t_end)
-    if world > 1:
-        t = torch.tensor([elapsed_ms], device=dev, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        elapsed_ms = float(t.item())
-    ms_per_step = elapsed_ms / args.steps
-    total_pixels = b * n * world
+    ms_per_step = statistics.median(block_ms) / args.steps
     value = total_pixels / (ms_per_step * 1e-3) / 1e6
 
-    # per-stage times of a call, averaged over all timed calls
+    # per-stage times of a call, averaged over the calls of the last block (this rank's slice)
     stage_ms = {name: 0.0 for name in capi.STAGE_NAMES}
     ncalls = 0
-    for s in ev:
-        for call in s:
-            for i, name in enumerate(capi.STAGE_NAMES):
-                stage_ms[name] += call[i].elapsed_time(call[i + 1])
-            ncalls += 1
-    stage_ms = {k: v / ncalls for k, v in stage_ms.items()}
+    if arm.b:
+        for s_ in ev:
+            for call in s_:
+                for i, name in enumerate(capi.STAGE_NAMES):
+                    stage_ms[name] += call[i].elapsed_time(call[i + 1])
+                ncalls += 1
+        stage_ms = {k: v / ncalls for k, v in stage_ms.items()}
 
-    # roofline
+    # roofline of the slowest kernel and of the whole call (this rank's launches: its slice of the batch)
     hbm_gbs, peak_kind = peaks()
-    stage_bytes, call_bytes, io_bytes = algorithmic_bytes(w, int(st.num_vertices))
+    frac_of_batch = (arm.b / B) if sharded else 1.0
+    stage_bytes, call_bytes, io_bytes = algorithmic_bytes(full, num_vertices // (1 if sharded else world))
+    stage_bytes = {k: v * frac_of_batch for k, v in stage_bytes.items()}
+    call_bytes *= frac_of_batch
+    io_bytes *= frac_of_batch
     kernel_ms = dict(stage_ms)
-    kernel_ms["blur"] = stage_ms["blur"] / (w.pd + 1)          # one blur_axis launch
+    kernel_ms["blur"] = stage_ms["blur"] / (full.pd + 1)          # one blur_axis launch
     kernel_bytes = dict(stage_bytes)
-    kernel_bytes["blur"] = stage_bytes["blur"] / (w.pd + 1)
+    kernel_bytes["blur"] = stage_bytes["blur"] / (full.pd + 1)
     kernel_names = {"build": "build_tiles", "splat": "splat_tiles", "blur": "blur_axis",
                     "slice": "slice_tiles"}
     dominant = max(kernel_names, key=lambda k: stage_ms[k])
-    achieved = kernel_bytes[dominant] / (kernel_ms[dominant] * 1e-3) / 1e9
-    traffic = None
-    if args.config == 2:
-        traffic = NCU_DRAM_BYTES_PER_POINT_C2[kernel_names[dominant]] * b * n
+    achieved = kernel_bytes[dominant] / max(kernel_ms[dominant] * 1e-3, 1e-12) / 1e9
+    traffic, traffic_source = measured_traffic(full.name, kernel_names[dominant], arm.b * n)
     roofline = {"bound": "hbm", "kernel": kernel_names[dominant], "achieved": achieved,
                 "peak": hbm_gbs, "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / hbm_gbs,
-                "traffic": traffic, "algorithmic_bytes_per_launch": kernel_bytes[dominant],
+                "traffic": traffic, "traffic_source": traffic_source,
+                "algorithmic_bytes_per_launch": kernel_bytes[dominant],
                 "ms_per_launch": kernel_ms[dominant]}
     call_ms = ms_per_step / calls_per_step
     call_gbs = call_bytes / (call_ms * 1e-3) / 1e9
@@ -382,145 +450,217 @@ def main():
                      "achieved": call_gbs, "peak": hbm_gbs, "unit": "GB/s", "frac": call_gbs / hbm_gbs,
                      "ms_per_call": call_ms}
 
-    # end to end through the public API from pinned host buffers
-    hx = torch.from_numpy(w.input).pin_memory()
-    href = None if w.reference is None else torch.from_numpy(w.reference).pin_memory()
-    hpos = None if not use_positions else torch.from_numpy(w.positions).pin_memory()
-    hgrad = None if w.grad is None else torch.from_numpy(w.grad).pin_memory()
+    # ---- the same step with the ranks' output slices gathered on rank 0 (NCCL over NVLink) ---------
+    gather = None
+    if world > 1 and sharded:
+        comm = torch.cuda.Stream(dev)
+        item_shape = tuple(arm.x.shape[1:])
+        gather_f = OutputGather(B, item_shape, arm.x.dtype, dev, dst=0)
+        gather_b = OutputGather(B, item_shape, arm.x.dtype, dev, dst=0) if full.backward else None
+        main = torch.cuda.current_stream(dev)
+
+        def gather_step(k):
+            # the forward result travels while the backward call computes
+            arm.call(arm.x, arm.out_f, False)
+            comm.wait_stream(main)
+            with torch.cuda.stream(comm):
+                gather_f(arm.out_f)
+            if full.backward:
+                arm.call(arm.grad, arm.out_b, True)
+                comm.wait_stream(main)
+                with torch.cuda.stream(comm):
+                    gather_b(arm.out_b)
+            main.wait_stream(comm)
+
+        for _ in range(3):
+            gather_step(0)
+        g_ms = statistics.median(timed_blocks(gather_step, args.steps, min(args.min_ms, 250.0))) / args.steps
+        per = -(-B // world)
+        gather = {"value": total_pixels / (g_ms * 1e-3) / 1e6, "unit": "Mpixels/s", "ms_per_step": g_ms,
+                  "bytes_received_by_rank0_per_step": (world - 1) * per * n * c * 4 * calls_per_step,
+                  "method": "torch.distributed gather (NCCL) of the ranks' output slices onto rank 0 on a side "
+                            "stream, forward result in flight during the backward call"}
+
+    # ---- end to end through the public API from pinned host buffers (this rank's slice) ------------
+    hslice = slice(lo, hi)
+    hx = torch.from_numpy(full.input[hslice]).pin_memory()
+    href = None if full.reference is None else torch.from_numpy(full.reference[hslice]).pin_memory()
+    hpos = None if not arm.use_positions else torch.from_numpy(full.positions[hslice]).pin_memory()
+    hgrad = None if full.grad is None else torch.from_numpy(full.grad[hslice]).pin_memory()
     hout_f = torch.empty_like(hx).pin_memory()
     hout_b = torch.empty_like(hx).pin_memory()
     # the op is stateless: the reference image travels with the forward and again with the backward call
     h2d = hx.numel() * 4 + (href.numel() * 4 * calls_per_step if href is not None else 0) + \
-        (hpos.numel() * 4 if hpos is not None else 0) + (hgrad.numel() * 4 if w.backward else 0)
+        (hpos.numel() * 4 if hpos is not None else 0) + (hgrad.numel() * 4 if full.backward else 0)
     d2h = hx.numel() * 4 * calls_per_step
+    (h2d, d2h) = [int(v) for v in sum_over_ranks([h2d, d2h], world, dev, dist)]   # whole job
 
-    pipe = plb.HostPipeline(dev, n_streams=3, chunk_items=2)
+    pipe = plb.HostPipeline(dev)
 
-    def e2e_step():
-        if use_positions:
+    def e2e_step(copy_only=False):
+        w = full
+        if arm.b == 0:
+            return
+        if arm.use_positions:
             dx = hx.to(dev, non_blocking=True)
             dp = hpos.to(dev, non_blocking=True)
-            o, _ = plb.filter_positions(dx.view(b, n, c), dp)
+            if copy_only:
+                o = dx
+            else:
+                o, _ = plb.filter_positions(dx.view(arm.b, n, c), dp)
             hout_f.copy_(o.view_as(hout_f), non_blocking=True)
             torch.cuda.current_stream().synchronize()
         else:
             pipe.filter(hx, href, w.bilateral, w.theta_alpha, w.theta_beta, w.theta_gamma, reverse=False,
-                        out_host=hout_f, wait=False)
+                        out_host=hout_f, wait=False, copy_only=copy_only)
             if w.backward:
                 pipe.filter(hgrad, href, w.bilateral, w.theta_alpha, w.theta_beta, w.theta_gamma, reverse=True,
-                            out_host=hout_b, wait=False)
+                            out_host=hout_b, wait=False, copy_only=copy_only)
             pipe.synchronize()     # both results are complete in host memory when the step ends
 
-    e2e_step()
-    barrier()
-    e0 = torch.cuda.Event(enable_timing=True)
-    e1 = torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(args.e2e_steps):
-        e2e_step()
-    e1.record()
-    barrier()
-    e2e_ms = e0.elapsed_time(e1)
-    if world > 1:
-        t = torch.tensor([e2e_ms], device=dev, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_ms = float(t.item())
-    e2e_value = total_pixels / (e2e_ms / args.e2e_steps * 1e-3) / 1e6
+    def timed_host_steps(fn, steps):
+        fn()
+        barrier()
+        t0 = time.perf_counter()
+        e0 = torch.cuda.Event(enable_timing=True)
+        e1 = torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        barrier()
+        wall = (time.perf_counter() - t0) * 1e3
+        (ms, wall) = max_over_ranks([e0.elapsed_time(e1), wall])
+        return ms / steps, wall / steps
+
+    e2e_ms, e2e_wall_ms = timed_host_steps(e2e_step, args.e2e_steps)
+    copy_ms, _ = timed_host_steps(lambda: e2e_step(copy_only=True), args.e2e_steps)
+    e2e_value = total_pixels / (e2e_ms * 1e-3) / 1e6
 
     # not the headline: the same step with the lattice built once and reused by the backward call
     # (pl_lattice_build_f32 + 2 x pl_lattice_apply_f32), as a training step through
     # lattice_filter(..., reuse_lattice=True) does
     reuse = None
-    if not use_positions and w.backward:
-        def reuse_step():
-            lat = plb.Lattice(ref, tuple(x.shape[:-1]), w.bilateral, w.theta_alpha, w.theta_beta, w.theta_gamma,
-                              max_channels=c)
-            lat.apply(x, False, out=out_f)
-            lat.apply(grad, True, out=out_b)
+    if not arm.use_positions and full.backward and arm.b:
+        w = full
+
+        def reuse_step(k):
+            lat = plb.Lattice(arm.ref, tuple(arm.x.shape[:-1]), w.bilateral, w.theta_alpha, w.theta_beta,
+                              w.theta_gamma, max_channels=c)
+            lat.apply(arm.x, False, out=arm.out_f)
+            lat.apply(arm.grad, True, out=arm.out_b)
         for _ in range(3):
-            reuse_step()
-        barrier()
-        r0 = torch.cuda.Event(enable_timing=True)
-        r1 = torch.cuda.Event(enable_timing=True)
-        r0.record()
-        for _ in range(args.steps):
-            reuse_step()
-        r1.record()
-        barrier()
-        reuse_ms = r0.elapsed_time(r1) / args.steps
-        if world > 1:
-            t = torch.tensor([reuse_ms], device=dev, dtype=torch.float64)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            reuse_ms = float(t.item())
+            reuse_step(0)
+        reuse_ms = statistics.median(timed_blocks(reuse_step, args.steps, min(args.min_ms, 100.0))) / args.steps
         reuse = {"value": total_pixels / (reuse_ms * 1e-3) / 1e6, "unit": "Mpixels/s", "ms_per_step": reuse_ms,
                  "note": "lattice built once per step and applied forward and reverse; not the headline metric"}
 
     # also not the headline: the same stateless step replayed from CUDA graphs (one launch per call)
     graph = None
-    if not use_positions:
-        gf = plb.GraphedLatticeFilter(x.shape, None if ref is None else ref.shape, w.bilateral, w.theta_alpha,
-                                      w.theta_beta, w.theta_gamma, False, device=dev)
-        gb = plb.GraphedLatticeFilter(x.shape, None if ref is None else ref.shape, w.bilateral, w.theta_alpha,
-                                      w.theta_beta, w.theta_gamma, True, device=dev) if w.backward else None
-        gf.input.copy_(x)
-        if ref is not None:
-            gf.reference.copy_(ref)
+    if not arm.use_positions and arm.b:
+        w = full
+        rshape = None if arm.ref is None else arm.ref.shape
+        gf = plb.GraphedLatticeFilter(arm.x.shape, rshape, w.bilateral, w.theta_alpha, w.theta_beta, w.theta_gamma,
+                                      False, device=dev)
+        gb = plb.GraphedLatticeFilter(arm.x.shape, rshape, w.bilateral, w.theta_alpha, w.theta_beta, w.theta_gamma,
+                                      True, device=dev) if w.backward else None
+        gf.input.copy_(arm.x)
+        if arm.ref is not None:
+            gf.reference.copy_(arm.ref)
         if gb is not None:
-            gb.input.copy_(grad)
-            if ref is not None:
-                gb.reference.copy_(ref)
+            gb.input.copy_(arm.grad)
+            if arm.ref is not None:
+                gb.reference.copy_(arm.ref)
+
+        def graph_step(k):
+            gf.replay()
+            if gb is not None:
+                gb.replay()
         for _ in range(3):
-            gf.replay()
-            if gb is not None:
-                gb.replay()
-        barrier()
-        g0 = torch.cuda.Event(enable_timing=True)
-        g1 = torch.cuda.Event(enable_timing=True)
-        g0.record()
-        for _ in range(args.steps):
-            gf.replay()
-            if gb is not None:
-                gb.replay()
-        g1.record()
-        barrier()
-        graph_ms = g0.elapsed_time(g1) / args.steps
-        if world > 1:
-            t = torch.tensor([graph_ms], device=dev, dtype=torch.float64)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            graph_ms = float(t.item())
+            graph_step(0)
+        graph_ms = statistics.median(timed_blocks(graph_step, args.steps, min(args.min_ms, 100.0))) / args.steps
         graph = {"value": total_pixels / (graph_ms * 1e-3) / 1e6, "unit": "Mpixels/s", "ms_per_step": graph_ms,
                  "note": "stateless forward + backward replayed from CUDA graphs; not the headline metric"}
         del gf, gb
 
-    kernels_per_call = 7 + (w.pd + 1)   # build, clear, insert, link x2, splat, slice + blur passes
+    # weak scaling beside the strong-scaling headline: every rank filters a whole batch of its own
+    weak = None
+    if world > 1 and sharded and not args.no_weak:
+        del arm
+        torch.cuda.empty_cache()
+        own = Arm(plb, capi, make_workload(args.config, rank, args.batch), 0, B, dev)
+        for _ in range(3):
+            own.step()
+        weak_ms = statistics.median(timed_blocks(lambda k: own.step(), args.steps, min(args.min_ms, 250.0))) \
+            / args.steps
+        weak = {"value": B * n * world / (weak_ms * 1e-3) / 1e6, "unit": "Mpixels/s", "ms_per_step": weak_ms,
+                "global_batch": B * world, "batch_per_gpu": B,
+                "note": "every rank filters its own whole batch (per-GPU work fixed); not the headline metric"}
+
     line = {
-        "metric": metric_name(args.config, w), "value": value, "unit": "Mpixels/s", "n_gpus": world,
-        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+        "metric": metric_name(args.config, full), "value": value, "unit": "Mpixels/s", "n_gpus": world,
+        "steps": args.steps, "warmup": warm, "ms_per_step": ms_per_step,
+        "higher_is_better": True, "scaling": "strong" if sharded else "weak", "vs_baseline": None, "dtype": "f32",
         "data": "synthetic",
-        "config": {"workload": w.name, "batch_per_gpu": b, "global_batch": b * world,
-                   "pixels_per_item": n, "pd": w.pd, "vd": w.vd,
-                   "direction": "fwd+bwd" if w.backward else "fwd", "parallelism": "batch-sharded x%d" % world,
-                   "mode": "atomic", "l2_policy": "inputs larger than L2 (%.0f MB read per call)"
-                   % ((x.numel() + (ref.numel() if ref is not None else 0)) * 4 / 1e6),
-                   "num_vertices": int(st.num_vertices), "num_entries": int(st.num_entries)},
+        "config": config_of(full, world),
+        "details": {"parallelism": ("one batch of %d items sharded over %d GPU(s), no collective in the data path"
+                                    % (B, world)) if sharded else "replicas only (single item), x%d" % world,
+                    "mode": "atomic", "bytes_read_per_call_on_this_rank": (hx.numel() + (
+                        href.numel() if href is not None else 0)) * 4,
+                    "num_vertices": num_vertices, "num_entries": num_entries,
+                    "timing": "median of %d blocks of %d steps, each block bracketed by barrier + synchronize, "
+                              "max over ranks per block" % (len(block_ms), args.steps)},
+        "blocks": {"count": len(block_ms), "min_ms": min(block_ms), "median_ms": statistics.median(block_ms),
+                   "max_ms": max(block_ms)},
         "clocks": clocks,
         "e2e": {"value": e2e_value, "unit": "Mpixels/s", "h2d_bytes_per_step": h2d,
-                "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms / args.e2e_steps},
-        "gpu_launches": kernels_per_call * calls_per_step * args.steps,
+                "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms, "wall_ms_per_step": e2e_wall_ms,
+                "copy_only_ms_per_step": copy_ms,
+                "note": "HostPipeline from pinned host buffers, single-item chunks on 4 streams; copy_only = the "
+                        "same copies on the same streams without the filter (what the host link allows)"},
+        "gpu_launches": int(launches) * world,
+        "launches_per_call": int(launches) // max(1, len(block_ms) * args.steps * calls_per_step),
         "roofline": roofline, "roofline_call": roofline_call,
         "stages_ms": stage_ms,
+        "gather": gather,
+        "weak_scaling": weak,
         "lattice_reuse": reuse,
         "graph_replay": graph,
     }
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        info = cpu_baseline(w, host_threads(args.cpu_threads, w.batch))
+        info = cpu_baseline(full, host_threads(args.cpu_threads, full.batch))
         info.pop("seconds", None)
         line["cpu_baseline"] = info
     if rank == 0:
         emit_line(line)
     if world > 1:
         dist.destroy_process_group()
+
+
+def sum_over_ranks(values, world, dev, dist):
+    if world == 1:
+        return values
+    import torch
+    t = torch.tensor(list(values), device=dev, dtype=torch.float64)
+    dist.all_reduce(t)
+    return t.tolist()
+
+
+def measured_traffic(workload_name, kernel, points):
+    """DRAM bytes of one launch of `kernel` over `points` points, scaled from the per-point figure of an ncu
+    capture of a reduced batch of the same workload (every item is an independent lattice, so traffic is
+    proportional to the number of points).  The figures live beside the captures' summaries; None if there
+    is none for this workload."""
+    path = os.path.join(ROOT, "profiles", "dram_bytes_per_point.json")
+    try:
+        with open(path) as f:
+            table = json.load(f)
+    except Exception:
+        return None, None
+    for prefix, entry in table.items():
+        if workload_name.startswith(prefix) and kernel in entry.get("kernels", {}):
+            return entry["kernels"][kernel] * points, entry.get("source")
+    return None, None
 
 
 class _StdoutToStderr:

@@ -129,7 +129,9 @@ int pl_lattice_apply_f32(float* output, const float* input, int n_input_channels
  *  - It calls no cudaMalloc / cudaFree and no allocating library routine.
  *  - A call whose pl_workspace_bytes exceeds PL_STATIC_SCRATCH_BYTES returns
  *    PL_WORKSPACE_TOO_SMALL before launching anything (pl_last_cuda_error then holds the two sizes);
- *    a smaller max_entries shrinks the need.
+ *    a smaller max_entries shrinks the need.  Whether the lattice stayed within that max_entries is
+ *    known only on the device: read it with pl_lattice_stats(NULL, &stats, stream) and check
+ *    stats.device_status (on PL_CAPACITY_EXCEEDED the output holds NaN).
  *  - The first call on each device looks up the scratch's device address (the device must be
  *    current, as for every call); make that first call outside any stream capture.
  *  - All calls on a device share the one scratch, which keeps the previous call's contents; each call
@@ -192,6 +194,11 @@ int pl_crf_update_f32(float* q_out, const float* unaries, const float* q_bilater
                       const float* compatibility, float bilateral_weight, float spatial_weight,
                       int64_t n_points, int n_labels, void* stream);
 
+/* Number of kernels the library has launched in this process so far (filter stages and pl_crf_update_f32;
+ * memsets, copies and event records are not counted).  The difference across a region is the number
+ * of kernels that region launched.  No counterpart in the reference. */
+unsigned long long pl_launch_count(void);
+
 /* Spatial-only calls (bilateral == 0: the features are the grid coordinates divided by theta_gamma,
  * src/LatticeFilterKernel.cpp:137-142, compute_spatial_kernel_gpu in Tests/PermutohedralLatticeGPU.cu:33-42)
  * locate their vertices by direct indexing instead of hashing whenever the dense index fits the
@@ -202,7 +209,11 @@ int pl_crf_update_f32(float* q_out, const float* unaries, const float* q_bilater
 int pl_debug_direct_index(int enable);
 
 /* Copies the counters of the last call that used `workspace` to the host.  SYNCHRONISES `stream`.
- * Returns PL_OK when read; the call's own outcome is stats->device_status.
+ * workspace == NULL reads the counters of the last pl_lattice_filter_f32_noalloc call on the current
+ * device (its scratch is inside the library, so that caller has no pointer to pass).
+ * Returns PL_OK when read; the call's own outcome is stats->device_status.  A call whose device_status
+ * is not PL_OK (for instance PL_CAPACITY_EXCEEDED under a max_entries that was too small) has filled
+ * its whole output with NaN: a failed call never leaves bytes that could pass for a result.
  * No counterpart in the reference (it prints or exits: src/PermutohedralLatticeGPU.cuh:49-55,442-445). */
 int pl_lattice_stats(const void* workspace, pl_stats* stats, void* stream);
 

@@ -25,7 +25,7 @@ EXPORTED_SYMBOLS = [
     "pl_export_lattice", "pl_profile_next_call", "pl_lattice_filter_f32_noalloc",
     "pl_lattice_build_f32", "pl_lattice_build_positions_f32", "pl_lattice_apply_f32",
     "pl_workspace_bytes_f64", "pl_compute_positions_f64", "pl_filter_f64", "pl_lattice_filter_f64",
-    "pl_export_lattice_f64", "pl_debug_direct_index", "pl_crf_update_f32",
+    "pl_export_lattice_f64", "pl_debug_direct_index", "pl_crf_update_f32", "pl_launch_count",
 ]
 STATIC_SCRATCH_BYTES = 64 << 20
 NUM_STAGE_EVENTS = 6
@@ -87,6 +87,8 @@ def lib():
         L.pl_debug_direct_index.argtypes = [i]
         L.pl_crf_update_f32.argtypes = [vp, vp, vp, vp, vp, f, f, i64, i, vp]
         L.pl_profile_next_call.argtypes = [ctypes.POINTER(ctypes.c_void_p)]
+        L.pl_launch_count.argtypes = []
+        L.pl_launch_count.restype = ctypes.c_ulonglong
         _lib = L
     return _lib
 

@@ -71,7 +71,10 @@ slice_tiles_fast(Geom g, float* __restrict__ output, const Header* hdr, const in
     float* rows_s = reinterpret_cast<float*>(smem_raw);                                         // [rows_cap][RS]
     float* out_s = reinterpret_cast<float*>(smem_raw);                                          // [TP][C], later
     int* prow_s = reinterpret_cast<int*>(smem_raw + SliceFast<PD, VD>::region(rows_cap));       // [TP]
-    if (call_failed(hdr)) return;
+    if (call_failed(hdr)) {
+        poison_tile_output(g, output, C);
+        return;
+    }
     PhaseClock pc(2);
     const TilePos tpos = this_tile(g);
     const int tid = threadIdx.x, tile = tpos.tile;
@@ -194,7 +197,10 @@ slice_tiles_generic(Geom g, float* __restrict__ output, const Header* hdr, const
     float4* rows4 = reinterpret_cast<float4*>(smem_raw);                            // [rows_cap][QPR]
     float* prec_s = reinterpret_cast<float*>(rows4 + (size_t)rows_cap * QPR);       // [TP][PW]
     int* prow_s = reinterpret_cast<int*>(prec_s + (size_t)TP * PW);                 // [TP]
-    if (call_failed(hdr)) return;
+    if (call_failed(hdr)) {
+        poison_tile_output(g, output, C);
+        return;
+    }
     const TilePos tpos = this_tile(g);
     const int tid = threadIdx.x, tile = tpos.tile, lane = tid & 31, warp = tid >> 5;
     const int2 info = tile_info[tile];

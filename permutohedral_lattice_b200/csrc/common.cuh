@@ -263,6 +263,18 @@ __device__ __forceinline__ bool call_failed(const Header* hdr) {
     return status_s != 0;
 }
 
+// A call that failed on the device (status word set by an earlier launch) must not leave bytes that
+// could pass for a result: the slice stage then fills the tile's output rows with NaN and returns.
+template <typename T>
+__device__ __forceinline__ void poison_tile_output(const Geom& g, T* __restrict__ output, int channels) {
+    const TilePos tpos = this_tile(g);
+    int item, pix;
+    if (!tile_point(g, tpos, threadIdx.x, item, pix)) return;
+    T* row = output + ((size_t)item * g.n + pix) * channels;
+    const T nan = (T)__int_as_float(0x7FC00000);
+    for (int j = 0; j < channels; j++) row[j] = nan;
+}
+
 // ---------------------------------------------------------------------------------------------
 // Value rows.  A vertex row holds vd floats padded to VP = a multiple of 4, so that rows are 16-byte
 // aligned: every row access below is a float4, and a row of 22 channels covers exactly three

@@ -119,7 +119,10 @@ slice_tiles_f64(Geom g, double* __restrict__ output, const Header* hdr, const in
     __shared__ double w_s[SPLATS];
     __shared__ u32 v_s[SPLATS];
     __shared__ int prow_s[TP];
-    if (call_failed(hdr)) return;
+    if (call_failed(hdr)) {
+        poison_tile_output(g, output, C);
+        return;
+    }
     const TilePos tpos = this_tile(g);
     const int tid = threadIdx.x, tile = tpos.tile, lane = tid & 31, warp = tid >> 5;
     const int base = tile_info[tile].x;

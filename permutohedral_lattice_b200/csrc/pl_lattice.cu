@@ -24,6 +24,7 @@
 // Device code lives in the headers included below (one translation unit); this file holds the host
 // side: geometry and workspace layout, launches, and the extern "C" entry points.
 #include <cuda_runtime.h>
+#include <atomic>
 #include <cmath>
 #include <mutex>
 #include <stdint.h>
@@ -47,6 +48,11 @@ namespace pl {
 static thread_local char g_cuda_error[256] = "";
 // Stage-boundary events for the next filter call of this thread (pl_profile_next_call); consumed by it.
 static thread_local cudaEvent_t* g_stage_events = nullptr;
+
+// Kernel launches issued by the library since it was loaded (pl_launch_count): memsets and event
+// records are not counted.
+static std::atomic<unsigned long long> g_launches{0};
+#define PL_COUNT_LAUNCHES(n) g_launches.fetch_add((n), std::memory_order_relaxed)
 
 static int cuda_fail(cudaError_t e, const char* where) {
     snprintf(g_cuda_error, sizeof(g_cuda_error), "%s: %s", where, cudaGetErrorString(e));
@@ -187,6 +193,30 @@ static int num_sms() {
     return g_num_sms;
 }
 
+// cudaFuncSetAttribute is a driver call and its effect lasts as long as the context: the dynamic
+// shared-memory limit (and carve-out preference) of a kernel is raised once per device, and again only
+// when a later call needs more than any call before it.
+constexpr int MAX_DEVICES = 64;
+template <auto Kernel>
+static int ensure_dynamic_smem(size_t bytes, bool max_carveout = false) {
+    static std::atomic<size_t> granted[MAX_DEVICES];   // zero-initialised: nothing granted yet
+    int dev = -1;
+    PL_CUDA(cudaGetDevice(&dev));
+    const bool cached = dev >= 0 && dev < MAX_DEVICES;
+    if (cached && granted[dev].load(std::memory_order_acquire) >= bytes + 1) return PL_OK;
+    PL_CUDA(cudaFuncSetAttribute(Kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
+    if (max_carveout)
+        PL_CUDA(cudaFuncSetAttribute(Kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                     cudaSharedmemCarveoutMaxShared));
+    if (cached) granted[dev].store(bytes + 1, std::memory_order_release);
+    return PL_OK;
+}
+#define PL_TRY(call)                     \
+    do {                                 \
+        const int rc_ = (call);          \
+        if (rc_ != PL_OK) return rc_;    \
+    } while (0)
+
 // Rows of the per-tile shared-memory vertex-row cache of slice_tiles (48 KB of rows at most).
 static int rows_cap_for(int pd, int vd) {
     const int splats = tp_of(pd) * (pd + 1);
@@ -212,11 +242,8 @@ static int launch_splat(const Geom& g, const float* input, Header* hdr, const in
                         const float* rec_w, const u32* list_ref, float* v0, int vd, cudaStream_t st) {
     if constexpr (VD > 8 && VD <= 32) {   // wide rows: a quarter warp per window, conflict-free row reads
         const size_t smem = SplatRows<PD, VD>::BYTES;
-        PL_CUDA(cudaFuncSetAttribute(splat_tiles_rows<PD, VD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     (int)smem));
         // five CTAs per SM need nearly all of the SM's shared memory: ask for the largest carve-out
-        PL_CUDA(cudaFuncSetAttribute(splat_tiles_rows<PD, VD>, cudaFuncAttributePreferredSharedMemoryCarveout,
-                                     cudaSharedmemCarveoutMaxShared));
+        PL_TRY((ensure_dynamic_smem<splat_tiles_rows<PD, VD>>(smem, true)));
         // bulk staging also needs 16-byte aligned landing zones inside the padded tile rows
         const bool bulk = bulk_rows_ok(g, input, VD - 1) && g.TX <= 16 &&
                           (g.TX * (SplatRows<PD, VD>::VP - (VD - 1))) % 4 == 0;
@@ -224,13 +251,13 @@ static int launch_splat(const Geom& g, const float* input, Header* hdr, const in
                                                                          list_ref, v0, bulk ? 1 : 0);
     } else if constexpr (VD > 0) {
         const size_t smem = SplatFast<PD, VD>::BYTES;
-        PL_CUDA(cudaFuncSetAttribute(splat_tiles_fast<PD, VD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        PL_TRY((ensure_dynamic_smem<splat_tiles_fast<PD, VD>>(smem)));
         splat_tiles_fast<PD, VD><<<tile_grid(g), Cfg<PD>::TP, smem, st>>>(
             g, input, hdr, tile_info, rec, rec_w, list_ref, v0, bulk_rows_ok(g, input, VD - 1) ? 1 : 0);
     } else {
         const size_t smem = SplatGeneric<PD>::bytes(vd);
         if (smem > 200 * 1024) return PL_UNSUPPORTED_DIMS;
-        PL_CUDA(cudaFuncSetAttribute(splat_tiles_generic<PD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        PL_TRY((ensure_dynamic_smem<splat_tiles_generic<PD>>(smem)));
         splat_tiles_generic<PD><<<tile_grid(g), Cfg<PD>::TP, smem, st>>>(g, input, hdr, tile_info, rec, rec_w,
                                                                         list_ref, v0, vd);
     }
@@ -244,7 +271,7 @@ static int launch_slice(const Geom& g, float* output, const Header* hdr, const i
         int rows_cap = (40 * 1024) / (SliceFast<PD, VD>::RS * 4);
         if (rows_cap > Cfg<PD>::SPLATS) rows_cap = Cfg<PD>::SPLATS;
         const size_t smem = SliceFast<PD, VD>::bytes(rows_cap);
-        PL_CUDA(cudaFuncSetAttribute(slice_tiles_fast<PD, VD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        PL_TRY((ensure_dynamic_smem<slice_tiles_fast<PD, VD>>(smem)));
         slice_tiles_fast<PD, VD><<<tile_grid(g), Cfg<PD>::TP, smem, st>>>(
             g, output, hdr, tile_info, rec, rec_w, list_ref, vsrc, rows_cap, bulk_rows_ok(g, output, VD - 1) ? 1 : 0);
     } else {
@@ -252,7 +279,7 @@ static int launch_slice(const Geom& g, float* output, const Header* hdr, const i
         const size_t fixed = sizeof(float) * Cfg<PD>::TP * SliceCfg<PD>::PW + sizeof(int) * Cfg<PD>::TP;
         const size_t smem = sizeof(float) * (size_t)rows_cap * padded_vd(vd) + fixed;
         if (smem > 200 * 1024) return PL_UNSUPPORTED_DIMS;
-        PL_CUDA(cudaFuncSetAttribute(slice_tiles_generic<PD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        PL_TRY((ensure_dynamic_smem<slice_tiles_generic<PD>>(smem)));
         slice_tiles_generic<PD><<<tile_grid(g), Cfg<PD>::TP, smem, st>>>(g, output, hdr, tile_info, rec, rec_w,
                                                                         list_ref, vsrc, vd, rows_cap);
     }
@@ -294,9 +321,7 @@ static int run_filter(const Geom& g, float* output, const float* input, const fl
     if (phases & PH_BUILD) PL_CUDA(cudaMemsetAsync(hdr, 0, sizeof(Header), st));
     if (g.num_tiles == 0) return PL_OK;
 
-    // per device and cheap, so set on every call rather than cached
-    PL_CUDA(cudaFuncSetAttribute(build_tiles<PD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 (int)Cfg<PD>::BUILD_SMEM));
+    PL_TRY((ensure_dynamic_smem<build_tiles<PD, float>>(Cfg<PD>::BUILD_SMEM)));
     const int sms = num_sms();
     const int wide = sms * 8;
     int table_log2 = 0;
@@ -305,6 +330,7 @@ static int run_filter(const Geom& g, float* output, const float* input, const fl
     if (phases & PH_BUILD) {
         build_tiles<PD><<<tile_grid(g), TP, Cfg<PD>::BUILD_SMEM, st>>>(
             g, positions, reference, hdr, tile_info, rec, rec_w, list_keys, (u32)L.max_entries);
+        PL_COUNT_LAUNCHES(5);   // build_tiles and the four launches of the index stage below
         if (ev) PL_CUDA(cudaEventRecord(ev[1], st));
         Direct direct;
         bool use_direct = false;
@@ -331,6 +357,7 @@ static int run_filter(const Geom& g, float* output, const float* input, const fl
     } else {
         if (ev) { PL_CUDA(cudaEventRecord(ev[1], st)); }
         zero_rows<<<wide, 256, 0, st>>>(hdr, v0, v64, padded_vd(vd));
+        PL_COUNT_LAUNCHES(1);
         if (ev) { PL_CUDA(cudaEventRecord(ev[2], st)); }
     }
     if (!(phases & PH_APPLY)) {
@@ -341,14 +368,16 @@ static int run_filter(const Geom& g, float* output, const float* input, const fl
     if (v64) {
         const size_t smem = SplatDet<PD>::bytes(vd);
         if (smem > 200 * 1024) return PL_UNSUPPORTED_DIMS;
-        PL_CUDA(cudaFuncSetAttribute(splat_tiles_det<PD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        PL_TRY((ensure_dynamic_smem<splat_tiles_det<PD>>(smem)));
         absmax_kernel<<<wide, 256, 0, st>>>(input, (u64)g.batch * g.n * (vd - 1), hdr);
         splat_tiles_det<PD><<<tile_grid(g), TP, smem, st>>>(g, input, hdr, tile_info, rec, rec_w, list_ref, v64, vd);
         convert_fixed<<<wide, 256, 0, st>>>(hdr, v64, v0, padded_vd(vd));
+        PL_COUNT_LAUNCHES(2);   // absmax_kernel, convert_fixed (the splat itself is counted below)
     } else {
         rc = PL_DISPATCH_VD(launch_splat, PD, vd, g, input, hdr, tile_info, rec, rec_w, list_ref, v0, vd, st);
     }
     if (rc != PL_OK) return rc;
+    PL_COUNT_LAUNCHES(1 + (PD + 1) + 1);   // splat, the blur passes, slice
     if (ev) PL_CUDA(cudaEventRecord(ev[3], st));
     float* src = v0;
     float* dst = v1;
@@ -389,10 +418,8 @@ static int run_filter_f64(const Geom& g, double* output, const double* input, co
 
     PL_CUDA(cudaMemsetAsync(hdr, 0, sizeof(Header), st));
     if (g.num_tiles == 0) return PL_OK;
-    PL_CUDA(cudaFuncSetAttribute(build_tiles<PD, double>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 (int)Cfg<PD>::BUILD_SMEM));
-    PL_CUDA(cudaFuncSetAttribute(splat_tiles_f64<PD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 (int)Splat64<PD>::BYTES));
+    PL_TRY((ensure_dynamic_smem<build_tiles<PD, double>>(Cfg<PD>::BUILD_SMEM)));
+    PL_TRY((ensure_dynamic_smem<splat_tiles_f64<PD>>(Splat64<PD>::BYTES)));
     const int wide = num_sms() * 8;
     int table_log2 = 0;
     while ((1ull << table_log2) < L.table_slots) table_log2++;
@@ -437,6 +464,7 @@ static int run_filter_f64(const Geom& g, double* output, const double* input, co
         double* tmp = src; src = dst; dst = tmp;
     }
     slice_tiles_f64<PD><<<tile_grid(g), TP, 0, st>>>(g, output, hdr, tile_info, rec, rec_w, list_ref, src, vd);
+    PL_COUNT_LAUNCHES(6 + 1 + (PD + 1) + 1);   // build, index (4) and zero_rows; splat; blur passes; slice
     PL_CUDA(cudaGetLastError());
     return PL_OK;
 }
@@ -495,7 +523,6 @@ static int filter_common(const Geom& g, float* output, const float* input, const
 // loads the library, until the process exits.  In host code the array's name is only a handle; the
 // device address comes from cudaGetSymbolAddress, once per device, with that device current.
 static __device__ __align__(256) unsigned char g_static_scratch[PL_STATIC_SCRATCH_BYTES];
-constexpr int MAX_DEVICES = 64;
 static void* g_static_scratch_addr[MAX_DEVICES] = {nullptr};
 static std::mutex g_static_scratch_mutex;
 
@@ -895,7 +922,7 @@ int pl_crf_update_f32(float* q_out, const float* unaries, const float* q_bilater
     if (blocks > 0x7FFFFFFFll) return PL_INVALID_ARGUMENT;
 #define PL_CRF_LAUNCH(TPB, LT)                                                                                   \
     do {                                                                                                         \
-        PL_CUDA(cudaFuncSetAttribute(crf_update<TPB, LT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+        PL_TRY((ensure_dynamic_smem<crf_update<TPB, LT>>(smem)));                                                \
         crf_update<TPB, LT><<<(unsigned)blocks, TPB, smem, st>>>(q_out, unaries, q_bilateral, q_spatial,         \
                                                                  compatibility, bilateral_weight, spatial_weight, \
                                                                  n_points, n_labels);                            \
@@ -904,10 +931,13 @@ int pl_crf_update_f32(float* q_out, const float* unaries, const float* q_bilater
     if (n_labels == 21 && !compatibility) PL_CRF_LAUNCH(256, 21);
     else if (n_labels <= 32) PL_CRF_LAUNCH(256, 0);
     else PL_CRF_LAUNCH(128, 0);
+    PL_COUNT_LAUNCHES(1);
 #undef PL_CRF_LAUNCH
     PL_CUDA(cudaGetLastError());
     return PL_OK;
 }
+
+unsigned long long pl_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
 int pl_debug_direct_index(int enable) {
     const int was = g_direct_index_enabled;
@@ -921,7 +951,13 @@ int pl_profile_next_call(void** stage_events) {
 }
 
 int pl_lattice_stats(const void* workspace, pl_stats* stats, void* stream) {
-    if (!workspace || !stats) return PL_INVALID_ARGUMENT;
+    if (!stats) return PL_INVALID_ARGUMENT;
+    if (!workspace) {   // the built-in scratch of pl_lattice_filter_f32_noalloc on the current device
+        void* scratch = nullptr;
+        const int rc = static_scratch_of_current_device(&scratch);
+        if (rc != PL_OK) return rc;
+        workspace = scratch;
+    }
     Header h;
     PL_CUDA(cudaMemcpyAsync(&h, workspace, sizeof(Header), cudaMemcpyDeviceToHost, (cudaStream_t)stream));
     PL_CUDA(cudaStreamSynchronize((cudaStream_t)stream));

@@ -167,8 +167,11 @@ splat_tiles_fast(Geom g, const float* __restrict__ input, Header* hdr, const int
     SplatCommon<PD>::template sort_splats<PD + 1>(valid, l, w, nloc, sorted_s, cur_s, nullptr, wsum_s);
 
     if (bulk_ok) {
-        if (!mbar_wait(&bar, 0)) {
-            atomicOr(&hdr->status, 1u << PL_INTERNAL_ERROR);
+        // the outcome of the bounded wait is made uniform over the CTA: either every thread goes on or
+        // every thread leaves (after one more bounded wait, so that no copy lands in a CTA that is gone)
+        if (!__syncthreads_and(mbar_wait(&bar, 0) ? 1 : 0)) {
+            if (tid == 0) atomicOr(&hdr->status, 1u << PL_INTERNAL_ERROR);
+            mbar_wait(&bar, 0);
             return;
         }
     } else {
@@ -300,11 +303,9 @@ splat_tiles_rows(Geom g, const float* __restrict__ input, Header* hdr, const int
 
     SplatCommon<PD>::template sort_splats<WL>(valid, l, w, nloc, sorted_s, cur_s, nullptr, wsum_s);
     pc.mark();
+    bool arrived = true;   // bulk form: did this thread see the copies complete within the bounded wait
     if (bulk_ok) {
-        if (!mbar_wait(&bar, 0)) {
-            atomicOr(&hdr->status, 1u << PL_INTERNAL_ERROR);
-            return;
-        }
+        arrived = mbar_wait(&bar, 0);
         constexpr int MAXE = (16 * C + 31) / 32;   // elements per lane of a tile row (TX <= 16)
         for (int ly = warp; ly < g.TY; ly += TP / 32) {
             // valid points of this tile row: its first point's validity and the row's width
@@ -342,7 +343,14 @@ splat_tiles_rows(Geom g, const float* __restrict__ input, Header* hdr, const int
                 for (int j = C + 1; j < VP; j++) region[lane * VP + j] = 0.f;
             }
         }
-        __syncthreads();
+        // this barrier also makes the outcome of the bounded wait uniform over the CTA: either every
+        // thread goes on or every thread leaves (after one more bounded wait, so that no copy lands in
+        // a CTA that is gone)
+        if (!__syncthreads_and(arrived ? 1 : 0)) {
+            if (tid == 0) atomicOr(&hdr->status, 1u << PL_INTERNAL_ERROR);
+            mbar_wait(&bar, 0);
+            return;
+        }
     } else {
         cp_async_wait_all();
         __syncthreads();

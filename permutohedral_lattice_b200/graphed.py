@@ -2,7 +2,7 @@
 a call cost more than the kernels, and a graph replay issues them with one launch."""
 import torch
 
-from .lattice_filter import lattice_filter_raw
+from .lattice_filter import FilterCall, lattice_filter_raw
 
 
 class GraphedLatticeFilter:
@@ -17,11 +17,17 @@ class GraphedLatticeFilter:
                                                                           dtype=torch.float32, device=device)
         self.output = torch.empty_like(self.input)
         args = (bilateral, theta_alpha, theta_beta, theta_gamma, reverse, mode)
-        # one ordinary call first: sets kernel attributes and sizes the workspace outside the capture
+        # The graph owns its workspace: the addresses baked into the captured launches must never be
+        # handed to another caller, as a workspace taken from the shared per-stream cache could be.
+        call = FilterCall(tuple(input_shape), None if reference_shape is None else tuple(reference_shape), bilateral,
+                          theta_alpha, theta_beta, theta_gamma)
+        with torch.cuda.device(device):
+            self._workspace = torch.empty(max(1, call.workspace_bytes()), dtype=torch.uint8, device=device)
+        # one ordinary call first: sets kernel attributes outside the capture
         side = torch.cuda.Stream(device)
         side.wait_stream(torch.cuda.current_stream(device))
         with torch.cuda.stream(side):
-            _, self._workspace, _ = lattice_filter_raw(self.input, self.reference, *args, out=self.output)
+            lattice_filter_raw(self.input, self.reference, *args, out=self.output, workspace=self._workspace)
         torch.cuda.current_stream(device).wait_stream(side)
         torch.cuda.synchronize(device)
         self.graph = torch.cuda.CUDAGraph()

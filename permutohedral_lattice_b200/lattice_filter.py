@@ -125,14 +125,19 @@ def lattice_filter_raw(input_image, reference_image, bilateral=True, theta_alpha
     return out, ws, call
 
 
-def lattice_stats(workspace, stream=None):
-    """Counters of the last call that used `workspace` (synchronises the stream)."""
+def lattice_stats(workspace, stream=None, device=None):
+    """Counters of the last call that used `workspace` (synchronises the stream).  workspace=None reads
+    those of the last pl_lattice_filter_f32_noalloc call on `device` (default: the current one)."""
     st = capi.PlStats()
+    if workspace is not None:
+        device = workspace.device
+    elif device is None:
+        device = torch.device("cuda", torch.cuda.current_device())
     if stream is None:
-        stream = _stream_handle(workspace.device)
-    with torch.cuda.device(workspace.device):
-        capi.check(capi.lib().pl_lattice_stats(workspace.data_ptr(), ctypes.byref(st), stream),
-                   "pl_lattice_stats")
+        stream = _stream_handle(device)
+    with torch.cuda.device(device):
+        capi.check(capi.lib().pl_lattice_stats(0 if workspace is None else workspace.data_ptr(),
+                                               ctypes.byref(st), stream), "pl_lattice_stats")
     return st
 
 
@@ -176,6 +181,10 @@ class Lattice:
                 call.r, int(call.bilateral), call.theta[0], call.theta[1], call.theta[2], call.vd,
                 self.workspace.data_ptr(), self.workspace.numel(), self.max_entries, _stream_handle(device)),
                 "pl_lattice_build_f32")
+            if self.max_entries > 0:   # a bound chosen by the caller may be too small: known on the device only
+                st = lattice_stats(self.workspace)
+                if st.device_status != capi.PL_OK:
+                    raise capi.PlError(st.device_status, "Lattice (device, max_entries=%d)" % self.max_entries)
 
     def apply(self, input_image, reverse=False, mode="atomic", out=None):
         """Filters input_image [B, *S, C] (C <= max_channels) through the lattice."""
@@ -285,7 +294,7 @@ def compute_positions(reference_image, spatial_dims, spatial_std, feature_std, d
 
 
 def filter_positions(input_values, positions, reverse=False, mode="atomic", max_entries=0,
-                     check=None, workspace=None):
+                     check=None, workspace=None, out=None):
     """The LatticeFilter functor (src/LatticeFilterKernel.h:28-38) on [batch, n, C] values at
     [batch, n, pd] positions (2-D tensors are taken as batch 1).  Returns (output, workspace)."""
     _check_tensor(input_values, "input_values")
@@ -301,7 +310,10 @@ def filter_positions(input_values, positions, reverse=False, mode="atomic", max_
     if tuple(p.shape[:2]) != (batch, n):
         raise ValueError("positions must be [batch, n, pd] matching input_values")
     vd = c + 1
-    out = torch.empty_like(x)
+    if out is None:
+        out = torch.empty_like(x)
+    elif tuple(out.shape) != tuple(x.shape) or out.dtype != x.dtype or not out.is_contiguous():
+        raise ValueError("out must be a contiguous tensor of the input's shape and dtype")
     ws = None
     if batch and n:
         stream = _stream_handle(x.device)

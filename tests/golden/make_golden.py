@@ -4,11 +4,18 @@ it never grows).  Needs the reference tree; run from the repository root:
 
     python tests/golden/make_golden.py          # the fp32 fixtures
     python tests/golden/make_golden.py f64      # the fp64 fixtures (*_f64.npz)
+    python tests/golden/make_golden.py images   # the reference's demo photograph and the two results it ships
 
 Each <case>.npz holds the inputs, the call arguments and what the reference produced: forward and
 reverse outputs, the vertex count, the vertex keys (sorted rows) and each pixel's enclosing-simplex
 keys and barycentric weights.  photo_crop.npz additionally carries a 96x96 crop of the reference's
 demo photograph (Images/input.bmp) as uint8.
+
+`images` re-encodes, pixel for pixel, the golden vectors the reference ships as image files, so that the
+full-size checks against them also run where the reference tree is absent: shipped_input.png
+(Images/input.bmp), shipped_bilateral_out_1.png (Images/bilateral_out_1.bmp, written by
+Tests/bilateral_filter.py:22-31) and shipped_filtered_grey.png (Images/filtered_grey.bmp, written by
+Tests/greyscale_test.py:17-36).
 """
 import os
 import sys
@@ -121,8 +128,22 @@ def main_f64():
              positions=rng.standard_normal((300, 16)) * 1.5, **f64)
 
 
+def main_images():
+    from PIL import Image
+    from oracle import build as B
+    src = os.path.join(B.reference_root(), "Images")
+    for bmp, png in (("input.bmp", "shipped_input.png"), ("bilateral_out_1.bmp", "shipped_bilateral_out_1.png"),
+                     ("filtered_grey.bmp", "shipped_filtered_grey.png")):
+        a = np.array(Image.open(os.path.join(src, bmp)))
+        Image.fromarray(a).save(os.path.join(HERE, png), optimize=True)
+        assert np.array_equal(np.array(Image.open(os.path.join(HERE, png))), a)
+        print(png, a.shape, os.path.getsize(os.path.join(HERE, png)), "bytes")
+
+
 if __name__ == "__main__":
     if sys.argv[1:] == ["f64"]:
         main_f64()
+    elif sys.argv[1:] == ["images"]:
+        main_images()
     else:
         main()

@@ -24,7 +24,7 @@ def assert_outputs_close(got, want, what=""):
 
 def assert_structure_equal(vkeys, vitem, pv, pw, oracle_items, what=""):
     """vkeys [M, pd], vitem [M], pv / pw [B, n, pd+1] from the GPU; oracle_items: LatticeResult per item.
-    Vertex count, vertex key set, per-point simplex keys: bit-exact.  Weights: bit-exact."""
+    Vertex count, vertex key set, per-point simplex keys: bit-exact.  Weights: within one ulp."""
     vkeys, vitem, pv, pw = (t.cpu().numpy() for t in (vkeys, vitem, pv, pw))
     assert len(vkeys) == sum(o.num_vertices for o in oracle_items), what + ": vertex count"
     for b, o in enumerate(oracle_items):
@@ -34,7 +34,12 @@ def assert_structure_equal(vkeys, vitem, pv, pw, oracle_items, what=""):
         assert np.array_equal(sorted_rows(mine), sorted_rows(o.keys)), what + ": vertex key set"
         assert np.all(vitem[pv[b]] == b), what + ": point refers to another item's vertex"
         assert np.array_equal(vkeys[pv[b]], o.pixel_keys()), what + ": per-point simplex keys"
-        assert np.array_equal(bits(pw[b]), bits(o.pix_weight)), what + ": barycentric weights"
+        # Weights: the kernels form the reference's float(double(x) * (1 / (pd + 1))) products in float-float
+        # arithmetic, which can differ from that double rounding in the last bit; one unit in the last place
+        # is what the code promises (keys, which decide the structure, are exact).  Same-sign floats order
+        # like their bit patterns, so the distance in ulps is the difference of the patterns.
+        gb, ob = bits(pw[b]).astype(np.int64), bits(o.pix_weight).astype(np.int64)
+        assert np.abs(gb - ob).max() <= 1, what + ": barycentric weights differ by more than one ulp"
 
 
 def run_op(inp, ref, bilateral, ta, tb, tg, reverse, **kw):

@@ -112,6 +112,9 @@ def test_volume_config_two_items_full_size(gpu, oracle):
     st, (vk, vi, pv, pw) = gpu.export_op(ws, call, r)
     gpu.assert_structure_equal(vk, vi, pv, pw, items, w.name)
     gpu.assert_outputs_close(out.cpu().numpy(), want, w.name)
+    want_f = oracle.lattice_filter(w.input, w.reference, True, w.theta_alpha, w.theta_beta, 1.0, False)
+    got_f = gpu.run_op(w.input, w.reference, True, w.theta_alpha, w.theta_beta, 1.0, False)[0]
+    gpu.assert_outputs_close(got_f.cpu().numpy(), want_f, w.name + " forward")
 
 
 def test_pd16_config_one_item_full_size(gpu, oracle):

@@ -44,6 +44,10 @@ def _worker(rank, world, port, batch, result_dir):
     kw = dict(bilateral=True, theta_alpha=4.0, theta_beta=0.25, theta_gamma=1.0, reverse=False)
     full = lattice_filter_sharded(inp, ref, filter_fn=_oracle_filter, gather=True, **kw)
     mine = lattice_filter_sharded(inp, ref, filter_fn=_oracle_filter, gather=False, **kw)
+    on_one = lattice_filter_sharded(inp, ref, filter_fn=_oracle_filter, gather=True, dst=1, **kw)
+    assert (on_one is None) == (rank != 1)
+    if rank == 1:
+        np.save(os.path.join(result_dir, "on_one.npy"), on_one.numpy())
     np.save(os.path.join(result_dir, "full_%d.npy" % rank), full.numpy())
     np.save(os.path.join(result_dir, "mine_%d.npy" % rank), mine.numpy())
     dist.barrier()
@@ -61,6 +65,7 @@ def test_two_rank_sharded_filter_matches_single_process(batch, tmp_path):
     ref = rng.random((batch, 12, 10, 3), dtype=np.float32)
     inp = rng.random((batch, 12, 10, 2), dtype=np.float32)
     want = O.lattice_filter(inp, ref, True, 4.0, 0.25, 1.0, False)
+    assert np.array_equal(np.load(tmp_path / "on_one.npy").view(np.uint32), want.view(np.uint32))
     for rank in range(2):
         full = np.load(tmp_path / ("full_%d.npy" % rank))
         assert np.array_equal(full.view(np.uint32), want.view(np.uint32))

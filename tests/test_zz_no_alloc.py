@@ -57,7 +57,36 @@ def test_noalloc_refuses_sizes_beyond_its_scratch():
     rng = np.random.default_rng(3)
     blocks = np.repeat(np.repeat(rng.random((1, 16, 16, 3), dtype=np.float32), 16, 1), 16, 2)
     img = torch.from_numpy(np.ascontiguousarray(blocks)).cuda()
+    import permutohedral_lattice_b200 as plb
     rc, out = _call_noalloc(img, img, [256, 256], True, 8.0, 0.125, 1.0, False, max_entries=200000)
     assert rc == capi.PL_OK
-    torch.cuda.synchronize()
+    # whether the lattice stayed within max_entries is known on the device only: the caller has no
+    # workspace pointer, so the counters of the built-in scratch are read with a null workspace
+    st = plb.lattice_stats(None)
+    assert st.device_status == capi.PL_OK and 0 < st.num_vertices <= st.num_entries <= 200000
+    want, ws, _ = plb.lattice_filter_raw(img, img, True, 8.0, 0.125, 1.0, False, max_entries=200000)
+    assert plb.lattice_stats(ws).num_vertices == st.num_vertices
+    w, g = want.cpu().numpy().astype(np.float64), out.cpu().numpy().astype(np.float64)
+    assert np.isfinite(g).all()
+    assert np.linalg.norm(g - w) / np.linalg.norm(w) <= REL_L2_TOL
+    assert np.abs(g - w).max() <= MAX_ABS_TOL
+
+
+def test_noalloc_reports_a_max_entries_that_was_too_small():
+    """The call itself returns PL_OK (nothing is known on the host); the device sets a status bit, every
+    later kernel of the call stands down, and the output is filled with NaN.  Nothing faults."""
+    import torch
+    import permutohedral_lattice_b200 as plb
+    from permutohedral_lattice_b200 import capi
+    rng = np.random.default_rng(5)
+    img = torch.from_numpy(rng.random((1, 64, 64, 3), dtype=np.float32)).cuda()
+    rc, out = _call_noalloc(img, img, [64, 64], True, 8.0, 0.125, 1.0, False, max_entries=100)
+    assert rc == capi.PL_OK
+    st = plb.lattice_stats(None)
+    assert st.device_status == capi.PL_CAPACITY_EXCEEDED
+    assert torch.isnan(out).all()
+    # the scratch is usable again by the next call
+    rc, out = _call_noalloc(img, img, [64, 64], True, 8.0, 0.125, 1.0, False)
+    assert rc == capi.PL_OK
+    assert plb.lattice_stats(None).device_status == capi.PL_OK
     assert torch.isfinite(out).all()
