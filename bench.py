@@ -616,8 +616,9 @@ def main():
         "e2e": {"value": e2e_value, "unit": "Mpixels/s", "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms, "wall_ms_per_step": e2e_wall_ms,
                 "copy_only_ms_per_step": copy_ms,
-                "note": "HostPipeline from pinned host buffers, single-item chunks on 4 streams; copy_only = the "
-                        "same copies on the same streams without the filter (what the host link allows)"},
+                "note": "HostPipeline from pinned host buffers (two-item chunks, single items at both ends of a "
+                        "call, 4 streams); copy_only = the same copies on the same streams without the filter "
+                        "(what the host link allows)"},
         "gpu_launches": int(launches) * world,
         "launches_per_call": int(launches) // max(1, len(block_ms) * args.steps * calls_per_step),
         "roofline": roofline, "roofline_call": roofline_call,

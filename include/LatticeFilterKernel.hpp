@@ -84,7 +84,7 @@ struct Abi;
 template <>
 struct Abi<float> {
     static int workspace_bytes(int batch, int n, int pd, int vd, int nsd, const int* sd, size_t* bytes) {
-        return pl_workspace_bytes(batch, n, pd, vd, nsd, sd, 0, bytes);
+        return pl_workspace_bytes(batch, n, pd, vd, nsd, sd, 0, PL_MODE_ATOMIC, bytes);
     }
     static int compute_positions(const float* ref, float* pos, int n, int r, int nsd, const int* sd, float s_std,
                                  float f_std, void* stream) {

@@ -58,11 +58,16 @@ const char* pl_last_cuda_error(void);
 /* Bytes of device workspace for `batch` items of `n` points each.  spatial_dims (HOST array, product
  * n) must be the one later given to pl_lattice_filter_f32; pass NULL for pl_filter_f32 (points are
  * then tiled in index order).  max_entries bounds the lattice entries the call may create over the
- * whole batch; 0 means the worst case batch*n*(pd+1), which can never overflow.  Replaces the
- * scratch allocations of PermutohedralLatticeGPU's constructor
- * (src/PermutohedralLatticeGPU.cuh:434-451) and src/DeviceMemoryAllocator.h:47-120. */
+ * whole batch; 0 means the worst case batch*n*(pd+1), which can never overflow.  A smaller bound (a
+ * previous call's pl_stats.num_entries for similar data, with some margin) shrinks everything that
+ * is indexed by entry or by vertex, which is most of the workspace; a call that outgrows it reports
+ * PL_CAPACITY_EXCEEDED through pl_lattice_stats, fills its output with NaN and can be repeated with a
+ * larger bound.  mode: the pl_mode the workspace will serve; PL_MODE_DETERMINISTIC adds the 64-bit
+ * sums (a workspace sized for it serves both modes).  Replaces the scratch allocations of
+ * PermutohedralLatticeGPU's constructor (src/PermutohedralLatticeGPU.cuh:434-451) and
+ * src/DeviceMemoryAllocator.h:47-120. */
 int pl_workspace_bytes(int batch, int n, int pd, int vd, int n_spatial_dims, const int* spatial_dims,
-                       int64_t max_entries, size_t* bytes);
+                       int64_t max_entries, int mode, size_t* bytes);
 
 /* positions[n*pd] (device) <- feature vectors: for each spatial dimension s (row-major pixel order,
  * last dimension fastest) coordinate / spatial_std, then reference[c] / feature_std.

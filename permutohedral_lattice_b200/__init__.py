@@ -5,3 +5,5 @@ from .lattice_filter import (compute_positions, export_lattice, filter_positions
 from .host_pipeline import HostPipeline  # noqa: F401,E402
 from .graphed import GraphedLatticeFilter  # noqa: F401,E402
 from .crf import DenseCRF  # noqa: F401,E402
+from .capi import PlError  # noqa: F401,E402
+from .sharding import OutputGather, lattice_filter_sharded, shard_range  # noqa: F401,E402

@@ -5,7 +5,8 @@ import ctypes
 import os
 
 PKG = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(PKG, "libpl_lattice.so")
+# PL_LATTICE_LIB names another build of the same library (a variant under test); default: the in-tree one
+LIB_PATH = os.environ.get("PL_LATTICE_LIB") or os.path.join(PKG, "libpl_lattice.so")
 
 PL_OK = 0
 PL_INVALID_ARGUMENT = 1
@@ -64,7 +65,7 @@ def lib():
         L.pl_strerror.argtypes = [i]
         L.pl_strerror.restype = ctypes.c_char_p
         L.pl_last_cuda_error.restype = ctypes.c_char_p
-        L.pl_workspace_bytes.argtypes = [i, i, i, i, i, ip, i64, ctypes.POINTER(ctypes.c_size_t)]
+        L.pl_workspace_bytes.argtypes = [i, i, i, i, i, ip, i64, i, ctypes.POINTER(ctypes.c_size_t)]
         L.pl_compute_positions_f32.argtypes = [vp, vp, i, i, i, ip, f, f, vp]
         L.pl_filter_f32.argtypes = [vp, vp, vp, i, i, i, i, i, vp, ctypes.c_size_t, i64, i, vp]
         L.pl_lattice_filter_f32.argtypes = [vp, vp, vp, i, i, ip, i, i, i, f, f, f, i, vp,
@@ -77,7 +78,7 @@ def lib():
         L.pl_lattice_build_positions_f32.argtypes = [vp, i, i, i, i, vp, ctypes.c_size_t, i64, vp]
         L.pl_lattice_apply_f32.argtypes = [vp, vp, i, i, i, i, i, i, i, ip, vp, ctypes.c_size_t, i64, vp]
         d = ctypes.c_double
-        L.pl_workspace_bytes_f64.argtypes = L.pl_workspace_bytes.argtypes
+        L.pl_workspace_bytes_f64.argtypes = [i, i, i, i, i, ip, i64, ctypes.POINTER(ctypes.c_size_t)]
         L.pl_compute_positions_f64.argtypes = [vp, vp, i, i, i, ip, d, d, vp]
         L.pl_filter_f64.argtypes = [vp, vp, vp, i, i, i, i, i, vp, ctypes.c_size_t, i64, vp]
         L.pl_lattice_filter_f64.argtypes = [vp, vp, vp, i, i, ip, i, i, i, d, d, d, i, vp, ctypes.c_size_t,

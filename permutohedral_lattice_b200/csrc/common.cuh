@@ -49,7 +49,7 @@ struct Header {   // first 256 bytes of the workspace
 };
 
 struct Layout {   // byte offsets into the workspace
-    size_t tile_info, rec, rec_w, list_keys, list_ref, vid, vowner, table, nbr, v0, v1, v64, total;
+    size_t tile_info, rec, rec_w, list_keys, list_ref, vid, vkeys, table, nbr, v0, v1, v64, total;
     u64 max_entries;   // capacity of entry- and vertex-indexed arrays
     u64 table_slots;   // allocated slots (power of two)
 };
@@ -92,6 +92,16 @@ __device__ __forceinline__ bool key_equal(const Key<KW>& a, const Key<KW>& b) {
 #pragma unroll
     for (int j = 0; j < KW; j++) eq = eq && (a.w[j] == b.w[j]);
     return eq;
+}
+
+// Key read straight from L2 (no L1): for data that another CTA of the SAME launch may have written.
+template <int KW>
+__device__ __forceinline__ Key<KW> load_key_l2(const Key<KW>* p) {
+    Key<KW> k;
+    const unsigned long long* w = reinterpret_cast<const unsigned long long*>(p);
+#pragma unroll
+    for (int j = 0; j < KW; j++) k.w[j] = __ldcg(w + j);
+    return k;
 }
 
 // 16-bit field f of a key.  Fields 0..PD-1: lattice coordinates biased by 0x8000 (so that adding small

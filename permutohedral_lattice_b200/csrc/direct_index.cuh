@@ -50,61 +50,53 @@ __global__ void clear_direct(Header* hdr, u32* __restrict__ table, u64 slots) {
 template <int PD>
 __global__ void __launch_bounds__(256)
 insert_direct(Header* hdr, Direct d, u32* __restrict__ table, const Key<Cfg<PD>::KW>* __restrict__ list_keys,
-              u32* __restrict__ list_ref, u32* __restrict__ vid, u32* __restrict__ vowner) {
-    if (call_failed(hdr)) return;
+              u32* __restrict__ list_ref, u32* __restrict__ vid, Key<Cfg<PD>::KW>* __restrict__ vkeys,
+              VertexInit vi) {
+    constexpr int KW = Cfg<PD>::KW;
+    __shared__ InsertRound rd;
+    if (threadIdx.x == 0) rd.count = 0;
+    if (call_failed(hdr)) return;   // (its barrier also publishes rd.count)
     const u32 T = hdr->num_entries;
-    __shared__ u32 warp_cnt[8];
-    __shared__ u32 block_base;
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    for (u32 start = blockIdx.x * 256u; start < T; start += gridDim.x * 256u) {
-        const u32 t = start + threadIdx.x;
-        bool winner = false;
-        if (t < T) {
-            u32 owner = t;
-            u64 s;
-            if (direct_slot<PD>(d, list_keys[t], s)) {
-                const u32 cur = atomicCAS(&table[s], DIRECT_EMPTY, t);
-                winner = cur == DIRECT_EMPTY;
-                if (!winner) owner = cur;
-            } else {
-                atomicOr(&hdr->status, 1u << PL_INTERNAL_ERROR);   // the host's bounds missed a point's vertex
+    const u32 stride = gridDim.x * 256u;
+    for (u32 start = blockIdx.x * 256u; start < T;) {
+        for (int c = 0; c < INSERT_CHUNKS && start < T; c++, start += stride) {
+            const u32 t = start + threadIdx.x;
+            bool winner = false;
+            u64 s = 0;
+            if (t < T) {
+                u32 ref = t;
+                if (direct_slot<PD>(d, list_keys[t], s)) {
+                    const u32 cur = atomicCAS(&table[s], DIRECT_EMPTY, t);
+                    winner = cur == DIRECT_EMPTY;
+                    if (!winner) ref = cur;   // owning entry, or (VERTEX_FLAG set) the vertex itself
+                } else {
+                    atomicOr(&hdr->status, 1u << PL_INTERNAL_ERROR);   // the host's bounds missed a point's vertex
+                }
+                list_ref[t] = ref;
             }
-            list_ref[t] = owner;
+            round_add_winner(rd, winner, t, (u32)s);
         }
-        const u32 ballot = __ballot_sync(0xFFFFFFFFu, winner);
-        if (lane == 0) warp_cnt[warp] = __popc(ballot);
-        __syncthreads();
-        if (threadIdx.x == 0) {
-            u32 tot = 0;
-#pragma unroll
-            for (int w = 0; w < 8; w++) { u32 c = warp_cnt[w]; warp_cnt[w] = tot; tot += c; }
-            block_base = tot ? atomicAdd(&hdr->num_vertices, tot) : 0u;
-        }
-        __syncthreads();
-        if (winner) {
-            const u32 v = block_base + warp_cnt[warp] + __popc(ballot & ((1u << lane) - 1u));
-            vid[t] = v;
-            vowner[v] = t;
-        }
-        __syncthreads();
+        finish_round<KW>(hdr, rd, list_keys, vid, vkeys, vi,
+                         [&](u32 slot, u32 v) { table[slot] = VERTEX_FLAG | v; });
     }
 }
 
 // The "+" neighbour of vertex v along axis a (src/PermutohedralLatticeCPU.h:381-388) by one load of
-// its slot; the same result fills that neighbour's "-" slot.
+// its slot (every slot carries a vertex index by now); the same result fills that neighbour's "-" slot.
 template <int PD>
 __global__ void __launch_bounds__(256)
-link_neighbours_direct(const Header* hdr, Direct d, const u32* __restrict__ table,
-                       const Key<Cfg<PD>::KW>* __restrict__ list_keys, const u32* __restrict__ vid,
-                       const u32* __restrict__ vowner, int* __restrict__ nbr, u64 max_entries) {
+link_neighbours_direct(const Header* hdr, Direct d, const u32* __restrict__ table, u32* __restrict__ list_ref,
+                       const u32* __restrict__ vid, const Key<Cfg<PD>::KW>* __restrict__ vkeys,
+                       int* __restrict__ nbr, u64 max_entries) {
     constexpr int KW = Cfg<PD>::KW;
     if (hdr->status != 0) return;
+    resolve_entries(hdr, list_ref, vid);
     const u32 M = hdr->num_vertices;
     const u64 items = (u64)M * (PD + 1);
     for (u64 e = (u64)blockIdx.x * blockDim.x + threadIdx.x; e < items; e += (u64)gridDim.x * blockDim.x) {
         const u32 v = (u32)(e / (PD + 1));
         const int a = (int)(e - (u64)v * (PD + 1));
-        const Key<KW> k = list_keys[vowner[v]];
+        const Key<KW> k = vkeys[v];
         Key<KW> nk;
 #pragma unroll
         for (int j = 0; j < KW; j++) nk.w[j] = 0;
@@ -115,7 +107,7 @@ link_neighbours_direct(const Header* hdr, Direct d, const u32* __restrict__ tabl
         if (!direct_slot<PD>(d, nk, s)) continue;
         const u32 o = table[s];
         if (o == DIRECT_EMPTY) continue;
-        const u32 u = vid[o];
+        const u32 u = o & ~VERTEX_FLAG;
         nbr[((u64)a * max_entries + v) * 2] = (int)u;
         nbr[((u64)a * max_entries + u) * 2 + 1] = (int)v;
     }

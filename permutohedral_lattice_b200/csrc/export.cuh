@@ -58,15 +58,14 @@ export_points(Geom g, const Header* hdr, const int2* __restrict__ tile_info, con
 }
 
 template <int PD>
-__global__ void export_vertices(const Header* hdr, const Key<Cfg<PD>::KW>* __restrict__ list_keys,
-                                const u32* __restrict__ vowner, long long max_vertices,
+__global__ void export_vertices(const Header* hdr, const Key<Cfg<PD>::KW>* __restrict__ vkeys, long long max_vertices,
                                 int16_t* __restrict__ vertex_keys, int32_t* __restrict__ vertex_item) {
     constexpr int KW = Cfg<PD>::KW;
     if (hdr->status != 0) return;
     const u32 M = hdr->num_vertices;
     for (u64 v = (u64)blockIdx.x * blockDim.x + threadIdx.x; v < M && v < (u64)max_vertices;
          v += (u64)gridDim.x * blockDim.x) {
-        const Key<KW> k = list_keys[vowner[v]];
+        const Key<KW> k = vkeys[v];
         if (vertex_keys) {
 #pragma unroll
             for (int i = 0; i < PD; i++) vertex_keys[v * PD + i] = (int16_t)(key_get<KW>(k, i) ^ 0x8000);

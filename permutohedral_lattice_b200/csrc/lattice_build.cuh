@@ -1,5 +1,5 @@
 // Lattice construction: per-tile key generation and de-duplication (build_tiles), the global hash
-// table (clear_table, insert_entries) and the vertex / neighbour tables (link_vertices, link_neighbours).
+// table (clear_table, insert_entries) and the vertex / neighbour tables (insert_entries, link_neighbours).
 #pragma once
 #include <type_traits>
 #include "common.cuh"
@@ -208,134 +208,213 @@ __global__ void clear_table(Header* hdr, u64* __restrict__ table, u32 max_log2) 
 // ---------------------------------------------------------------------------------------------
 // insert_entries
 // ---------------------------------------------------------------------------------------------
-// Returns the index of the entry owning `k` in the table, or -1 if absent.
+// What the insert launch sets up for every vertex it creates, so that no later launch has to: the
+// vertex's key (vertex order), its slots of the neighbour table ("missing") and, when `rows` is given,
+// its value row (zero).
+struct VertexInit {
+    int* nbr;            // [pd + 1][max_entries] pairs
+    u64 max_entries;
+    int pd;
+    void* rows;          // value rows to zero (float rows, or the 64-bit sums of the deterministic mode); may be null
+    u32 row_bytes;       // bytes of one such row (a multiple of 16)
+};
+
+// Entries are inserted in rounds of INSERT_CHUNKS chunks of 256: the winners of a round (entries that
+// created a vertex) are collected in shared memory and numbered with ONE atomic on the global vertex
+// counter.  One atomic per chunk, all on the same address, was what bounded this launch.
+constexpr int INSERT_CHUNKS = 8;
+constexpr u32 VERTEX_FLAG = 0x80000000u;   // low word of a table slot: vertex index (set) or entry index (clear)
+
+struct InsertRound {
+    u32 t[INSERT_CHUNKS * 256];      // winners of the round: entry ...
+    u32 slot[INSERT_CHUNKS * 256];   // ... and the table slot it claimed
+    u32 count, base;
+};
+
+// Appends a winner to the round's list; one shared-memory atomic per warp.
+__device__ __forceinline__ void round_add_winner(InsertRound& rd, bool winner, u32 t, u32 slot) {
+    const unsigned ballot = __ballot_sync(0xFFFFFFFFu, winner);
+    if (!ballot) return;
+    const int lane = threadIdx.x & 31, leader = __ffs(ballot) - 1;
+    u32 first = 0;
+    if (lane == leader) first = atomicAdd(&rd.count, (u32)__popc(ballot));
+    first = __shfl_sync(0xFFFFFFFFu, first, leader);
+    if (winner) {
+        const u32 pos = first + __popc(ballot & ((1u << lane) - 1u));
+        rd.t[pos] = t;
+        rd.slot[pos] = slot;
+    }
+}
+
+// Ends a round: numbers its winners (consecutive vertex indices), writes vid and the vertex-ordered keys,
+// initialises the new vertices, and re-labels the winners' table slots with the vertex index, so that a
+// lookup ends at the slot (tag, vertex) and the vertex's key instead of walking entry -> owner -> vertex.
+// `relabel` writes the slot (hash table: 64-bit slots; direct index: 32-bit slots).  Called by all threads.
+template <int KW, typename Relabel>
+__device__ __forceinline__ void finish_round(Header* hdr, InsertRound& rd, const Key<KW>* __restrict__ list_keys,
+                                             u32* __restrict__ vid, Key<KW>* __restrict__ vkeys,
+                                             const VertexInit& vi, Relabel relabel) {
+    __syncthreads();
+    if (threadIdx.x == 0) rd.base = rd.count ? atomicAdd(&hdr->num_vertices, rd.count) : 0u;
+    __syncthreads();
+    const u32 base = rd.base, tot = rd.count;
+    for (u32 i = threadIdx.x; i < tot; i += 256) {
+        const u32 t = rd.t[i], v = base + i;
+        vid[t] = v;
+        vkeys[v] = list_keys[t];
+        __threadfence();              // the key is visible before the slot says "vertex v"
+        relabel(rd.slot[i], v);
+    }
+    if (tot) {
+        int2* nb = reinterpret_cast<int2*>(vi.nbr);
+        for (int a = 0; a <= vi.pd; a++)
+            for (u32 i = threadIdx.x; i < tot; i += 256) nb[(u64)a * vi.max_entries + base + i] = make_int2(-1, -1);
+        if (vi.rows) {
+            uint4* rows = reinterpret_cast<uint4*>(static_cast<unsigned char*>(vi.rows) + (u64)base * vi.row_bytes);
+            const u32 quads = tot * (vi.row_bytes / 16);
+            for (u32 i = threadIdx.x; i < quads; i += 256) rows[i] = make_uint4(0u, 0u, 0u, 0u);
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) rd.count = 0;
+    __syncthreads();
+}
+
+// Looks key `k` up in the table.  A slot holds (32-bit hash tag, index): the index of the vertex once its
+// creator's round has ended (VERTEX_FLAG set; full key in vkeys), before that the index of the entry that
+// created it (full key in list_keys, which the previous launch has completely written).  Returns the low
+// word of the matching slot, or 0xFFFFFFFF and the first empty slot met in `empty_slot` (~0 if the
+// table is full).
 template <int KW>
-__device__ __forceinline__ int table_find(const u64* __restrict__ table, u64 mask,
-                                          const Key<KW>* __restrict__ list_keys, const Key<KW>& k) {
-    const u64 h = hash_key<KW>(k);
+__device__ __forceinline__ u32 table_probe(const u64* __restrict__ table, u64 mask,
+                                           const Key<KW>* __restrict__ list_keys,
+                                           const Key<KW>* __restrict__ vkeys, const Key<KW>& k, u64 h,
+                                           u64& empty_slot) {
     const u32 tag = (u32)(h >> 32);
     u64 s = h & mask;
     for (u64 it = 0; it <= mask; it++) {
         const u64 cur = table[s];
-        if (cur == EMPTY_SLOT) return -1;
+        if (cur == EMPTY_SLOT) {
+            empty_slot = s;
+            return 0xFFFFFFFFu;
+        }
         if ((u32)(cur >> 32) == tag) {
-            const u32 o = (u32)cur;
-            if (key_equal<KW>(list_keys[o], k)) return (int)o;
+            const u32 low = (u32)cur;
+            const Key<KW>& other = (low & VERTEX_FLAG) ? vkeys[low & ~VERTEX_FLAG] : list_keys[low];
+            if (key_equal<KW>(other, k)) return low;
         }
         s = (s + 1) & mask;
     }
-    return -1;
+    empty_slot = ~0ull;
+    return 0xFFFFFFFFu;
 }
 
 template <int KW>
 __global__ void __launch_bounds__(256)
 insert_entries(Header* hdr, u64* __restrict__ table, const Key<KW>* __restrict__ list_keys,
-               u32* __restrict__ list_ref, u32* __restrict__ vid, u32* __restrict__ vowner) {
-    if (call_failed(hdr)) return;
+               u32* __restrict__ list_ref, u32* __restrict__ vid, Key<KW>* __restrict__ vkeys, VertexInit vi) {
+    __shared__ InsertRound rd;
+    if (threadIdx.x == 0) rd.count = 0;
+    if (call_failed(hdr)) return;   // (its barrier also publishes rd.count)
     const u32 T = hdr->num_entries;
     const u64 mask = (1ull << hdr->table_log2) - 1;
-    __shared__ u32 warp_cnt[8];
-    __shared__ u32 block_base;
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    for (u32 start = blockIdx.x * 256u; start < T; start += gridDim.x * 256u) {
-        const u32 t = start + threadIdx.x;
-        bool winner = false;
-        if (t < T) {
-            const Key<KW> k = list_keys[t];
-            const u64 h = hash_key<KW>(k);
-            const u32 tag = (u32)(h >> 32);
-            const u64 mine = ((u64)tag << 32) | (u64)t;
-            u64 s = h & mask;
-            u32 owner = 0xFFFFFFFFu;
-            for (u64 it = 0; it <= mask; it++) {
-                u64 cur = table[s];
-                if (cur == EMPTY_SLOT) {
-                    cur = atomicCAS(&table[s], EMPTY_SLOT, mine);
-                    if (cur == EMPTY_SLOT) { owner = t; winner = true; break; }
+    const u32 stride = gridDim.x * 256u;
+    for (u32 start = blockIdx.x * 256u; start < T;) {
+        for (int c = 0; c < INSERT_CHUNKS && start < T; c++, start += stride) {
+            const u32 t = start + threadIdx.x;
+            bool winner = false;
+            u64 my_slot = 0;
+            if (t < T) {
+                const Key<KW> k = list_keys[t];
+                const u64 h = hash_key<KW>(k);
+                const u64 mine = (h & 0xFFFFFFFF00000000ull) | (u64)t;
+                u32 ref = 0xFFFFFFFFu;
+                // probe; on an empty slot try to claim it, and keep probing from there if another entry was faster
+                u64 s = h & mask;
+                for (u64 it = 0; it <= mask; it++) {
+                    // slots and vertex keys change during this launch: read them from L2, never from an
+                    // L1 line that may predate another CTA's write
+                    u64 cur = __ldcg(&table[s]);
+                    if (cur == EMPTY_SLOT) {
+                        cur = atomicCAS(&table[s], EMPTY_SLOT, mine);
+                        if (cur == EMPTY_SLOT) { ref = t; winner = true; my_slot = s; break; }
+                    }
+                    if ((u32)(cur >> 32) == (u32)(h >> 32)) {
+                        const u32 low = (u32)cur;
+                        const Key<KW> other = (low & VERTEX_FLAG) ? load_key_l2<KW>(&vkeys[low & ~VERTEX_FLAG])
+                                                                  : list_keys[low];
+                        if (key_equal<KW>(other, k)) { ref = low; break; }
+                    }
+                    s = (s + 1) & mask;
                 }
-                if ((u32)(cur >> 32) == tag) {
-                    const u32 o = (u32)cur;
-                    if (key_equal<KW>(list_keys[o], k)) { owner = o; break; }
+                if (ref == 0xFFFFFFFFu) {
+                    atomicOr(&hdr->status, 1u << PL_INTERNAL_ERROR);
+                    ref = t;
                 }
-                s = (s + 1) & mask;
+                list_ref[t] = ref;   // owning entry, or (VERTEX_FLAG set) the vertex itself
             }
-            if (owner == 0xFFFFFFFFu) {
-                atomicOr(&hdr->status, 1u << PL_INTERNAL_ERROR);
-                owner = t;
-            }
-            list_ref[t] = owner;
+            round_add_winner(rd, winner, t, (u32)my_slot);
         }
-        // vertex indices: one atomic per CTA and chunk
-        const u32 ballot = __ballot_sync(0xFFFFFFFFu, winner);
-        if (lane == 0) warp_cnt[warp] = __popc(ballot);
-        __syncthreads();
-        if (threadIdx.x == 0) {
-            u32 tot = 0;
-#pragma unroll
-            for (int w = 0; w < 8; w++) { u32 c = warp_cnt[w]; warp_cnt[w] = tot; tot += c; }
-            block_base = tot ? atomicAdd(&hdr->num_vertices, tot) : 0u;
-        }
-        __syncthreads();
-        if (winner) {
-            const u32 v = block_base + warp_cnt[warp] + __popc(ballot & ((1u << lane) - 1u));
-            vid[t] = v;
-            vowner[v] = t;
-        }
-        __syncthreads();
+        finish_round<KW>(hdr, rd, list_keys, vid, vkeys, vi, [&](u32 slot, u32 v) {
+            table[slot] = (__ldcg(&table[slot]) & 0xFFFFFFFF00000000ull) | (u64)(VERTEX_FLAG | v);
+        });
+    }
+}
+
+// entry -> vertex: after the insert launch list_ref[t] names the entry that owns t's key; the link launch
+// turns that into the owner's vertex index (first loop of link_neighbours / link_neighbours_direct).
+__device__ __forceinline__ void resolve_entries(const Header* hdr, u32* __restrict__ list_ref,
+                                                const u32* __restrict__ vid) {
+    const u32 T = hdr->num_entries;
+    for (u64 t = (u64)blockIdx.x * blockDim.x + threadIdx.x; t < T; t += (u64)gridDim.x * blockDim.x) {
+        const u32 ref = list_ref[t];
+        list_ref[t] = (ref & VERTEX_FLAG) ? (ref & ~VERTEX_FLAG) : vid[ref];
     }
 }
 
 // ---------------------------------------------------------------------------------------------
-// link_vertices: entry -> vertex, neighbour table preset to "missing", zeroed value rows.
-// link_neighbours: the +-1 neighbours of every vertex along each of the PD+1 lattice axes.
+// link_neighbours: entry -> vertex, then the +-1 neighbours of every vertex along each of the PD+1
+// lattice axes.
 // ---------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(256)
-link_vertices(Header* hdr, u32* __restrict__ list_ref, const u32* __restrict__ vid, int* __restrict__ nbr,
-              float* __restrict__ v0, long long* __restrict__ v64, u64 max_entries, int pd, int vd) {
-    if (hdr->status != 0) return;
-    const u32 T = hdr->num_entries, M = hdr->num_vertices;
-    const u64 gtid = (u64)blockIdx.x * blockDim.x + threadIdx.x;
-    const u64 gsz = (u64)gridDim.x * blockDim.x;
-    for (u64 t = gtid; t < T; t += gsz) list_ref[t] = vid[list_ref[t]];
-    int2* nb = reinterpret_cast<int2*>(nbr);
-    for (int a = 0; a <= pd; a++)
-        for (u64 v = gtid; v < M; v += gsz) nb[(u64)a * max_entries + v] = make_int2(-1, -1);
-    if (vd == 0) return;   // lattice built ahead of its use: rows are zeroed by each apply
-    const u64 cells = (u64)M * padded_vd(vd);
-    if (v64) {
-        for (u64 e = gtid; e < cells; e += gsz) v64[e] = 0;
-    } else {
-        for (u64 e = gtid; e < cells; e += gsz) v0[e] = 0.f;
-    }
-}
-
 // One table lookup per (vertex v, axis a): the neighbour u whose key is v's key with every stored
 // coordinate +1, except coordinate a which moves by -PD (along axis PD no stored coordinate is
 // special; src/PermutohedralLatticeCPU.h:381-388).  Then u is v's "+" neighbour and v is u's "-"
-// neighbour, so the second lookup of the reference is not needed.
+// neighbour, so the second lookup of the reference is not needed.  Keys are read in vertex order
+// (coalesced); every slot carries a vertex index by now, so a lookup is two dependent accesses.
 template <int PD>
 __global__ void __launch_bounds__(256)
 link_neighbours(const Header* hdr, const u64* __restrict__ table,
-                const Key<Cfg<PD>::KW>* __restrict__ list_keys, const u32* __restrict__ vid,
-                const u32* __restrict__ vowner, int* __restrict__ nbr, u64 max_entries) {
+                const Key<Cfg<PD>::KW>* __restrict__ list_keys, u32* __restrict__ list_ref,
+                const u32* __restrict__ vid, const Key<Cfg<PD>::KW>* __restrict__ vkeys, int* __restrict__ nbr,
+                u64 max_entries, void* zero_rows_ptr, u32 zero_row_bytes) {
     constexpr int KW = Cfg<PD>::KW;
     if (hdr->status != 0) return;
+    resolve_entries(hdr, list_ref, vid);
     const u32 M = hdr->num_vertices;
     const u64 mask = (1ull << hdr->table_log2) - 1;
+    if (zero_rows_ptr) {   // streaming stores that overlap the latency of the lookups below
+        uint4* rows = reinterpret_cast<uint4*>(zero_rows_ptr);
+        const u64 quads = (u64)M * (zero_row_bytes / 16);
+        for (u64 i = (u64)blockIdx.x * blockDim.x + threadIdx.x; i < quads; i += (u64)gridDim.x * blockDim.x)
+            rows[i] = make_uint4(0u, 0u, 0u, 0u);
+    }
     const u64 items = (u64)M * (PD + 1);
     for (u64 e = (u64)blockIdx.x * blockDim.x + threadIdx.x; e < items; e += (u64)gridDim.x * blockDim.x) {
-        const u32 v = (u32)(e / (PD + 1));
-        const int a = (int)(e - (u64)v * (PD + 1));
-        const Key<KW> k = list_keys[vowner[v]];
+        // axis-major: neighbouring threads take neighbouring vertices of one axis, so their key loads and
+        // their own slots of the neighbour table are contiguous
+        const int a = (int)(e / M);
+        const u32 v = (u32)(e - (u64)a * M);
+        const Key<KW> k = vkeys[v];
         Key<KW> nk;
 #pragma unroll
         for (int j = 0; j < KW; j++) nk.w[j] = 0;
 #pragma unroll
         for (int i = 0; i < PD; i++) key_set<KW>(nk, i, (u16)(key_get<KW>(k, i) + ((i == a) ? -PD : 1)));
         key_set<KW>(nk, PD, key_get<KW>(k, PD));
-        const int o = table_find<KW>(table, mask, list_keys, nk);
-        if (o >= 0) {
-            const u32 u = vid[o];
+        u64 unused;
+        const u32 low = table_probe<KW>(table, mask, list_keys, vkeys, nk, hash_key<KW>(nk), unused);
+        if (low != 0xFFFFFFFFu) {
+            const u32 u = low & ~VERTEX_FLAG;
             nbr[((u64)a * max_entries + v) * 2] = (int)u;
             nbr[((u64)a * max_entries + u) * 2 + 1] = (int)v;
         }

@@ -7,10 +7,10 @@
 //                   distinct keys become a contiguous run of "entries" in a global list and every
 //                   splat records the 16-bit index of its entry inside the tile.
 //   clear_table     sizes the global hash table from the entry count (on the device) and clears it.
-//   insert_entries  one CAS per entry into the table; the first entry of a key owns a new vertex.
-//   link_vertices   entry -> vertex index; presets the neighbour table, zeroes the value rows.
-//   link_neighbours the +-1 neighbours of every vertex along each of the pd+1 axes: one table lookup
-//                   per vertex and axis fills both directions.
+//   insert_entries  one CAS per entry into the table; the first entry of a key owns a new vertex, whose
+//                   neighbour slots and value row the same launch initialises.
+//   link_neighbours entry -> vertex index; then the +-1 neighbours of every vertex along each of the
+//                   pd+1 axes: one table lookup per vertex and axis fills both directions.
 //   splat_tiles     one CTA per tile: input block staged in shared memory (bulk async copies), splats
 //                   sorted by entry, runs summed in registers, vector reductions into the vertex rows.
 //   blur_axis       pd+1 launches: V'[v] = (V[n1] + 2 V[v] + V[n2]) / 4, Jacobi, ping-pong buffers.
@@ -30,6 +30,7 @@
 #include <stdint.h>
 #include <stdio.h>
 #include <string.h>
+#include <utility>
 
 #include "common.cuh"
 #include "lattice_build.cuh"
@@ -63,6 +64,20 @@ static int cuda_fail(cudaError_t e, const char* where) {
         cudaError_t e_ = (call);                        \
         if (e_ != cudaSuccess) return cuda_fail(e_, #call); \
     } while (0)
+
+// Kernel launch with the error check of every other runtime call.
+template <typename... Params, typename... Args>
+static cudaError_t launch_kernel(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                                 Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
+#define PL_LAUNCH(kernel, grid, block, smem, st, ...) \
+    PL_CUDA(launch_kernel(kernel, dim3(grid), dim3(block), smem, st, __VA_ARGS__))
 
 static size_t align_up(size_t x) { return (x + 255) & ~(size_t)255; }
 
@@ -134,7 +149,9 @@ static int make_geom(Geom& g, int batch, int n, int pd, int n_sdims, const int* 
 }
 
 // real_bytes: 4 for float calls, 8 for double calls (wider weights and value rows, no fixed-point sums).
-static int make_layout(Layout& L, const Geom& g, int pd, int vd, int64_t max_entries_arg, int real_bytes = 4) {
+// with_fixed_point: the workspace also holds the 64-bit sums of the deterministic mode (float calls only).
+static int make_layout(Layout& L, const Geom& g, int pd, int vd, int64_t max_entries_arg, int real_bytes = 4,
+                       bool with_fixed_point = false) {
     const u64 S = (u64)g.batch * (u64)g.n * (u64)(pd + 1);
     if (S >= 0x7FFFFFF0ull) return PL_INVALID_ARGUMENT;
     u64 E = (max_entries_arg <= 0 || (u64)max_entries_arg > S) ? S : (u64)max_entries_arg;
@@ -151,7 +168,7 @@ static int make_layout(Layout& L, const Geom& g, int pd, int vd, int64_t max_ent
     L.list_keys = off; off += align_up(sizeof(u64) * kw_of(pd) * E);
     L.list_ref = off;  off += align_up(sizeof(u32) * E);
     L.vid = off;       off += align_up(sizeof(u32) * E);
-    L.vowner = off;    off += align_up(sizeof(u32) * E);
+    L.vkeys = off;     off += align_up(sizeof(u64) * kw_of(pd) * E);
     L.table = off;     off += align_up(sizeof(u64) * slots);
     L.nbr = off;       off += align_up(sizeof(int) * 2 * (size_t)(pd + 1) * E);
     const size_t row_bytes = real_bytes == 8 ? sizeof(double) * (size_t)padded_vd_f64(vd)
@@ -159,7 +176,7 @@ static int make_layout(Layout& L, const Geom& g, int pd, int vd, int64_t max_ent
     L.v0 = off;        off += align_up(row_bytes * E);
     L.v1 = off;        off += align_up(row_bytes * E);
     L.v64 = off;       // deterministic mode sums (float calls only)
-    if (real_bytes == 4) off += align_up(sizeof(long long) * (size_t)padded_vd(vd) * E);
+    if (real_bytes == 4 && with_fixed_point) off += align_up(sizeof(long long) * (size_t)padded_vd(vd) * E);
     L.total = off;
     return PL_OK;
 }
@@ -247,18 +264,17 @@ static int launch_splat(const Geom& g, const float* input, Header* hdr, const in
         // bulk staging also needs 16-byte aligned landing zones inside the padded tile rows
         const bool bulk = bulk_rows_ok(g, input, VD - 1) && g.TX <= 16 &&
                           (g.TX * (SplatRows<PD, VD>::VP - (VD - 1))) % 4 == 0;
-        splat_tiles_rows<PD, VD><<<tile_grid(g), Cfg<PD>::TP, smem, st>>>(g, input, hdr, tile_info, rec, rec_w,
+        PL_LAUNCH((splat_tiles_rows<PD, VD>), tile_grid(g), Cfg<PD>::TP, smem, st, g, input, hdr, tile_info, rec, rec_w,
                                                                          list_ref, v0, bulk ? 1 : 0);
     } else if constexpr (VD > 0) {
         const size_t smem = SplatFast<PD, VD>::BYTES;
         PL_TRY((ensure_dynamic_smem<splat_tiles_fast<PD, VD>>(smem)));
-        splat_tiles_fast<PD, VD><<<tile_grid(g), Cfg<PD>::TP, smem, st>>>(
-            g, input, hdr, tile_info, rec, rec_w, list_ref, v0, bulk_rows_ok(g, input, VD - 1) ? 1 : 0);
+        PL_LAUNCH((splat_tiles_fast<PD, VD>), tile_grid(g), Cfg<PD>::TP, smem, st, g, input, hdr, tile_info, rec, rec_w, list_ref, v0, bulk_rows_ok(g, input, VD - 1) ? 1 : 0);
     } else {
         const size_t smem = SplatGeneric<PD>::bytes(vd);
         if (smem > 200 * 1024) return PL_UNSUPPORTED_DIMS;
         PL_TRY((ensure_dynamic_smem<splat_tiles_generic<PD>>(smem)));
-        splat_tiles_generic<PD><<<tile_grid(g), Cfg<PD>::TP, smem, st>>>(g, input, hdr, tile_info, rec, rec_w,
+        PL_LAUNCH((splat_tiles_generic<PD>), tile_grid(g), Cfg<PD>::TP, smem, st, g, input, hdr, tile_info, rec, rec_w,
                                                                         list_ref, v0, vd);
     }
     return PL_OK;
@@ -272,15 +288,14 @@ static int launch_slice(const Geom& g, float* output, const Header* hdr, const i
         if (rows_cap > Cfg<PD>::SPLATS) rows_cap = Cfg<PD>::SPLATS;
         const size_t smem = SliceFast<PD, VD>::bytes(rows_cap);
         PL_TRY((ensure_dynamic_smem<slice_tiles_fast<PD, VD>>(smem)));
-        slice_tiles_fast<PD, VD><<<tile_grid(g), Cfg<PD>::TP, smem, st>>>(
-            g, output, hdr, tile_info, rec, rec_w, list_ref, vsrc, rows_cap, bulk_rows_ok(g, output, VD - 1) ? 1 : 0);
+        PL_LAUNCH((slice_tiles_fast<PD, VD>), tile_grid(g), Cfg<PD>::TP, smem, st, g, output, hdr, tile_info, rec, rec_w, list_ref, vsrc, rows_cap, bulk_rows_ok(g, output, VD - 1) ? 1 : 0);
     } else {
         const int rows_cap = rows_cap_for(PD, vd);
         const size_t fixed = sizeof(float) * Cfg<PD>::TP * SliceCfg<PD>::PW + sizeof(int) * Cfg<PD>::TP;
         const size_t smem = sizeof(float) * (size_t)rows_cap * padded_vd(vd) + fixed;
         if (smem > 200 * 1024) return PL_UNSUPPORTED_DIMS;
         PL_TRY((ensure_dynamic_smem<slice_tiles_generic<PD>>(smem)));
-        slice_tiles_generic<PD><<<tile_grid(g), Cfg<PD>::TP, smem, st>>>(g, output, hdr, tile_info, rec, rec_w,
+        PL_LAUNCH((slice_tiles_generic<PD>), tile_grid(g), Cfg<PD>::TP, smem, st, g, output, hdr, tile_info, rec, rec_w,
                                                                         list_ref, vsrc, vd, rows_cap);
     }
     return PL_OK;
@@ -308,7 +323,7 @@ static int run_filter(const Geom& g, float* output, const float* input, const fl
     Key<KW>* list_keys = reinterpret_cast<Key<KW>*>(ws + L.list_keys);
     u32* list_ref = reinterpret_cast<u32*>(ws + L.list_ref);
     u32* vid = reinterpret_cast<u32*>(ws + L.vid);
-    u32* vowner = reinterpret_cast<u32*>(ws + L.vowner);
+    Key<KW>* vkeys = reinterpret_cast<Key<KW>*>(ws + L.vkeys);
     u64* table = reinterpret_cast<u64*>(ws + L.table);
     int* nbr = reinterpret_cast<int*>(ws + L.nbr);
     float* v0 = reinterpret_cast<float*>(ws + L.v0);
@@ -328,35 +343,42 @@ static int run_filter(const Geom& g, float* output, const float* input, const fl
     while ((1ull << table_log2) < L.table_slots) table_log2++;
 
     if (phases & PH_BUILD) {
-        build_tiles<PD><<<tile_grid(g), TP, Cfg<PD>::BUILD_SMEM, st>>>(
-            g, positions, reference, hdr, tile_info, rec, rec_w, list_keys, (u32)L.max_entries);
-        PL_COUNT_LAUNCHES(5);   // build_tiles and the four launches of the index stage below
+        PL_LAUNCH((build_tiles<PD>), tile_grid(g), TP, Cfg<PD>::BUILD_SMEM, st, g, positions, reference, hdr, tile_info, rec, rec_w, list_keys, (u32)L.max_entries);
+        PL_COUNT_LAUNCHES(4);   // build_tiles and the three launches of the index stage below
         if (ev) PL_CUDA(cudaEventRecord(ev[1], st));
         Direct direct;
         bool use_direct = false;
         if constexpr (PD <= MAX_SDIMS) use_direct = make_direct(direct, g, PD, L);
+        // a new vertex's neighbour slots and (when this call also applies) its value row are initialised
+        // by the launch that creates it
+        VertexInit vinit;
+        vinit.nbr = nbr;
+        vinit.max_entries = L.max_entries;
+        vinit.pd = PD;
+        vinit.rows = (phases & PH_APPLY) ? (v64 ? static_cast<void*>(v64) : static_cast<void*>(v0)) : nullptr;
+        vinit.row_bytes = (u32)padded_vd(vd) * (v64 ? 8u : 4u);
         if constexpr (PD <= MAX_SDIMS) {
             if (use_direct) {
                 u32* table32 = reinterpret_cast<u32*>(table);
-                clear_direct<<<wide, 256, 0, st>>>(hdr, table32, direct.slots);
-                insert_direct<PD><<<wide, 256, 0, st>>>(hdr, direct, table32, list_keys, list_ref, vid, vowner);
-                link_vertices<<<wide, 256, 0, st>>>(hdr, list_ref, vid, nbr, v0, v64, L.max_entries, PD,
-                                                    (phases & PH_APPLY) ? vd : 0);
-                link_neighbours_direct<PD><<<wide, 256, 0, st>>>(hdr, direct, table32, list_keys, vid, vowner, nbr,
+                PL_LAUNCH((clear_direct), wide, 256, 0, st, hdr, table32, direct.slots);
+                PL_LAUNCH((insert_direct<PD>), wide, 256, 0, st, hdr, direct, table32, list_keys, list_ref, vid, vkeys, vinit);
+                PL_LAUNCH((link_neighbours_direct<PD>), wide, 256, 0, st, hdr, direct, table32, list_ref, vid, vkeys, nbr,
                                                                  L.max_entries);
             }
         }
         if (!use_direct) {
-            clear_table<<<wide, 256, 0, st>>>(hdr, table, (u32)table_log2);
-            insert_entries<KW><<<wide, 256, 0, st>>>(hdr, table, list_keys, list_ref, vid, vowner);
-            link_vertices<<<wide, 256, 0, st>>>(hdr, list_ref, vid, nbr, v0, v64, L.max_entries, PD,
-                                                (phases & PH_APPLY) ? vd : 0);
-            link_neighbours<PD><<<wide, 256, 0, st>>>(hdr, table, list_keys, vid, vowner, nbr, L.max_entries);
+            // the value rows are zeroed by the link launch, whose lookups leave the memory system idle
+            void* zrows = vinit.rows;
+            vinit.rows = nullptr;
+            PL_LAUNCH((clear_table), wide, 256, 0, st, hdr, table, (u32)table_log2);
+            PL_LAUNCH((insert_entries<KW>), wide, 256, 0, st, hdr, table, list_keys, list_ref, vid, vkeys, vinit);
+            PL_LAUNCH((link_neighbours<PD>), wide, 256, 0, st, hdr, table, list_keys, list_ref, vid, vkeys, nbr,
+                                                      L.max_entries, zrows, vinit.row_bytes);
         }
         if (ev) PL_CUDA(cudaEventRecord(ev[2], st));
     } else {
         if (ev) { PL_CUDA(cudaEventRecord(ev[1], st)); }
-        zero_rows<<<wide, 256, 0, st>>>(hdr, v0, v64, padded_vd(vd));
+        PL_LAUNCH((zero_rows), wide, 256, 0, st, hdr, v0, v64, padded_vd(vd));
         PL_COUNT_LAUNCHES(1);
         if (ev) { PL_CUDA(cudaEventRecord(ev[2], st)); }
     }
@@ -369,15 +391,15 @@ static int run_filter(const Geom& g, float* output, const float* input, const fl
         const size_t smem = SplatDet<PD>::bytes(vd);
         if (smem > 200 * 1024) return PL_UNSUPPORTED_DIMS;
         PL_TRY((ensure_dynamic_smem<splat_tiles_det<PD>>(smem)));
-        absmax_kernel<<<wide, 256, 0, st>>>(input, (u64)g.batch * g.n * (vd - 1), hdr);
-        splat_tiles_det<PD><<<tile_grid(g), TP, smem, st>>>(g, input, hdr, tile_info, rec, rec_w, list_ref, v64, vd);
-        convert_fixed<<<wide, 256, 0, st>>>(hdr, v64, v0, padded_vd(vd));
+        PL_LAUNCH((absmax_kernel), wide, 256, 0, st, input, (u64)g.batch * g.n * (vd - 1), hdr);
+        PL_LAUNCH((splat_tiles_det<PD>), tile_grid(g), TP, smem, st, g, input, hdr, tile_info, rec, rec_w, list_ref, v64, vd);
+        PL_LAUNCH((convert_fixed), wide, 256, 0, st, hdr, v64, v0, padded_vd(vd));
         PL_COUNT_LAUNCHES(2);   // absmax_kernel, convert_fixed (the splat itself is counted below)
     } else {
         rc = PL_DISPATCH_VD(launch_splat, PD, vd, g, input, hdr, tile_info, rec, rec_w, list_ref, v0, vd, st);
     }
     if (rc != PL_OK) return rc;
-    PL_COUNT_LAUNCHES(1 + (PD + 1) + 1);   // splat, the blur passes, slice
+    PL_COUNT_LAUNCHES(1 + 1);   // splat, slice (the blur launches are counted where they are issued)
     if (ev) PL_CUDA(cudaEventRecord(ev[3], st));
     float* src = v0;
     float* dst = v1;
@@ -385,9 +407,10 @@ static int run_filter(const Geom& g, float* output, const float* input, const fl
     for (int step = 0; step <= PD; step++) {
         const int axis = reverse ? PD - step : step;
         const int* nb = nbr + (size_t)axis * L.max_entries * 2;
-        blur_axis<<<wide, 256, 0, st>>>(hdr, nb, src, dst, qpr);
+        PL_LAUNCH((blur_axis), wide, 256, 0, st, hdr, nb, src, dst, qpr);
         float* tmp = src; src = dst; dst = tmp;
     }
+    PL_COUNT_LAUNCHES(PD + 1);
     if (ev) PL_CUDA(cudaEventRecord(ev[4], st));
     rc = PL_DISPATCH_VD(launch_slice, PD, vd, g, output, hdr, tile_info, rec, rec_w, list_ref, src, vd, st);
     if (rc != PL_OK) return rc;
@@ -410,7 +433,7 @@ static int run_filter_f64(const Geom& g, double* output, const double* input, co
     Key<KW>* list_keys = reinterpret_cast<Key<KW>*>(ws + L.list_keys);
     u32* list_ref = reinterpret_cast<u32*>(ws + L.list_ref);
     u32* vid = reinterpret_cast<u32*>(ws + L.vid);
-    u32* vowner = reinterpret_cast<u32*>(ws + L.vowner);
+    Key<KW>* vkeys = reinterpret_cast<Key<KW>*>(ws + L.vkeys);
     u64* table = reinterpret_cast<u64*>(ws + L.table);
     int* nbr = reinterpret_cast<int*>(ws + L.nbr);
     double* v0 = reinterpret_cast<double*>(ws + L.v0);
@@ -425,46 +448,44 @@ static int run_filter_f64(const Geom& g, double* output, const double* input, co
     while ((1ull << table_log2) < L.table_slots) table_log2++;
     const int vp = padded_vd_f64(vd);
 
-    build_tiles<PD, double><<<tile_grid(g), TP, Cfg<PD>::BUILD_SMEM, st>>>(
-        g, positions, reference, hdr, tile_info, rec, rec_w, list_keys, (u32)L.max_entries);
+    PL_LAUNCH((build_tiles<PD, double>), tile_grid(g), TP, Cfg<PD>::BUILD_SMEM, st, g, positions, reference, hdr, tile_info, rec, rec_w, list_keys, (u32)L.max_entries);
     // spatial-only calls index their vertices directly, as the float calls do (the key bounds hold for
     // either arithmetic: the margin is far wider than any rounding)
     Direct direct;
     bool use_direct = false;
     if constexpr (PD <= MAX_SDIMS) use_direct = make_direct(direct, g, PD, L);
     u32* table32 = reinterpret_cast<u32*>(table);
+    VertexInit vinit;
+    vinit.nbr = nbr;
+    vinit.max_entries = L.max_entries;
+    vinit.pd = PD;
+    vinit.rows = v0;   // rows of vp doubles
+    vinit.row_bytes = (u32)vp * 8u;
     if constexpr (PD <= MAX_SDIMS) {
         if (use_direct) {
-            clear_direct<<<wide, 256, 0, st>>>(hdr, table32, direct.slots);
-            insert_direct<PD><<<wide, 256, 0, st>>>(hdr, direct, table32, list_keys, list_ref, vid, vowner);
+            PL_LAUNCH((clear_direct), wide, 256, 0, st, hdr, table32, direct.slots);
+            PL_LAUNCH((insert_direct<PD>), wide, 256, 0, st, hdr, direct, table32, list_keys, list_ref, vid, vkeys, vinit);
+            PL_LAUNCH((link_neighbours_direct<PD>), wide, 256, 0, st, hdr, direct, table32, list_ref, vid, vkeys, nbr,
+                                                             L.max_entries);
         }
     }
     if (!use_direct) {
-        clear_table<<<wide, 256, 0, st>>>(hdr, table, (u32)table_log2);
-        insert_entries<KW><<<wide, 256, 0, st>>>(hdr, table, list_keys, list_ref, vid, vowner);
+        PL_LAUNCH((clear_table), wide, 256, 0, st, hdr, table, (u32)table_log2);
+        PL_LAUNCH((insert_entries<KW>), wide, 256, 0, st, hdr, table, list_keys, list_ref, vid, vkeys, vinit);
+        PL_LAUNCH((link_neighbours<PD>), wide, 256, 0, st, hdr, table, list_keys, list_ref, vid, vkeys, nbr, L.max_entries,
+                                                  nullptr, 0u);
     }
-    // rows of vp doubles are zeroed through the 64-bit branch (vp cells of 8 bytes per vertex)
-    link_vertices<<<wide, 256, 0, st>>>(hdr, list_ref, vid, nbr, nullptr, reinterpret_cast<long long*>(v0),
-                                        L.max_entries, PD, 0);
-    zero_rows<<<wide, 256, 0, st>>>(hdr, nullptr, reinterpret_cast<long long*>(v0), vp);
-    if constexpr (PD <= MAX_SDIMS) {
-        if (use_direct)
-            link_neighbours_direct<PD><<<wide, 256, 0, st>>>(hdr, direct, table32, list_keys, vid, vowner, nbr,
-                                                             L.max_entries);
-    }
-    if (!use_direct)
-        link_neighbours<PD><<<wide, 256, 0, st>>>(hdr, table, list_keys, vid, vowner, nbr, L.max_entries);
-    splat_tiles_f64<PD><<<tile_grid(g), TP, Splat64<PD>::BYTES, st>>>(g, input, hdr, tile_info, rec, rec_w,
+    PL_LAUNCH((splat_tiles_f64<PD>), tile_grid(g), TP, Splat64<PD>::BYTES, st, g, input, hdr, tile_info, rec, rec_w,
                                                                       list_ref, v0, vd);
     double* src = v0;
     double* dst = v1;
     for (int step = 0; step <= PD; step++) {
         const int axis = reverse ? PD - step : step;
-        blur_axis_f64<<<wide, 256, 0, st>>>(hdr, nbr + (size_t)axis * L.max_entries * 2, src, dst, vp / 2);
+        PL_LAUNCH((blur_axis_f64), wide, 256, 0, st, hdr, nbr + (size_t)axis * L.max_entries * 2, src, dst, vp / 2);
         double* tmp = src; src = dst; dst = tmp;
     }
-    slice_tiles_f64<PD><<<tile_grid(g), TP, 0, st>>>(g, output, hdr, tile_info, rec, rec_w, list_ref, src, vd);
-    PL_COUNT_LAUNCHES(6 + 1 + (PD + 1) + 1);   // build, index (4) and zero_rows; splat; blur passes; slice
+    PL_LAUNCH((slice_tiles_f64<PD>), tile_grid(g), TP, 0, st, g, output, hdr, tile_info, rec, rec_w, list_ref, src, vd);
+    PL_COUNT_LAUNCHES(4 + 1 + (PD + 1) + 1);   // build and index (3); splat; blur passes; slice
     PL_CUDA(cudaGetLastError());
     return PL_OK;
 }
@@ -485,8 +506,7 @@ static int run_export(const Geom& g, const R* positions, const R* reference, con
             pixel_vertex, pixel_weight);
     if (vertex_keys || vertex_item)
         export_vertices<PD><<<num_sms() * 4, 256, 0, st>>>(
-            hdr, reinterpret_cast<const Key<KW>*>(ws + L.list_keys),
-            reinterpret_cast<const u32*>(ws + L.vowner), max_vertices, vertex_keys, vertex_item);
+            hdr, reinterpret_cast<const Key<KW>*>(ws + L.vkeys), max_vertices, vertex_keys, vertex_item);
     PL_CUDA(cudaGetLastError());
     return PL_OK;
 }
@@ -511,7 +531,7 @@ static int filter_common(const Geom& g, float* output, const float* input, const
                          int phases = PH_BUILD | PH_APPLY) {
     if (mode != PL_MODE_ATOMIC && mode != PL_MODE_DETERMINISTIC) return PL_INVALID_ARGUMENT;
     Layout L;
-    int rc = make_layout(L, g, pd, vd, max_entries);
+    int rc = make_layout(L, g, pd, vd, max_entries, 4, mode == PL_MODE_DETERMINISTIC);
     if (rc != PL_OK) return rc;
     if (workspace_bytes < L.total) return PL_WORKSPACE_TOO_SMALL;
 #define CALL(P) run_filter<P>(g, output, input, positions, reference, vd, reverse, mode, workspace, L, st, phases)
@@ -564,8 +584,9 @@ const char* pl_strerror(int status) {
 const char* pl_last_cuda_error(void) { return g_cuda_error; }
 
 int pl_workspace_bytes(int batch, int n, int pd, int vd, int n_spatial_dims, const int* spatial_dims,
-                       int64_t max_entries, size_t* bytes) {
+                       int64_t max_entries, int mode, size_t* bytes) {
     if (!bytes || batch < 0 || n < 0 || batch > 65535) return PL_INVALID_ARGUMENT;
+    if (mode != PL_MODE_ATOMIC && mode != PL_MODE_DETERMINISTIC) return PL_INVALID_ARGUMENT;
     if (!pl_supported(pd, vd)) return PL_UNSUPPORTED_DIMS;
     Geom g;
     int rc;
@@ -581,7 +602,7 @@ int pl_workspace_bytes(int batch, int n, int pd, int vd, int n_spatial_dims, con
     }
     if (rc != PL_OK) return rc;
     Layout L;
-    rc = make_layout(L, g, pd, vd, max_entries);
+    rc = make_layout(L, g, pd, vd, max_entries, 4, mode == PL_MODE_DETERMINISTIC);
     if (rc != PL_OK) return rc;
     *bytes = L.total;
     return PL_OK;

@@ -225,8 +225,11 @@ struct SplatRows {
                                     sizeof(int) * TP;
 };
 
+#ifndef PL_SPLAT_ROWS_CTAS
+#define PL_SPLAT_ROWS_CTAS 1
+#endif
 template <int PD, int VD>
-__global__ void __launch_bounds__(Cfg<PD>::TP)
+__global__ void __launch_bounds__(Cfg<PD>::TP, PL_SPLAT_ROWS_CTAS)
 splat_tiles_rows(Geom g, const float* __restrict__ input, Header* hdr, const int2* __restrict__ tile_info,
                  const u16* __restrict__ rec, const float* __restrict__ rec_w,
                  const u32* __restrict__ list_ref, float* __restrict__ v0, int bulk_ok) {

@@ -22,7 +22,7 @@ class GraphedLatticeFilter:
         call = FilterCall(tuple(input_shape), None if reference_shape is None else tuple(reference_shape), bilateral,
                           theta_alpha, theta_beta, theta_gamma)
         with torch.cuda.device(device):
-            self._workspace = torch.empty(max(1, call.workspace_bytes()), dtype=torch.uint8, device=device)
+            self._workspace = torch.empty(max(1, call.workspace_bytes(mode=mode)), dtype=torch.uint8, device=device)
         # one ordinary call first: sets kernel attributes outside the capture
         side = torch.cuda.Stream(device)
         side.wait_stream(torch.cuda.current_stream(device))

@@ -3,10 +3,12 @@ batch chunks overlap on a few CUDA streams (both copy engines and the SMs busy a
 item is an independent lattice, so chunking the batch changes no result.
 
 The step is bound by the two copy directions (for the dense-CRF benchmark 0.8 GB in and 0.7 GB out
-against 2 ms of kernels), so the chunks are single items: the first result starts back to the host
-after one item has arrived, and only one item's result is still to be copied once the last input has
-landed.  Calls queued back to back (forward, then backward) share the streams, so the flow of copies
-does not stop at the call boundary."""
+against 2 ms of kernels; the link carries about 47 GB/s each way when both directions run).  What the
+pipeline can win or lose is the ramp: nothing flows back before the first chunk has arrived and been
+filtered, nothing flows in while the last chunk's result leaves.  So the first and last chunks of a call
+are single items and the ones between are larger (two items measured best: single items everywhere cost
+more in small launches than they save).  Calls queued back to back (forward, then backward) share the
+streams, so the flow of copies does not stop at the call boundary."""
 import torch
 
 from .lattice_filter import FilterCall, lattice_filter_raw
@@ -17,10 +19,12 @@ class HostPipeline:
     and writes a pinned host tensor of the input's shape; it returns when the result is complete.
     Every stream slot owns its device buffers and its workspace."""
 
-    def __init__(self, device=None, n_streams=4, chunk_items=1):
+    def __init__(self, device=None, n_streams=4, chunk_items=2, edge_chunks=2):
+        """chunk_items: items per chunk; edge_chunks: how many chunks at each end of a call are single items."""
         self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
         self.streams = [torch.cuda.Stream(self.device) for _ in range(max(1, n_streams))]
         self.chunk_items = max(1, chunk_items)
+        self.edge_chunks = max(0, edge_chunks)
         self._bufs = {}
         self._next_slot = 0
 
@@ -32,8 +36,8 @@ class HostPipeline:
             self._bufs[key] = t
         return t[:shape[0]]
 
-    def _workspace(self, slot, call):
-        need = call.workspace_bytes()
+    def _workspace(self, slot, call, mode):
+        need = call.workspace_bytes(mode=mode)
         ws = self._bufs.get((slot, "ws"))
         if ws is None or ws.numel() < need:
             ws = torch.empty(need, dtype=torch.uint8, device=self.device)
@@ -58,8 +62,7 @@ class HostPipeline:
         main = torch.cuda.current_stream(self.device)
         ready = torch.cuda.Event()
         ready.record(main)
-        for lo in range(0, batch, self.chunk_items):
-            hi = min(batch, lo + self.chunk_items)
+        for lo, hi in self.chunks(batch):
             slot = self._next_slot
             self._next_slot = (slot + 1) % len(self.streams)
             stream = self.streams[slot]
@@ -76,11 +79,19 @@ class HostPipeline:
                     call = FilterCall(tuple(dx.shape), None if dr is None else tuple(dr.shape), bilateral,
                                       theta_alpha, theta_beta, theta_gamma)
                     lattice_filter_raw(dx, dr, bilateral, theta_alpha, theta_beta, theta_gamma, reverse, mode,
-                                       out=do, workspace=self._workspace(slot, call))
+                                       out=do, workspace=self._workspace(slot, call, mode))
                 out_host[lo:hi].copy_(do, non_blocking=True)
         if wait:
             self.synchronize()
         return out_host
+
+    def chunks(self, batch):
+        """[lo, hi) of every chunk of a `batch`-item call, in order."""
+        head = min(self.edge_chunks, batch)
+        tail = min(self.edge_chunks, batch - head)
+        cuts = list(range(0, head)) + list(range(head, batch - tail, self.chunk_items)) + \
+            list(range(batch - tail, batch)) + [batch]
+        return [(cuts[i], cuts[i + 1]) for i in range(len(cuts) - 1)]
 
     def synchronize(self):
         for stream in self.streams:

@@ -73,11 +73,14 @@ class FilterCall:
         self.vd = self.c + 1
         self.theta = (float(theta_alpha), float(theta_beta), float(theta_gamma))
 
-    def workspace_bytes(self, max_entries=0, dtype=torch.float32):
+    def workspace_bytes(self, max_entries=0, dtype=torch.float32, mode="atomic"):
         nbytes = ctypes.c_size_t(0)
-        fn = capi.lib().pl_workspace_bytes_f64 if dtype == torch.float64 else capi.lib().pl_workspace_bytes
-        capi.check(fn(self.batch, self.n, self.pd, self.vd, len(self.sdims), capi.int_array(self.sdims),
-                      int(max_entries), ctypes.byref(nbytes)), "pl_workspace_bytes")
+        head = (self.batch, self.n, self.pd, self.vd, len(self.sdims), capi.int_array(self.sdims), int(max_entries))
+        if dtype == torch.float64:
+            rc = capi.lib().pl_workspace_bytes_f64(*head, ctypes.byref(nbytes))
+        else:
+            rc = capi.lib().pl_workspace_bytes(*head, capi.MODES[mode], ctypes.byref(nbytes))
+        capi.check(rc, "pl_workspace_bytes")
         return nbytes.value
 
 
@@ -105,7 +108,7 @@ def lattice_filter_raw(input_image, reference_image, bilateral=True, theta_alpha
         return out, None, call
     stream = _stream_handle(x.device)
     with torch.cuda.device(x.device):
-        nbytes = call.workspace_bytes(max_entries, x.dtype)
+        nbytes = call.workspace_bytes(max_entries, x.dtype, mode)
         ws = workspace if workspace is not None else _workspace(x.device, stream, nbytes)
         head = (out.data_ptr(), x.data_ptr(), 0 if ref is None else ref.data_ptr(), call.batch,
                 len(call.sdims), capi.int_array(call.sdims), call.c, call.r, int(call.bilateral),
@@ -150,9 +153,10 @@ class Lattice:
     own and only splats, blurs and slices per call."""
 
     def __init__(self, reference_image, spatial_shape=None, bilateral=True, theta_alpha=1.0, theta_beta=1.0,
-                 theta_gamma=1.0, max_channels=1, max_entries=0):
+                 theta_gamma=1.0, max_channels=1, max_entries=0, mode="atomic"):
         """reference_image [B, *S, R] (bilateral) — or None with spatial_shape = (B, *S) for a purely
-        spatial kernel.  max_channels: the widest input that will be applied."""
+        spatial kernel.  max_channels: the widest input that will be applied.  mode: "deterministic"
+        sizes the workspace for `apply(..., mode="deterministic")` too (it then serves both modes)."""
         _float32_only(reference_image, "Lattice (build once, apply many times)")
         if bilateral:
             _check_tensor(reference_image, "reference_image")
@@ -175,7 +179,8 @@ class Lattice:
         if call.batch == 0 or call.n == 0:
             return
         with torch.cuda.device(device):
-            self.workspace = torch.empty(call.workspace_bytes(self.max_entries), dtype=torch.uint8, device=device)
+            self.workspace = torch.empty(call.workspace_bytes(self.max_entries, mode=mode), dtype=torch.uint8,
+                                         device=device)
             capi.check(capi.lib().pl_lattice_build_f32(
                 0 if ref is None else ref.data_ptr(), call.batch, len(call.sdims), capi.int_array(call.sdims),
                 call.r, int(call.bilateral), call.theta[0], call.theta[1], call.theta[2], call.vd,
@@ -218,7 +223,7 @@ class _LatticeFilterReuseFunction(torch.autograd.Function):
     def forward(ctx, input_image, reference_image, bilateral, theta_alpha, theta_beta, theta_gamma, reverse,
                 mode):
         lattice = Lattice(reference_image, tuple(input_image.shape[:-1]), bilateral, theta_alpha, theta_beta,
-                          theta_gamma, max_channels=input_image.shape[-1])
+                          theta_gamma, max_channels=input_image.shape[-1], mode=mode)
         ctx.lattice, ctx.mode = lattice, mode
         ctx.save_for_backward(reference_image)   # autograd's version check guards against in-place edits
         return lattice.apply(input_image, reverse, mode)
@@ -319,9 +324,12 @@ def filter_positions(input_values, positions, reverse=False, mode="atomic", max_
         stream = _stream_handle(x.device)
         with torch.cuda.device(x.device):
             nbytes = ctypes.c_size_t(0)
-            size_fn = capi.lib().pl_workspace_bytes_f64 if f64 else capi.lib().pl_workspace_bytes
-            capi.check(size_fn(batch, n, pd, vd, 0, None, int(max_entries), ctypes.byref(nbytes)),
-                       "pl_workspace_bytes")
+            if f64:
+                rc = capi.lib().pl_workspace_bytes_f64(batch, n, pd, vd, 0, None, int(max_entries), ctypes.byref(nbytes))
+            else:
+                rc = capi.lib().pl_workspace_bytes(batch, n, pd, vd, 0, None, int(max_entries), capi.MODES[mode],
+                                                   ctypes.byref(nbytes))
+            capi.check(rc, "pl_workspace_bytes")
             ws = workspace if workspace is not None else _workspace(x.device, stream, nbytes.value)
             head = (out.data_ptr(), x.data_ptr(), p.data_ptr(), batch, n, pd, vd, int(bool(reverse)),
                     ws.data_ptr(), ws.numel(), int(max_entries))

@@ -54,16 +54,16 @@ def test_workspace_bytes_and_argument_checks(capi):
     lib = capi.lib()
     b = ctypes.c_size_t(0)
     sd = capi.int_array([512, 512])
-    assert lib.pl_workspace_bytes(16, 512 * 512, 5, 22, 2, sd, 0, ctypes.byref(b)) == capi.PL_OK
+    assert lib.pl_workspace_bytes(16, 512 * 512, 5, 22, 2, sd, 0, 0, ctypes.byref(b)) == capi.PL_OK
     worst = b.value
-    assert lib.pl_workspace_bytes(16, 512 * 512, 5, 22, 2, sd, 4_000_000, ctypes.byref(b)) == capi.PL_OK
+    assert lib.pl_workspace_bytes(16, 512 * 512, 5, 22, 2, sd, 4_000_000, 0, ctypes.byref(b)) == capi.PL_OK
     assert 0 < b.value < worst
-    assert lib.pl_workspace_bytes(1, 512 * 512, 5, 22, 2, capi.int_array([512, 500]), 0,
+    assert lib.pl_workspace_bytes(1, 512 * 512, 5, 22, 2, capi.int_array([512, 500]), 0, 0,
                                   ctypes.byref(b)) == capi.PL_INVALID_ARGUMENT
-    assert lib.pl_workspace_bytes(1, 100, 11, 4, 0, None, 0, ctypes.byref(b)) == capi.PL_UNSUPPORTED_DIMS
-    assert lib.pl_workspace_bytes(1, 100, 5, 4, 0, None, 0, None) == capi.PL_INVALID_ARGUMENT
+    assert lib.pl_workspace_bytes(1, 100, 11, 4, 0, None, 0, 0, ctypes.byref(b)) == capi.PL_UNSUPPORTED_DIMS
+    assert lib.pl_workspace_bytes(1, 100, 5, 4, 0, None, 0, 0, None) == capi.PL_INVALID_ARGUMENT
     # more than 2^31 splats cannot be indexed
-    assert lib.pl_workspace_bytes(65535, 1 << 20, 5, 4, 0, None, 0, ctypes.byref(b)) == capi.PL_INVALID_ARGUMENT
+    assert lib.pl_workspace_bytes(65535, 1 << 20, 5, 4, 0, None, 0, 0, ctypes.byref(b)) == capi.PL_INVALID_ARGUMENT
 
 
 def test_null_pointers_are_rejected_before_any_launch(capi):

@@ -289,7 +289,7 @@ def test_lattice_built_once_applied_many_times(gpu, oracle):
     rng = np.random.default_rng(41)
     ref_n = rng.random((2, 30, 26, 3), dtype=np.float32)
     ref = torch.from_numpy(ref_n).cuda()
-    lat = plb.Lattice(ref, bilateral=True, theta_alpha=5.0, theta_beta=0.2, max_channels=6)
+    lat = plb.Lattice(ref, bilateral=True, theta_alpha=5.0, theta_beta=0.2, max_channels=6, mode="deterministic")
     for c, reverse in ((6, False), (2, True), (6, True), (1, False)):
         x_n = rng.standard_normal((2, 30, 26, c)).astype(np.float32)
         got = lat.apply(torch.from_numpy(x_n).cuda(), reverse=reverse).cpu().numpy()
@@ -300,6 +300,11 @@ def test_lattice_built_once_applied_many_times(gpu, oracle):
     a = lat.apply(x, mode="deterministic").cpu().numpy()
     b = plb.lattice_filter(x, ref, True, 5.0, 0.2, mode="deterministic").cpu().numpy()
     assert np.array_equal(bits(a), bits(b))
+    # a workspace sized for the atomic mode has no room for the fixed-point sums: refused before any launch
+    small = plb.Lattice(ref, bilateral=True, theta_alpha=5.0, theta_beta=0.2, max_channels=6)
+    with pytest.raises(plb.PlError) as err:
+        small.apply(x, mode="deterministic")
+    assert err.value.status == 3   # PL_WORKSPACE_TOO_SMALL
 
 
 def test_autograd_with_lattice_reuse(gpu, oracle):

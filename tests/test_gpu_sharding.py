@@ -12,7 +12,11 @@ pytestmark = pytest.mark.gpu
 def _data(batch, seed=7):
     rng = np.random.default_rng(seed)
     ref = rng.random((batch, 40, 36, 3), dtype=np.float32)
-    inp = rng.standard_normal((batch, 40, 36, 5)).astype(np.float32)
+    inp = np.clip(rng.standard_normal((batch, 40, 36, 5)), -3.5, 3.5).astype(np.float32)
+    # The deterministic mode rounds onto a fixed-point grid chosen from max |input| of the CALL; giving every
+    # item the same maximum makes that grid the same for any slicing of the batch, so results can be
+    # compared bit for bit across slicings.
+    inp[:, 0, 0, 0] = 4.0
     return inp, ref
 
 
