@@ -52,10 +52,22 @@ def parse_args():
     ap.add_argument("--min-ms", type=float, default=500.0,
                     help="the timed blocks of --steps steps are repeated until they fill this much device time")
     ap.add_argument("--no-weak", action="store_true", help="skip the extra weak-scaling measurement at N > 1")
+    ap.add_argument("--channels", type=int, default=0,
+                    help="override the channel count of configuration 2 / 5 (value widths without a register-resident "
+                         "instantiation run the generic splat / slice kernels)")
+    ap.add_argument("--headline-only", action="store_true",
+                    help="only the device-resident measurement (no end-to-end, gather, reuse, graph or weak-scaling "
+                         "legs): short runs for profiler captures")
+    ap.add_argument("--mode", default="atomic", choices=["atomic", "deterministic"],
+                    help="accumulation mode of the splat stage (the headline is atomic)")
+    ap.add_argument("--dtype", default="f32", choices=["f32", "f64"],
+                    help="number type of the call (the headline is f32; f64 is the reference's other registered type)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-threads", type=int, default=0)
     ap.add_argument("--batch", type=int, default=0,
                     help="override the batch size of the configuration (profiling of smaller cases)")
+    ap.add_argument("--size", type=int, default=0,
+                    help="override the side length of the configuration's images or volumes (smaller cases)")
     return ap.parse_args()
 
 
@@ -65,9 +77,16 @@ def metric_name(cfg, w):
     return "Mpixels/s %s (pd=%d, vd=%d)" % ("fwd+bwd" if w.backward else "fwd", w.pd, w.vd)
 
 
-def make_workload(cfg, rank, batch=0):
+def make_workload(cfg, rank, batch=0, size=0, channels=0):
     from permutohedral_lattice_b200 import workloads
-    w = workloads.CONFIGS[cfg](batch=batch) if batch and cfg >= 2 else workloads.CONFIGS[cfg]()
+    kw = {}
+    if batch and cfg >= 2:
+        kw["batch"] = batch
+    if size:
+        kw["size"] = size
+    if channels and cfg in (2, 5):
+        kw["channels"] = channels
+    w = workloads.CONFIGS[cfg](**kw)
     if rank:   # another rank's batch: same distributions, other content
         rng = np.random.default_rng(1000 + rank)
         perm = rng.permutation(w.batch)
@@ -242,7 +261,7 @@ def run_reference(args, rank, world):
     """--impl reference: the reference's own CPU implementation of the path on the host cores."""
     if rank != 0:
         return
-    w = make_workload(args.config, 0, args.batch)
+    w = make_workload(args.config, 0, args.batch, args.size, args.channels)
     threads = host_threads(args.cpu_threads, w.batch)
     times = []
     info = None
@@ -273,15 +292,16 @@ class Arm:
     """One arm of the measurement: a set of device-resident tensors (a rank's slice of the batch, or a whole
     batch) and the forward (+ backward) step over them."""
 
-    def __init__(self, plb, capi, w, lo, hi, dev):
+    def __init__(self, plb, capi, w, lo, hi, dev, mode="atomic", dtype="f32"):
         import torch
-        self.plb, self.capi, self.w = plb, capi, w
+        self.plb, self.capi, self.w, self.mode = plb, capi, w, mode
         self.b, self.n, self.c = hi - lo, w.pixels_per_item, w.vd - 1
         self.use_positions = w.positions is not None
-        self.x = torch.from_numpy(w.input[lo:hi]).to(dev)
-        self.ref = None if w.reference is None else torch.from_numpy(w.reference[lo:hi]).to(dev)
-        self.pos = None if not self.use_positions else torch.from_numpy(w.positions[lo:hi]).to(dev)
-        self.grad = None if w.grad is None else torch.from_numpy(w.grad[lo:hi]).to(dev)
+        tt = torch.float64 if dtype == "f64" else torch.float32
+        self.x = torch.from_numpy(w.input[lo:hi]).to(dev, tt)
+        self.ref = None if w.reference is None else torch.from_numpy(w.reference[lo:hi]).to(dev, tt)
+        self.pos = None if not self.use_positions else torch.from_numpy(w.positions[lo:hi]).to(dev, tt)
+        self.grad = None if w.grad is None else torch.from_numpy(w.grad[lo:hi]).to(dev, tt)
         self.out_f = torch.empty_like(self.x)
         self.out_b = torch.empty_like(self.x)
         self.ws = None
@@ -295,10 +315,10 @@ class Arm:
             self.capi.lib().pl_profile_next_call(arr)
         if self.use_positions:
             _, self.ws = self.plb.filter_positions(inp.view(self.b, self.n, self.c), self.pos, reverse=reverse,
-                                                   out=out.view(self.b, self.n, self.c))
+                                                   mode=self.mode, out=out.view(self.b, self.n, self.c))
         else:
             _, self.ws, _ = self.plb.lattice_filter_raw(inp, self.ref, w.bilateral, w.theta_alpha, w.theta_beta,
-                                                        w.theta_gamma, reverse, out=out)
+                                                        w.theta_gamma, reverse, mode=self.mode, out=out)
 
     def step(self, events_f=None, events_b=None):
         self.call(self.x, self.out_f, False, events_f)
@@ -366,11 +386,13 @@ def main():
     # ---- the workload and this rank's share of it -------------------------------------------------
     # The same seeded batch on every rank; a batch of several items is SHARDED over the ranks (strong
     # scaling: total work fixed), a single-item configuration is replicated (every rank filters it).
-    full = make_workload(args.config, 0, args.batch)
+    full = make_workload(args.config, 0, args.batch, args.size, args.channels)
     B, n, c = full.batch, full.pixels_per_item, full.vd - 1
     sharded = B >= 2
     lo, hi = shard_range(B, world, rank) if sharded else (0, B)
-    arm = Arm(plb, capi, full, lo, hi, dev)
+    arm = Arm(plb, capi, full, lo, hi, dev, args.mode, args.dtype)
+    real_bytes = 8 if args.dtype == "f64" else 4
+    extras = not args.headline_only and args.dtype == "f32" and args.mode == "atomic"
     calls_per_step = 2 if full.backward else 1
     total_pixels = B * n * (1 if sharded else world)
 
@@ -404,8 +426,9 @@ def main():
     sampler.start()
     launches0 = capi.lib().pl_launch_count()
     sampler.mark_begin()
+    staged = args.dtype == "f32"    # the stage-event hook belongs to the float calls
     block_ms = timed_blocks(lambda k: arm.step(), args.steps, args.min_ms,
-                            lambda k: arm.step(ev[k][0], ev[k][1] if full.backward else None))
+                            (lambda k: arm.step(ev[k][0], ev[k][1] if full.backward else None)) if staged else None)
     sampler.mark_end()
     launches = capi.lib().pl_launch_count() - launches0
     clocks = sampler.stop()
@@ -415,7 +438,7 @@ def main():
     # per-stage times of a call, averaged over the calls of the last block (this rank's slice)
     stage_ms = {name: 0.0 for name in capi.STAGE_NAMES}
     ncalls = 0
-    if arm.b:
+    if arm.b and staged:
         for s_ in ev:
             for call in s_:
                 for i, name in enumerate(capi.STAGE_NAMES):
@@ -427,24 +450,31 @@ def main():
     hbm_gbs, peak_kind = peaks()
     frac_of_batch = (arm.b / B) if sharded else 1.0
     stage_bytes, call_bytes, io_bytes = algorithmic_bytes(full, num_vertices // (1 if sharded else world))
-    stage_bytes = {k: v * frac_of_batch for k, v in stage_bytes.items()}
-    call_bytes *= frac_of_batch
-    io_bytes *= frac_of_batch
+    scale_b = frac_of_batch * real_bytes / 4
+    stage_bytes = {k: v * scale_b for k, v in stage_bytes.items()}
+    call_bytes *= scale_b
+    io_bytes *= scale_b
     kernel_ms = dict(stage_ms)
     kernel_ms["blur"] = stage_ms["blur"] / (full.pd + 1)          # one blur_axis launch
     kernel_bytes = dict(stage_bytes)
     kernel_bytes["blur"] = stage_bytes["blur"] / (full.pd + 1)
     kernel_names = {"build": "build_tiles", "splat": "splat_tiles", "blur": "blur_axis",
                     "slice": "slice_tiles"}
-    dominant = max(kernel_names, key=lambda k: stage_ms[k])
-    achieved = kernel_bytes[dominant] / max(kernel_ms[dominant] * 1e-3, 1e-12) / 1e9
-    traffic, traffic_source = measured_traffic(full.name, kernel_names[dominant], arm.b * n)
-    roofline = {"bound": "hbm", "kernel": kernel_names[dominant], "achieved": achieved,
-                "peak": hbm_gbs, "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / hbm_gbs,
-                "traffic": traffic, "traffic_source": traffic_source,
-                "algorithmic_bytes_per_launch": kernel_bytes[dominant],
-                "ms_per_launch": kernel_ms[dominant]}
     call_ms = ms_per_step / calls_per_step
+    if staged:
+        dominant = max(kernel_names, key=lambda k: stage_ms[k])
+        achieved = kernel_bytes[dominant] / max(kernel_ms[dominant] * 1e-3, 1e-12) / 1e9
+        traffic, traffic_source = measured_traffic(full.name, kernel_names[dominant], arm.b * n)
+        roofline = {"bound": "hbm", "kernel": kernel_names[dominant], "achieved": achieved,
+                    "peak": hbm_gbs, "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / hbm_gbs,
+                    "traffic": traffic, "traffic_source": traffic_source,
+                    "algorithmic_bytes_per_launch": kernel_bytes[dominant],
+                    "ms_per_launch": kernel_ms[dominant]}
+    else:   # no per-stage events: the whole call stands for the kernel
+        achieved = call_bytes / (call_ms * 1e-3) / 1e9
+        roofline = {"bound": "hbm", "kernel": "whole call", "achieved": achieved, "peak": hbm_gbs,
+                    "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / hbm_gbs, "traffic": None,
+                    "algorithmic_bytes_per_launch": call_bytes, "ms_per_launch": call_ms}
     call_gbs = call_bytes / (call_ms * 1e-3) / 1e9
     roofline_call = {"algorithmic_bytes_per_call": call_bytes, "io_floor_bytes_per_call": io_bytes,
                      "achieved": call_gbs, "peak": hbm_gbs, "unit": "GB/s", "frac": call_gbs / hbm_gbs,
@@ -452,7 +482,7 @@ def main():
 
     # ---- the same step with the ranks' output slices gathered on rank 0 (NCCL over NVLink) ---------
     gather = None
-    if world > 1 and sharded:
+    if world > 1 and sharded and extras:
         comm = torch.cuda.Stream(dev)
         item_shape = tuple(arm.x.shape[1:])
         gather_f = OutputGather(B, item_shape, arm.x.dtype, dev, dst=0)
@@ -533,15 +563,27 @@ def main():
         (ms, wall) = max_over_ranks([e0.elapsed_time(e1), wall])
         return ms / steps, wall / steps
 
-    e2e_ms, e2e_wall_ms = timed_host_steps(e2e_step, args.e2e_steps)
-    copy_ms, _ = timed_host_steps(lambda: e2e_step(copy_only=True), args.e2e_steps)
-    e2e_value = total_pixels / (e2e_ms * 1e-3) / 1e6
+    e2e_reuse = None
+    if extras and full.backward and not arm.use_positions and arm.b:
+        def e2e_reuse_step():
+            pipe.filter_forward_backward(hx, hgrad, href, full.bilateral, full.theta_alpha, full.theta_beta,
+                                         full.theta_gamma, out_host=hout_f, grad_out_host=hout_b, wait=True)
+        r_ms, _ = timed_host_steps(e2e_reuse_step, args.e2e_steps)
+        e2e_reuse = {"value": total_pixels / (r_ms * 1e-3) / 1e6, "unit": "Mpixels/s", "ms_per_step": r_ms,
+                     "note": "forward + backward through HostPipeline.filter_forward_backward: the reference image "
+                             "is sent once and one lattice serves both directions; not the headline metric"}
+    if extras:
+        e2e_ms, e2e_wall_ms = timed_host_steps(e2e_step, args.e2e_steps)
+        copy_ms, _ = timed_host_steps(lambda: e2e_step(copy_only=True), args.e2e_steps)
+        e2e_value = total_pixels / (e2e_ms * 1e-3) / 1e6
+    else:
+        e2e_ms = e2e_wall_ms = copy_ms = e2e_value = None
 
     # not the headline: the same step with the lattice built once and reused by the backward call
     # (pl_lattice_build_f32 + 2 x pl_lattice_apply_f32), as a training step through
     # lattice_filter(..., reuse_lattice=True) does
     reuse = None
-    if not arm.use_positions and full.backward and arm.b:
+    if not arm.use_positions and full.backward and arm.b and extras:
         w = full
 
         def reuse_step(k):
@@ -557,7 +599,7 @@ def main():
 
     # also not the headline: the same stateless step replayed from CUDA graphs (one launch per call)
     graph = None
-    if not arm.use_positions and arm.b:
+    if not arm.use_positions and arm.b and extras:
         w = full
         rshape = None if arm.ref is None else arm.ref.shape
         gf = plb.GraphedLatticeFilter(arm.x.shape, rshape, w.bilateral, w.theta_alpha, w.theta_beta, w.theta_gamma,
@@ -585,10 +627,10 @@ def main():
 
     # weak scaling beside the strong-scaling headline: every rank filters a whole batch of its own
     weak = None
-    if world > 1 and sharded and not args.no_weak:
+    if world > 1 and sharded and not args.no_weak and extras:
         del arm
         torch.cuda.empty_cache()
-        own = Arm(plb, capi, make_workload(args.config, rank, args.batch), 0, B, dev)
+        own = Arm(plb, capi, make_workload(args.config, rank, args.batch, args.size, args.channels), 0, B, dev)
         for _ in range(3):
             own.step()
         weak_ms = statistics.median(timed_blocks(lambda k: own.step(), args.steps, min(args.min_ms, 250.0))) \
@@ -600,13 +642,14 @@ def main():
     line = {
         "metric": metric_name(args.config, full), "value": value, "unit": "Mpixels/s", "n_gpus": world,
         "steps": args.steps, "warmup": warm, "ms_per_step": ms_per_step,
-        "higher_is_better": True, "scaling": "strong" if sharded else "weak", "vs_baseline": None, "dtype": "f32",
+        "higher_is_better": True, "scaling": "strong" if sharded else "weak", "vs_baseline": None,
+        "dtype": args.dtype,
         "data": "synthetic",
         "config": config_of(full, world),
         "details": {"parallelism": ("one batch of %d items sharded over %d GPU(s), no collective in the data path"
                                     % (B, world)) if sharded else "replicas only (single item), x%d" % world,
-                    "mode": "atomic", "bytes_read_per_call_on_this_rank": (hx.numel() + (
-                        href.numel() if href is not None else 0)) * 4,
+                    "mode": args.mode, "bytes_read_per_call_on_this_rank": (hx.numel() + (
+                        href.numel() if href is not None else 0)) * real_bytes,
                     "num_vertices": num_vertices, "num_entries": num_entries,
                     "timing": "median of %d blocks of %d steps, each block bracketed by barrier + synchronize, "
                               "max over ranks per block" % (len(block_ms), args.steps)},
@@ -623,6 +666,7 @@ def main():
         "launches_per_call": int(launches) // max(1, len(block_ms) * args.steps * calls_per_step),
         "roofline": roofline, "roofline_call": roofline_call,
         "stages_ms": stage_ms,
+        "e2e_lattice_reuse": e2e_reuse,
         "gather": gather,
         "weak_scaling": weak,
         "lattice_reuse": reuse,

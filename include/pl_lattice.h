@@ -43,6 +43,8 @@ typedef struct pl_stats {
                               dense index's slot count rounded up to a power of two) */
     int32_t device_status; /* pl_status recorded by the kernels (PL_OK, PL_CAPACITY_EXCEEDED, ...) */
     int32_t direct_index;  /* 1: vertices were located by direct indexing (spatial-only call), 0: hash table */
+    int64_t max_entries;   /* the entry bound the workspace was laid out for (the worst case if the call passed 0):
+                              what pl_export_lattice and pl_lattice_apply_f32 must be given again */
 } pl_stats;
 
 /* 1 if position dimension pd and value dimension vd (= input channels + 1) can be filtered.
@@ -212,6 +214,14 @@ unsigned long long pl_launch_count(void);
  * off (enable == 0) or back on, for A/B timing and tests; it returns the previous setting.  The
  * reference hashes always (src/PermutohedralLatticeGPU.cuh:76-143). */
 int pl_debug_direct_index(int enable);
+
+/* min_entries <- the smallest max_entries whose workspace lets a spatial-only call on this grid locate its
+ * vertices by direct indexing (the dense index lives in the table region, whose size follows max_entries), or
+ * 0 when the grid cannot be indexed directly at all.  For callers that pass a max_entries of their own: a
+ * smaller bound still works, the call then hashes.  The reference hashes always
+ * (src/PermutohedralLatticeGPU.cuh:76-143). */
+int pl_direct_index_min_entries(int batch, int n_spatial_dims, const int* spatial_dims, float theta_gamma,
+                                int64_t* min_entries);
 
 /* Copies the counters of the last call that used `workspace` to the host.  SYNCHRONISES `stream`.
  * workspace == NULL reads the counters of the last pl_lattice_filter_f32_noalloc call on the current

@@ -9,7 +9,8 @@ Flags follow the parity-critical ones of the reference CPU build: -O2, no FMA co
 (-ffp-contract=off), no -ffast-math, no -march=native.
 
 Run:  python oracle/build.py [--force]
-The reference tree is searched in $PL_REFERENCE_DIR, then in DEFAULT_REFERENCE_DIR.
+The reference tree (a checkout of MiguelMonteiro/permutohedral_lattice) is searched in $PL_REFERENCE_DIR,
+then in a directory named "reference" beside this repository.
 """
 import os
 import subprocess
@@ -19,11 +20,11 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 ORACLE_SO = os.path.join(HERE, "libpl_oracle.so")
 REF_DIR_OUT = os.path.join(HERE, "_ref")
 REF_SO = os.path.join(REF_DIR_OUT, "libpl_ref.so")
-DEFAULT_REFERENCE_DIR = "/root/reference"
+SIBLING_REFERENCE_DIR = os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
 
 
 def reference_root():
-    for cand in (os.environ.get("PL_REFERENCE_DIR"), DEFAULT_REFERENCE_DIR):
+    for cand in (os.environ.get("PL_REFERENCE_DIR"), SIBLING_REFERENCE_DIR):
         if cand and os.path.isfile(os.path.join(cand, "src", "PermutohedralLatticeCPU.h")):
             return cand
     return None

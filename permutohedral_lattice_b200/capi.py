@@ -27,6 +27,7 @@ EXPORTED_SYMBOLS = [
     "pl_lattice_build_f32", "pl_lattice_build_positions_f32", "pl_lattice_apply_f32",
     "pl_workspace_bytes_f64", "pl_compute_positions_f64", "pl_filter_f64", "pl_lattice_filter_f64",
     "pl_export_lattice_f64", "pl_debug_direct_index", "pl_crf_update_f32", "pl_launch_count",
+    "pl_direct_index_min_entries",
 ]
 STATIC_SCRATCH_BYTES = 64 << 20
 NUM_STAGE_EVENTS = 6
@@ -36,7 +37,7 @@ STAGE_NAMES = ["build", "index", "splat", "blur", "slice"]
 class PlStats(ctypes.Structure):
     _fields_ = [("num_vertices", ctypes.c_int64), ("num_entries", ctypes.c_int64),
                 ("table_slots", ctypes.c_int64), ("device_status", ctypes.c_int32),
-                ("direct_index", ctypes.c_int32)]
+                ("direct_index", ctypes.c_int32), ("max_entries", ctypes.c_int64)]
 
 
 class PlError(RuntimeError):
@@ -86,6 +87,7 @@ def lib():
         L.pl_export_lattice_f64.argtypes = [vp, vp, vp, i, i, i, i, i, ip, i, d, d, i64, i64, vp, vp, vp,
                                             vp, vp]
         L.pl_debug_direct_index.argtypes = [i]
+        L.pl_direct_index_min_entries.argtypes = [i, i, ip, f, ctypes.POINTER(ctypes.c_int64)]
         L.pl_crf_update_f32.argtypes = [vp, vp, vp, vp, vp, f, f, i64, i, vp]
         L.pl_profile_next_call.argtypes = [ctypes.POINTER(ctypes.c_void_p)]
         L.pl_launch_count.argtypes = []

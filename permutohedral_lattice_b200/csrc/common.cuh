@@ -45,7 +45,8 @@ struct Header {   // first 256 bytes of the workspace
     u32 table_log2;
     u32 absmax_bits;   // deterministic mode: bit pattern of max |input| (non-negative floats order as integers)
     u32 direct;        // 1: vertices were found by direct indexing (spatial-only call), 0: through the hash table
-    u32 pad[58];
+    u32 capacity;      // the max_entries the workspace was laid out for (written by build_tiles)
+    u32 pad[57];
 };
 
 struct Layout {   // byte offsets into the workspace

@@ -35,6 +35,7 @@ build_tiles(Geom g, const R* __restrict__ positions, const R* __restrict__ refer
     const int tid = threadIdx.x, tile = tpos.tile;
     for (int i = tid; i < LS; i += TP) hslots[i] = -1;
     if (tid <= PD) cnt_s[tid] = 0;
+    if (tile == 0 && tid == 0) hdr->capacity = max_entries;
 
     int item, pix, po, py, px;
     const bool valid = tile_point(g, tpos, tid, item, pix, po, py, px);
@@ -401,7 +402,8 @@ link_neighbours(const Header* hdr, const u64* __restrict__ table,
     const u64 items = (u64)M * (PD + 1);
     for (u64 e = (u64)blockIdx.x * blockDim.x + threadIdx.x; e < items; e += (u64)gridDim.x * blockDim.x) {
         // axis-major: neighbouring threads take neighbouring vertices of one axis, so their key loads and
-        // their own slots of the neighbour table are contiguous
+        // their own slots of the neighbour table are contiguous (vertex-major, where the threads of a vertex
+        // share one key load, measured slower at pd = 5 and at pd = 16)
         const int a = (int)(e / M);
         const u32 v = (u32)(e - (u64)a * M);
         const Key<KW> k = vkeys[v];

@@ -960,6 +960,20 @@ int pl_crf_update_f32(float* q_out, const float* unaries, const float* q_bilater
 
 unsigned long long pl_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
+int pl_direct_index_min_entries(int batch, int n_spatial_dims, const int* spatial_dims, float theta_gamma,
+                                int64_t* min_entries) {
+    if (!min_entries || !spatial_dims || batch < 0 || n_spatial_dims < 1) return PL_INVALID_ARGUMENT;
+    *min_entries = 0;
+    if (n_spatial_dims > MAX_SDIMS || !pd_supported(n_spatial_dims) || batch == 0) return PL_OK;
+    float scale[MAX_PD];
+    scale_factors(n_spatial_dims, scale);
+    Direct d;
+    if (!direct_bounds(d, n_spatial_dims, spatial_dims, theta_gamma, scale, batch, ~0ull)) return PL_OK;
+    // the index uses the hash table's region as 32-bit slots: 2 * table slots, table slots >= 2 * max_entries
+    *min_entries = (int64_t)((d.slots + 3) / 4);
+    return PL_OK;
+}
+
 int pl_debug_direct_index(int enable) {
     const int was = g_direct_index_enabled;
     g_direct_index_enabled = enable ? 1 : 0;
@@ -989,6 +1003,7 @@ int pl_lattice_stats(const void* workspace, pl_stats* stats, void* stream) {
     for (int code = PL_INVALID_ARGUMENT; code <= PL_INTERNAL_ERROR; code++)
         if (h.status & (1u << code)) stats->device_status = code;
     stats->direct_index = (int32_t)h.direct;
+    stats->max_entries = (int64_t)h.capacity;
     return PL_OK;
 }
 

@@ -50,7 +50,7 @@ def run_op(inp, ref, bilateral, ta, tb, tg, reverse, **kw):
     return out, ws, call, x, r
 
 
-def export_op(ws, call, r, max_entries=0):
+def export_op(ws, call, r, max_entries=None):
     st = plb.lattice_stats(ws)
     assert st.device_status == 0, "device status %d" % st.device_status
     return st, plb.export_lattice(ws, st, call.batch, call.n, call.pd, call.vd, reference=r,

@@ -103,3 +103,21 @@ def test_crf_update_rejects_bad_arguments():
     assert L.pl_crf_update_f32(0, t.data_ptr(), t.data_ptr(), t.data_ptr(), 0, 1.0, 1.0, 4, 3, s) \
         == capi.PL_INVALID_ARGUMENT
     assert L.pl_crf_update_f32(0, 0, 0, 0, 0, 1.0, 1.0, 0, 3, s) == capi.PL_OK      # nothing to do
+
+
+def test_host_pipeline_forward_backward_through_one_lattice(oracle):
+    """HostPipeline.filter_forward_backward: reference sent once, one lattice per chunk, against the CPU oracle's
+    forward and reverse calls."""
+    import torch
+    import permutohedral_lattice_b200 as plb
+    import gpu_helpers
+    rng = np.random.default_rng(77)
+    ref = rng.random((5, 28, 30, 3), dtype=np.float32)
+    x = rng.standard_normal((5, 28, 30, 4)).astype(np.float32)
+    g = rng.standard_normal((5, 28, 30, 4)).astype(np.float32)
+    pipe = plb.HostPipeline(torch.device("cuda", 0), n_streams=3, chunk_items=2, edge_chunks=1)
+    hx, hg, hr = (torch.from_numpy(a).pin_memory() for a in (x, g, ref))
+    for _ in range(2):      # twice: the second pass reuses the slots' buffers
+        out, gout = pipe.filter_forward_backward(hx, hg, hr, True, 5.0, 0.2)
+        gpu_helpers.assert_outputs_close(out.numpy(), oracle.lattice_filter(x, ref, True, 5.0, 0.2, 1.0, False), "fwd")
+        gpu_helpers.assert_outputs_close(gout.numpy(), oracle.lattice_filter(g, ref, True, 5.0, 0.2, 1.0, True), "bwd")

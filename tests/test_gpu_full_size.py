@@ -38,8 +38,6 @@ def test_config2_full_batch_forward_and_backward_against_oracle(gpu, oracle, crf
     st = plb.lattice_stats(ws)
     assert st.device_status == 0
     gpu.assert_outputs_close(out_f.cpu().numpy(), want_f, "c2 forward")
-    out_b = plb.lattice_filter(g, ref, True, w.theta_alpha, w.theta_beta, 1.0, reverse=True)
-    gpu.assert_outputs_close(out_b.cpu().numpy(), want_b, "c2 backward")
     # vertex count of the whole batch = sum of the per-item counts of the oracle (checked on two items
     # in full, structure included, and on the total through the reference's own count for the rest)
     items = [oracle.lattice_filter(w.input[i:i + 1], w.reference[i:i + 1], True, w.theta_alpha, w.theta_beta,
@@ -54,6 +52,9 @@ def test_config2_full_batch_forward_and_backward_against_oracle(gpu, oracle, crf
         assert len(mine) == o.num_vertices
         assert np.array_equal(sorted_rows(mine), sorted_rows(o.keys))
         assert np.array_equal(vk[pv[i]], o.pixel_keys())
+    # (the backward call comes last: it reuses the stream's workspace, which the export above still needed)
+    out_b = plb.lattice_filter(g, ref, True, w.theta_alpha, w.theta_beta, 1.0, reverse=True)
+    gpu.assert_outputs_close(out_b.cpu().numpy(), want_b, "c2 backward")
 
 
 def test_config2_properties_at_full_size(gpu, crf16):
