@@ -154,10 +154,15 @@ def _run_sized(kind, identity, batch, worst, device, stream, launch, verify="aut
     if known is not None and known[0] == identity:
         return launch(known[1]), known[1]          # the same lattice as a call that fitted this bound
     max_entries = _guess_bound(kind, batch, worst, floor)
+    repeated = False
     while True:
         ws = launch(max_entries)
         if max_entries == 0:                       # the worst case cannot overflow: nothing to verify
+            if repeated:                           # (but what the lattice needed is worth knowing for the next call)
+                st = lattice_stats(ws, stream)
+                _entries_per_item[kind] = max(_entries_per_item.get(kind, 0.0), st.num_entries / max(batch, 1))
             break
+        repeated = True
         st = lattice_stats(ws, stream)
         if st.device_status == capi.PL_CAPACITY_EXCEEDED:
             grown = max_entries * FIRST_GUESS_DIVISOR

@@ -140,3 +140,15 @@ def test_host_pipeline_repeats_chunks_that_did_not_fit(policy):
     got = out.numpy()
     assert np.isfinite(got).all()
     assert np.abs(got - want).max() <= 1e-4
+
+
+def test_host_pipeline_gives_back_its_workspaces_when_closed(policy):
+    import torch
+    import permutohedral_lattice_b200 as plb
+    x, ref = _data(6, batch=3)
+    pipe = plb.HostPipeline(torch.device("cuda", 0), n_streams=2)
+    pipe.filter(x.cpu().pin_memory(), ref.cpu().pin_memory(), **KW)
+    mine = [k for k in policy._workspaces if isinstance(k[1], tuple) and k[1][:2] == ("HostPipeline", id(pipe))]
+    assert mine                                   # one workspace per stream slot that was used
+    pipe.close()
+    assert not [k for k in policy._workspaces if isinstance(k[1], tuple) and k[1][:2] == ("HostPipeline", id(pipe))]
