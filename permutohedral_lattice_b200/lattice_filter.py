@@ -328,9 +328,9 @@ class Lattice:
         """reference_image [B, *S, R] (bilateral) — or None with spatial_shape = (B, *S) for a purely
         spatial kernel.  max_channels: the widest input that will be applied.  mode: "deterministic"
         sizes the workspace for `apply(..., mode="deterministic")` too (it then serves both modes).
-        max_entries: None sizes the workspace from earlier lattices of the same kind and verifies that this
-        one fits (building synchronises; a lattice that does not fit is rebuilt with a larger bound), 0 is
-        the worst case, > 0 the caller's own bound (verified)."""
+        max_entries: None sizes the workspace from what the lattice needs and verifies that it fits (building
+        synchronises once per reference image; a lattice that does not fit is rebuilt with a larger bound), 0
+        is the worst case (never synchronises), > 0 the caller's own bound (verified)."""
         _float32_only(reference_image, "Lattice (build once, apply many times)")
         if bilateral:
             _check_tensor(reference_image, "reference_image")
@@ -365,11 +365,10 @@ class Lattice:
         with torch.cuda.device(device):
             if max_entries is None:
                 worst = call.batch * call.n * (call.pd + 1)
-                # a lattice of its own workspace: always verified (identity None never matches an earlier call)
-                self.workspace, self.max_entries = _run_sized(("Lattice",) + _kind(device, call), None, call.batch,
-                                                              worst, device, stream, build,
-                                                              floor=_direct_index_floor(call))
-                _verified.pop(("Lattice",) + _kind(device, call), None)
+                # verified like a filter call: once per reference image, not again for a lattice rebuilt on it
+                self.workspace, self.max_entries = _run_sized(
+                    ("Lattice",) + _kind(device, call), _identity(reference_image if bilateral else None, call.batch),
+                    call.batch, worst, device, stream, build, floor=_direct_index_floor(call))
             else:
                 self.workspace = build(self.max_entries)
                 if self.max_entries > 0:   # a bound chosen by the caller may be too small: known on the device only
