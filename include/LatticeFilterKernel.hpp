@@ -83,8 +83,9 @@ template <typename T>
 struct Abi;
 template <>
 struct Abi<float> {
-    static int workspace_bytes(int batch, int n, int pd, int vd, int nsd, const int* sd, size_t* bytes) {
-        return pl_workspace_bytes(batch, n, pd, vd, nsd, sd, 0, PL_MODE_ATOMIC, bytes);
+    static int workspace_bytes(int batch, int n, int pd, int vd, int nsd, const int* sd, size_t* bytes,
+                               int64_t max_entries = 0) {
+        return pl_workspace_bytes(batch, n, pd, vd, nsd, sd, max_entries, PL_MODE_ATOMIC, bytes);
     }
     static int compute_positions(const float* ref, float* pos, int n, int r, int nsd, const int* sd, float s_std,
                                  float f_std, void* stream) {
@@ -96,15 +97,16 @@ struct Abi<float> {
     }
     static int lattice_filter(float* out, const float* in, const float* ref, int batch, int nsd, const int* sd,
                               int c, int r, int bilateral, float ta, float tb, float tg, int reverse, void* ws,
-                              size_t ws_bytes, void* stream) {
+                              size_t ws_bytes, void* stream, int64_t max_entries = 0) {
         return pl_lattice_filter_f32(out, in, ref, batch, nsd, sd, c, r, bilateral, ta, tb, tg, reverse, ws,
-                                     ws_bytes, 0, PL_MODE_ATOMIC, stream);
+                                     ws_bytes, max_entries, PL_MODE_ATOMIC, stream);
     }
 };
 template <>
 struct Abi<double> {
-    static int workspace_bytes(int batch, int n, int pd, int vd, int nsd, const int* sd, size_t* bytes) {
-        return pl_workspace_bytes_f64(batch, n, pd, vd, nsd, sd, 0, bytes);
+    static int workspace_bytes(int batch, int n, int pd, int vd, int nsd, const int* sd, size_t* bytes,
+                               int64_t max_entries = 0) {
+        return pl_workspace_bytes_f64(batch, n, pd, vd, nsd, sd, max_entries, bytes);
     }
     static int compute_positions(const double* ref, double* pos, int n, int r, int nsd, const int* sd,
                                  double s_std, double f_std, void* stream) {
@@ -116,9 +118,9 @@ struct Abi<double> {
     }
     static int lattice_filter(double* out, const double* in, const double* ref, int batch, int nsd, const int* sd,
                               int c, int r, int bilateral, double ta, double tb, double tg, int reverse, void* ws,
-                              size_t ws_bytes, void* stream) {
+                              size_t ws_bytes, void* stream, int64_t max_entries = 0) {
         return pl_lattice_filter_f64(out, in, ref, batch, nsd, sd, c, r, bilateral, ta, tb, tg, reverse, ws,
-                                     ws_bytes, 0, stream);
+                                     ws_bytes, max_entries, stream);
     }
 };
 
@@ -184,6 +186,46 @@ public:
                                      n_reference_channels, bilateral_ ? 1 : 0, theta_alpha_, theta_beta_,
                                      theta_gamma_, reverse_ ? 1 : 0, ws, context->temp_bytes(), d.stream()),
               "LatticeFilterOp::Compute");
+    }
+
+    // Compute with a workspace sized for `max_entries` lattice entries instead of the bound that can never
+    // overflow (batch * points * (pd + 1), several times what lattices need).  Whether the lattice fitted is
+    // known on the device only: the status is read after the call (this SYNCHRONISES the stream) and the call
+    // is repeated with four times the bound as long as it did not fit (a call that did not fit has filled
+    // `output` with NaN).  Returns the counters of the call that succeeded: stats.num_entries is what this data
+    // needed, a bound for the next call on similar data.  The reference allocates its worst case on every
+    // call (src/PermutohedralLatticeGPU.cuh:434-451).
+    pl_stats ComputeSized(const GpuDevice& d, OpContext* context, const T* input,
+                          const std::vector<int>& input_shape, const T* reference, int n_reference_channels,
+                          T* output, int64_t max_entries) const {
+        if (input_shape.size() < 3) throw Error(PL_INVALID_ARGUMENT, "LatticeFilterOp::ComputeSized");
+        const int batch = input_shape.front(), channels = input_shape.back();
+        std::vector<int> sdims(input_shape.begin() + 1, input_shape.end() - 1);
+        long long n = 1;
+        for (int s : sdims) n *= s;
+        const int pd = (int)sdims.size() + (bilateral_ ? n_reference_channels : 0), vd = channels + 1;
+        pl_stats stats = {};
+        if (batch == 0 || n == 0) return stats;
+        const int64_t worst = (int64_t)batch * n * (pd + 1);
+        for (;;) {
+            if (max_entries <= 0 || max_entries >= worst) max_entries = 0;   // 0: the worst case
+            size_t bytes = 0;
+            check(Abi<T>::workspace_bytes(batch, (int)n, pd, vd, (int)sdims.size(), sdims.data(), &bytes, max_entries),
+                  "LatticeFilterOp::ComputeSized");
+            void* ws = context->allocate_temp(bytes);
+            check(Abi<T>::lattice_filter(output, input, reference, batch, (int)sdims.size(), sdims.data(), channels,
+                                         n_reference_channels, bilateral_ ? 1 : 0, theta_alpha_, theta_beta_,
+                                         theta_gamma_, reverse_ ? 1 : 0, ws, context->temp_bytes(), d.stream(),
+                                         max_entries),
+                  "LatticeFilterOp::ComputeSized");
+            check(pl_lattice_stats(ws, &stats, d.stream()), "LatticeFilterOp::ComputeSized");
+            if (stats.device_status == PL_CAPACITY_EXCEEDED && max_entries > 0) {
+                max_entries *= 4;
+                continue;
+            }
+            if (stats.device_status != PL_OK) throw Error(stats.device_status, "LatticeFilterOp::ComputeSized (device)");
+            return stats;
+        }
     }
 
     // The reference's own structure (src/LatticeFilterKernel.cpp:145-179): a positions buffer, then

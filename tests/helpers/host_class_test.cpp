@@ -44,6 +44,7 @@ static int run(FILE* f, const char* out_path) {
     if (R) cudaMemcpyAsync(d_ref, ref.data(), ref.size() * sizeof(T), cudaMemcpyHostToDevice, stream);
 
     int n_allocs = 0;
+    long long sized_entries = 0, sized_bound = 0;
     pl::OpContext context([&](size_t bytes) { void* p = nullptr; cudaMalloc(&p, bytes); n_allocs++; return p; },
                           [](void* p) { cudaFree(p); });
     pl::GpuDevice device{stream};
@@ -53,6 +54,24 @@ static int run(FILE* f, const char* out_path) {
         cudaMemcpyAsync(out.data(), d_out, out.size() * sizeof(T), cudaMemcpyDeviceToHost, stream);
         op.ComputePerItem(device, &context, d_in, shape, d_ref, R, d_pos, d_out);
         cudaMemcpyAsync(out2.data(), d_out, out2.size() * sizeof(T), cudaMemcpyDeviceToHost, stream);
+        // the same op with a workspace sized from a (far too small) entry bound: verified and repeated until it fits
+        {
+            std::vector<T> out3(out.size());
+            const pl_stats st = op.ComputeSized(device, &context, d_in, shape, d_ref, R, d_out, 64);
+            cudaMemcpyAsync(out3.data(), d_out, out3.size() * sizeof(T), cudaMemcpyDeviceToHost, stream);
+            if (cudaStreamSynchronize(stream) != cudaSuccess) die("stream failed");
+            if (st.device_status != PL_OK || st.num_entries <= 64 || st.max_entries < st.num_entries)
+                die("ComputeSized: unexpected counters");
+            double worst = 0;
+            for (size_t i = 0; i < out.size(); i++) {
+                const double diff = (double)out3[i] - (double)out[i];
+                if (!(diff == diff)) die("ComputeSized: NaN in the output");
+                if (diff < 0 ? -diff > worst : diff > worst) worst = diff < 0 ? -diff : diff;
+            }
+            if (worst > 1e-4) die("ComputeSized: output differs from Compute");
+            sized_entries = (long long)st.num_entries;
+            sized_bound = (long long)st.max_entries;
+        }
         // an unsupported position dimension must surface as an exception, not abort the process
         bool threw = false;
         try {
@@ -70,7 +89,7 @@ static int run(FILE* f, const char* out_path) {
     fwrite(out.data(), sizeof(T), out.size(), f);
     fwrite(out2.data(), sizeof(T), out2.size(), f);
     fclose(f);
-    printf("ok allocs=%d\n", n_allocs);
+    printf("ok allocs=%d sized_entries=%lld sized_bound=%lld\n", n_allocs, sized_entries, sized_bound);
     return 0;
 }
 

@@ -40,6 +40,9 @@ def test_cpp_op_class_matches_oracle(shape, c, r, bilateral, reverse, dtype, tmp
                          timeout=300)
     assert res.returncode == 0, res.stderr
     assert res.stdout.startswith("ok")
+    # ComputeSized started from a bound of 64 entries and grew it until the lattice fitted
+    fields = dict(kv.split("=") for kv in res.stdout.split()[1:])
+    assert 64 < int(fields["sized_entries"]) <= int(fields["sized_bound"])
     got = np.fromfile(dst, dtype).reshape((2,) + inp.shape)
     want = oracle.lattice_filter(inp, ref, bilateral, ta, tb, tg, reverse, dtype=dtype)
     for which, name in ((0, "whole batch"), (1, "per item")):
