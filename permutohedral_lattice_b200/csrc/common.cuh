@@ -46,11 +46,12 @@ struct Header {   // first 256 bytes of the workspace
     u32 absmax_bits;   // deterministic mode: bit pattern of max |input| (non-negative floats order as integers)
     u32 direct;        // 1: vertices were found by direct indexing (spatial-only call), 0: through the hash table
     u32 capacity;      // the max_entries the workspace was laid out for (written by build_tiles)
-    u32 pad[57];
+    u32 sorted;        // 1: the lattice was built for reuse and holds every tile's splats sorted by entry
+    u32 pad[56];
 };
 
 struct Layout {   // byte offsets into the workspace
-    size_t tile_info, rec, rec_w, list_keys, list_ref, vid, vkeys, table, nbr, v0, v1, v64, total;
+    size_t tile_info, rec, rec_w, srec, list_keys, list_ref, vid, vkeys, table, nbr, v0, v1, v64, total;
     u64 max_entries;   // capacity of entry- and vertex-indexed arrays
     u64 table_slots;   // allocated slots (power of two)
 };
@@ -70,7 +71,17 @@ struct Cfg {
                               : (5 * SPLATS <= 4 * 4096) ? 4096
                               : (5 * SPLATS <= 4 * 8192) ? 8192
                                                          : 16384;   // shared hash slots (>= 1.25 * SPLATS)
-    static constexpr size_t BUILD_SMEM = sizeof(Key<KW>) * SPLATS + sizeof(int) * LS + sizeof(u16) * SPLATS;
+    // The tile's splats sorted by entry, as build_tiles leaves them for the splat kernels: cut into windows
+    // of WL splats, each followed by one spare 8-byte word (lanes that walk neighbouring windows in step then
+    // read words an odd number of 8-byte words apart: no shared-memory bank collisions), SREC words per tile
+    // (even: the list moves by bulk copies, whose sizes are multiples of 16 bytes).
+    static constexpr int WL = 8 * (PD + 1);
+    static constexpr int SREC = (SPLATS + SPLATS / WL + 1 + 1) & ~1;
+    __host__ __device__ static constexpr int srec_slot(int pos) { return pos + pos / WL; }
+    // build_tiles assembles that list in the memory of its key list, which is therefore at least as large
+    static constexpr size_t BUILD_KEYS = sizeof(Key<KW>) * SPLATS > sizeof(uint2) * SREC ? sizeof(Key<KW>) * SPLATS
+                                                                                        : sizeof(uint2) * SREC;
+    static constexpr size_t BUILD_SMEM = BUILD_KEYS + sizeof(int) * LS + sizeof(u16) * SPLATS;
 };
 
 template <int KW>

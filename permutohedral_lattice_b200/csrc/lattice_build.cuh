@@ -18,24 +18,32 @@ struct is_double<double> { static constexpr bool value = true; };
 
 // Up to pd = 5 six CTAs fit an SM's shared memory; capping the registers for that (40 per thread, a
 // few bytes of spills at pd = 5) measured 13 % faster than five CTAs with 48.
-template <int PD, typename R = float>
+// SORTED (float calls that build a lattice for reuse): also leave every tile's splats sorted by entry in
+// `srec`, in the form the splat kernels walk, so that no later splat through this lattice sorts again.
+// It costs this kernel a quarter more time and saves every splat a fifth: worth it from the second
+// splat on, which is why the one-call filter does not ask for it.
+template <int PD, typename R = float, bool SORTED = false>
 __global__ void __launch_bounds__(Cfg<PD>::TP, (PD <= 5 && !is_double<R>::value) ? 6 : 1)
 build_tiles(Geom g, const R* __restrict__ positions, const R* __restrict__ reference,
             Header* hdr, int2* __restrict__ tile_info, u16* __restrict__ rec, R* __restrict__ rec_w,
-            Key<Cfg<PD>::KW>* __restrict__ list_keys, u32 max_entries) {
+            uint2* __restrict__ srec, Key<Cfg<PD>::KW>* __restrict__ list_keys, u32 max_entries) {
     constexpr int KW = Cfg<PD>::KW, TP = Cfg<PD>::TP, SPLATS = Cfg<PD>::SPLATS, LS = Cfg<PD>::LS;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     Key<KW>* keys_s = reinterpret_cast<Key<KW>*>(smem_raw);
-    int* hslots = reinterpret_cast<int*>(smem_raw + sizeof(Key<KW>) * SPLATS);
-    u16* lidx_s = reinterpret_cast<u16*>(smem_raw + sizeof(Key<KW>) * SPLATS + sizeof(int) * LS);
+    int* hslots = reinterpret_cast<int*>(smem_raw + Cfg<PD>::BUILD_KEYS);
+    u16* lidx_s = reinterpret_cast<u16*>(smem_raw + Cfg<PD>::BUILD_KEYS + sizeof(int) * LS);
     __shared__ int cnt_s[PD + 1], base_s;   // entries per remainder; first global entry of the tile
+    __shared__ int wsum_s[TP / 32];
 
     PhaseClock pc(0);
     const TilePos tpos = this_tile(g);
     const int tid = threadIdx.x, tile = tpos.tile;
     for (int i = tid; i < LS; i += TP) hslots[i] = -1;
     if (tid <= PD) cnt_s[tid] = 0;
-    if (tile == 0 && tid == 0) hdr->capacity = max_entries;
+    if (tile == 0 && tid == 0) {
+        hdr->capacity = max_entries;
+        hdr->sorted = SORTED ? 1u : 0u;
+    }
 
     int item, pix, po, py, px;
     const bool valid = tile_point(g, tpos, tid, item, pix, po, py, px);
@@ -133,6 +141,9 @@ build_tiles(Geom g, const R* __restrict__ positions, const R* __restrict__ refer
     // entries grouped by warp).  Per warp ONE shared-memory atomic instruction: lane r adds the warp's
     // number of new remainder-r entries to counter r.  The index stored now is relative to the
     // remainder's segment; the segment starts are known after the barrier.
+    int* run_s = hslots;   // the tile hash is dead from here on: its memory counts the splats of every entry
+    if constexpr (SORTED)
+        for (int i = tid; i < SPLATS; i += TP) run_s[i] = 0;
     {
         const int lane = tid & 31;
         unsigned owners[PD + 1];
@@ -179,6 +190,13 @@ build_tiles(Geom g, const R* __restrict__ positions, const R* __restrict__ refer
         lfin[r] = (valid && rep[r] >= 0) ? (u16)(seg[r] + lidx_s[rep[r]]) : (u16)0;   // the representative has the same remainder
         rec_tile[r * TP + tid] = lfin[r];
     }
+    // The tile's splats sorted by entry (what the splat stage walks): a counting sort whose first half,
+    // one shared-memory atomic per splat, returns the splat's place inside its entry's run.
+    int place[PD + 1];
+    if constexpr (SORTED) {
+#pragma unroll
+        for (int r = 0; r <= PD; r++) place[r] = valid ? atomicAdd(&run_s[lfin[r]], 1) : 0;
+    }
     __syncthreads();
     pc.mark();
     const int base = base_s;
@@ -187,6 +205,55 @@ build_tiles(Geom g, const R* __restrict__ positions, const R* __restrict__ refer
         for (int r = 0; r <= PD; r++) {
             const int me = r * TP + tid;
             if (rep[r] == me) list_keys[(size_t)base + lfin[r]] = keys_s[me];
+        }
+    }
+    if constexpr (SORTED && !is_double<R>::value) {
+        // run starts: exclusive prefix sum of the entries' splat counts (thread t owns entries
+        // t (PD+1) .. t (PD+1) + PD)
+        const int lane = tid & 31, warp = tid >> 5;
+        int local[PD + 1];
+        int sum = 0;
+#pragma unroll
+        for (int r = 0; r <= PD; r++) {
+            const int i = tid * (PD + 1) + r;
+            local[r] = sum;
+            sum += (i < cnt) ? run_s[i] : 0;
+        }
+        int incl = sum;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const int t = __shfl_up_sync(0xFFFFFFFFu, incl, d);
+            if (lane >= d) incl += t;
+        }
+        if (lane == 31) wsum_s[warp] = incl;
+        __syncthreads();
+        int before = 0;
+#pragma unroll
+        for (int q = 0; q < TP / 32; q++) before += (q < warp) ? wsum_s[q] : 0;
+        const int excl = incl - sum + before;
+#pragma unroll
+        for (int r = 0; r <= PD; r++) {
+            const int i = tid * (PD + 1) + r;
+            if (i < cnt) run_s[i] = excl + local[r];
+        }
+        __syncthreads();
+        // the list is assembled in shared memory (the key list is dead: the barriers above are behind every
+        // thread's key stores) and leaves as one bulk copy
+        uint2* sorted_s = reinterpret_cast<uint2*>(smem_raw);
+        if (valid) {
+            const R* recw_mine = rec_w + (size_t)tile * SPLATS + tid;   // this thread's own earlier stores
+#pragma unroll
+            for (int r = 0; r <= PD; r++) {
+                const int pos = run_s[lfin[r]] + place[r];
+                sorted_s[Cfg<PD>::srec_slot(pos)] =
+                    make_uint2((unsigned)tid | ((unsigned)lfin[r] << 16), __float_as_uint(recw_mine[r * TP]));
+            }
+        }
+        fence_async_proxy();
+        __syncthreads();
+        if (tid == 0) {
+            bulk_store(srec + (size_t)tile * Cfg<PD>::SREC, sorted_s, (unsigned)(sizeof(uint2) * Cfg<PD>::SREC));
+            bulk_store_finish();
         }
     }
     pc.mark(true);

@@ -29,6 +29,7 @@
 #include <mutex>
 #include <stdint.h>
 #include <stdio.h>
+#include <stdlib.h>
 #include <string.h>
 #include <utility>
 
@@ -83,6 +84,11 @@ static size_t align_up(size_t x) { return (x + 255) & ~(size_t)255; }
 
 static int tp_of(int pd) { return pd <= 8 ? 256 : 128; }
 static int kw_of(int pd) { return (pd + 1 + 3) / 4; }
+// 8-byte words of a tile's sorted splat list (Cfg<PD>::SREC)
+static int srec_words_of(int pd) {
+    const int splats = tp_of(pd) * (pd + 1), wl = 8 * (pd + 1);
+    return (splats + splats / wl + 1 + 1) & ~1;
+}
 
 static bool pd_supported(int pd) {
     return pd == 1 || pd == 2 || pd == 3 || pd == 4 || pd == 5 || pd == 6 || pd == 7 || pd == 8 ||
@@ -165,6 +171,8 @@ static int make_layout(Layout& L, const Geom& g, int pd, int vd, int64_t max_ent
     L.tile_info = off; off += align_up(sizeof(int2) * (size_t)g.num_tiles);
     L.rec = off;       off += align_up(sizeof(u16) * tile_splats * (size_t)g.num_tiles);
     L.rec_w = off;     off += align_up((size_t)real_bytes * tile_splats * (size_t)g.num_tiles);
+    L.srec = off;      // the splats of every tile sorted by entry (float calls: what their splat kernels walk)
+    if (real_bytes == 4) off += align_up(sizeof(uint2) * (size_t)srec_words_of(pd) * (size_t)g.num_tiles);
     L.list_keys = off; off += align_up(sizeof(u64) * kw_of(pd) * E);
     L.list_ref = off;  off += align_up(sizeof(u32) * E);
     L.vid = off;       off += align_up(sizeof(u32) * E);
@@ -254,22 +262,24 @@ static bool bulk_rows_ok(const Geom& g, const void* ptr, int channels) {
 
 // splat / slice for value dimension vd: the instantiation with vd fixed at compile time where there
 // is one, else the generic one.
-template <int PD, int VD>
-static int launch_splat(const Geom& g, const float* input, Header* hdr, const int2* tile_info, const u16* rec,
-                        const float* rec_w, const u32* list_ref, float* v0, int vd, cudaStream_t st) {
+template <int PD, int VD, bool PRE>
+static int launch_splat_as(const Geom& g, const float* input, Header* hdr, const int2* tile_info, const u16* rec,
+                           const float* rec_w, const uint2* srec, const u32* list_ref, float* v0, int vd,
+                           cudaStream_t st) {
     if constexpr (VD > 8 && VD <= 32) {   // wide rows: a quarter warp per window, conflict-free row reads
-        const size_t smem = SplatRows<PD, VD>::BYTES;
+        using SR = SplatRows<PD, VD, PRE>;
+        const size_t smem = SR::BYTES;
         // five CTAs per SM need nearly all of the SM's shared memory: ask for the largest carve-out
-        PL_TRY((ensure_dynamic_smem<splat_tiles_rows<PD, VD>>(smem, true)));
+        PL_TRY((ensure_dynamic_smem<splat_tiles_rows<PD, VD, PRE>>(smem, true)));
         // bulk staging also needs 16-byte aligned landing zones inside the padded tile rows
-        const bool bulk = bulk_rows_ok(g, input, VD - 1) && g.TX <= 16 &&
-                          (g.TX * (SplatRows<PD, VD>::VP - (VD - 1))) % 4 == 0;
-        PL_LAUNCH((splat_tiles_rows<PD, VD>), tile_grid(g), Cfg<PD>::TP, smem, st, g, input, hdr, tile_info, rec, rec_w,
-                                                                         list_ref, v0, bulk ? 1 : 0);
+        const bool bulk = bulk_rows_ok(g, input, VD - 1) && g.TX <= 16 && (g.TX * (SR::VP - (VD - 1))) % 4 == 0;
+        PL_LAUNCH((splat_tiles_rows<PD, VD, PRE>), tile_grid(g), Cfg<PD>::TP, smem, st, g, input, hdr, tile_info, rec, rec_w,
+                                                                              srec, list_ref, v0, bulk ? 1 : 0);
     } else if constexpr (VD > 0) {
-        const size_t smem = SplatFast<PD, VD>::BYTES;
-        PL_TRY((ensure_dynamic_smem<splat_tiles_fast<PD, VD>>(smem)));
-        PL_LAUNCH((splat_tiles_fast<PD, VD>), tile_grid(g), Cfg<PD>::TP, smem, st, g, input, hdr, tile_info, rec, rec_w, list_ref, v0, bulk_rows_ok(g, input, VD - 1) ? 1 : 0);
+        const size_t smem = SplatFast<PD, VD, PRE>::BYTES;
+        PL_TRY((ensure_dynamic_smem<splat_tiles_fast<PD, VD, PRE>>(smem)));
+        PL_LAUNCH((splat_tiles_fast<PD, VD, PRE>), tile_grid(g), Cfg<PD>::TP, smem, st, g, input, hdr, tile_info, rec, rec_w,
+                                                                              srec, list_ref, v0, bulk_rows_ok(g, input, VD - 1) ? 1 : 0);
     } else {
         const size_t smem = SplatGeneric<PD>::bytes(vd);
         if (smem > 200 * 1024) return PL_UNSUPPORTED_DIMS;
@@ -278,6 +288,15 @@ static int launch_splat(const Geom& g, const float* input, Header* hdr, const in
                                                                         list_ref, v0, vd);
     }
     return PL_OK;
+}
+
+// presorted: the lattice was built for reuse (build_tiles with SORTED) and holds its splats sorted in srec
+template <int PD, int VD>
+static int launch_splat(const Geom& g, const float* input, Header* hdr, const int2* tile_info, const u16* rec,
+                        const float* rec_w, const uint2* srec, bool presorted, const u32* list_ref, float* v0, int vd,
+                        cudaStream_t st) {
+    return presorted ? launch_splat_as<PD, VD, true>(g, input, hdr, tile_info, rec, rec_w, srec, list_ref, v0, vd, st)
+                     : launch_splat_as<PD, VD, false>(g, input, hdr, tile_info, rec, rec_w, srec, list_ref, v0, vd, st);
 }
 
 template <int PD, int VD>
@@ -320,6 +339,8 @@ static int run_filter(const Geom& g, float* output, const float* input, const fl
     int2* tile_info = reinterpret_cast<int2*>(ws + L.tile_info);
     u16* rec = reinterpret_cast<u16*>(ws + L.rec);
     float* rec_w = reinterpret_cast<float*>(ws + L.rec_w);
+    uint2* srec = reinterpret_cast<uint2*>(ws + L.srec);
+    if (srec_words_of(PD) != Cfg<PD>::SREC) return PL_INTERNAL_ERROR;   // the layout and the kernels agree on the stride
     Key<KW>* list_keys = reinterpret_cast<Key<KW>*>(ws + L.list_keys);
     u32* list_ref = reinterpret_cast<u32*>(ws + L.list_ref);
     u32* vid = reinterpret_cast<u32*>(ws + L.vid);
@@ -343,7 +364,15 @@ static int run_filter(const Geom& g, float* output, const float* input, const fl
     while ((1ull << table_log2) < L.table_slots) table_log2++;
 
     if (phases & PH_BUILD) {
-        PL_LAUNCH((build_tiles<PD>), tile_grid(g), TP, Cfg<PD>::BUILD_SMEM, st, g, positions, reference, hdr, tile_info, rec, rec_w, list_keys, (u32)L.max_entries);
+        // a lattice built to be applied later (no values in this call) also gets its splats sorted
+        if (phases & PH_APPLY) {
+            PL_LAUNCH((build_tiles<PD, float, false>), tile_grid(g), TP, Cfg<PD>::BUILD_SMEM, st, g, positions, reference, hdr,
+                                                                         tile_info, rec, rec_w, srec, list_keys, (u32)L.max_entries);
+        } else {
+            PL_TRY((ensure_dynamic_smem<build_tiles<PD, float, true>>(Cfg<PD>::BUILD_SMEM)));
+            PL_LAUNCH((build_tiles<PD, float, true>), tile_grid(g), TP, Cfg<PD>::BUILD_SMEM, st, g, positions, reference, hdr,
+                                                                        tile_info, rec, rec_w, srec, list_keys, (u32)L.max_entries);
+        }
         PL_COUNT_LAUNCHES(4);   // build_tiles and the three launches of the index stage below
         if (ev) PL_CUDA(cudaEventRecord(ev[1], st));
         Direct direct;
@@ -396,7 +425,7 @@ static int run_filter(const Geom& g, float* output, const float* input, const fl
         PL_LAUNCH((convert_fixed), wide, 256, 0, st, hdr, v64, v0, padded_vd(vd));
         PL_COUNT_LAUNCHES(2);   // absmax_kernel, convert_fixed (the splat itself is counted below)
     } else {
-        rc = PL_DISPATCH_VD(launch_splat, PD, vd, g, input, hdr, tile_info, rec, rec_w, list_ref, v0, vd, st);
+        rc = PL_DISPATCH_VD(launch_splat, PD, vd, g, input, hdr, tile_info, rec, rec_w, srec, !(phases & PH_BUILD), list_ref, v0, vd, st);
     }
     if (rc != PL_OK) return rc;
     PL_COUNT_LAUNCHES(1 + 1);   // splat, slice (the blur launches are counted where they are issued)
@@ -448,7 +477,7 @@ static int run_filter_f64(const Geom& g, double* output, const double* input, co
     while ((1ull << table_log2) < L.table_slots) table_log2++;
     const int vp = padded_vd_f64(vd);
 
-    PL_LAUNCH((build_tiles<PD, double>), tile_grid(g), TP, Cfg<PD>::BUILD_SMEM, st, g, positions, reference, hdr, tile_info, rec, rec_w, list_keys, (u32)L.max_entries);
+    PL_LAUNCH((build_tiles<PD, double>), tile_grid(g), TP, Cfg<PD>::BUILD_SMEM, st, g, positions, reference, hdr, tile_info, rec, rec_w, static_cast<uint2*>(nullptr), list_keys, (u32)L.max_entries);
     // spatial-only calls index their vertices directly, as the float calls do (the key bounds hold for
     // either arithmetic: the margin is far wider than any rounding)
     Direct direct;
@@ -905,16 +934,16 @@ int pl_export_lattice_f64(const void* workspace, const double* positions, const 
 int pl_debug_occupancy(int* out) {
     PL_CUDA(cudaFuncSetAttribute(build_tiles<5>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg<5>::BUILD_SMEM));
     PL_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&out[0], build_tiles<5>, 256, Cfg<5>::BUILD_SMEM));
-    const size_t ss = SplatRows<5, 22>::BYTES;
-    PL_CUDA(cudaFuncSetAttribute(splat_tiles_rows<5, 22>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ss));
-    PL_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&out[1], splat_tiles_rows<5, 22>, 256, ss));
+    const size_t ss = SplatRows<5, 22, false>::BYTES;
+    PL_CUDA(cudaFuncSetAttribute(splat_tiles_rows<5, 22, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ss));
+    PL_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&out[1], splat_tiles_rows<5, 22, false>, 256, ss));
     int rows_cap = (40 * 1024) / (SliceFast<5, 22>::RS * 4);
     const size_t sl = SliceFast<5, 22>::bytes(rows_cap);
     PL_CUDA(cudaFuncSetAttribute(slice_tiles_fast<5, 22>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sl));
     PL_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&out[2], slice_tiles_fast<5, 22>, 256, sl));
     out[3] = (int)Cfg<5>::BUILD_SMEM; out[4] = (int)ss; out[5] = (int)sl;
     cudaFuncAttributes fa;
-    PL_CUDA(cudaFuncGetAttributes(&fa, splat_tiles_rows<5, 22>));
+    PL_CUDA(cudaFuncGetAttributes(&fa, splat_tiles_rows<5, 22, false>));
     out[6] = fa.numRegs; out[7] = (int)fa.sharedSizeBytes;
     return PL_OK;
 }

@@ -90,12 +90,40 @@ struct SplatCommon {
     }
 };
 
-template <int PD, int VD>
+// A splat kernel that expects sorted splats met a lattice without them (pl_lattice_apply_f32 on a workspace
+// that no pl_lattice_build*_f32 prepared): the call fails, its output is poisoned by the slice stage.
+__device__ __forceinline__ bool lattice_is_sorted(Header* hdr) {
+    if (hdr->sorted) return true;
+    if (threadIdx.x == 0) atomicOr(&hdr->status, 1u << PL_INVALID_ARGUMENT);
+    return false;
+}
+
+// The tile's splats as build_tiles sorted them (entry order; (point | entry << 16, weight bits) each),
+// copied into the windowed shared-memory list.  The caller's next barrier publishes them.
+template <int PD, int WL>
+__device__ __forceinline__ void load_sorted_splats(const uint2* __restrict__ srec_tile, int total, uint2* sorted_s) {
+    constexpr int TP = Cfg<PD>::TP;
+    uint2 v[PD + 1];
+#pragma unroll
+    for (int r = 0; r <= PD; r++) {
+        const int pos = r * TP + (int)threadIdx.x;
+        v[r] = (pos < total) ? srec_tile[Cfg<PD>::srec_slot(pos)] : make_uint2(0u, 0u);
+    }
+#pragma unroll
+    for (int r = 0; r <= PD; r++) {
+        const int pos = r * TP + (int)threadIdx.x;
+        if (pos < total) sorted_s[SplatCommon<PD>::template slot<WL>(pos)] = v[r];
+    }
+}
+
+// PRE: the lattice was built for reuse and holds every tile's splats already sorted (build_tiles with
+// SORTED = true); the kernel copies that list instead of sorting the tile's records.
+template <int PD, int VD, bool PRE>
 struct SplatFast {
     static constexpr int TP = Cfg<PD>::TP, SPLATS = Cfg<PD>::SPLATS, C = VD - 1;
     static constexpr size_t IN_BYTES = ((sizeof(float) * TP * C + 15) / 16) * 16;
     static constexpr int SORTED = SplatCommon<PD>::SORTED;
-    static constexpr size_t BYTES = IN_BYTES + sizeof(uint2) * SORTED + 2 * sizeof(int) * SPLATS + sizeof(int) * TP;
+    static constexpr size_t BYTES = IN_BYTES + sizeof(uint2) * SORTED + (PRE ? 1 : 2) * sizeof(int) * SPLATS + sizeof(int) * TP;
 };
 
 // Adds a row held in registers to vertex row `vrow` (VP floats, 16-byte aligned).
@@ -108,21 +136,23 @@ __device__ __forceinline__ void flush_row(float* vrow, float* acc) {
     for (int j = 0; j < VP; j++) acc[j] = 0.f;
 }
 
-template <int PD, int VD>
+template <int PD, int VD, bool PRE>
 __global__ void __launch_bounds__(Cfg<PD>::TP)
 splat_tiles_fast(Geom g, const float* __restrict__ input, Header* hdr, const int2* __restrict__ tile_info,
-                 const u16* __restrict__ rec, const float* __restrict__ rec_w,
+                 const u16* __restrict__ rec, const float* __restrict__ rec_w, const uint2* __restrict__ srec,
                  const u32* __restrict__ list_ref, float* __restrict__ v0, int bulk_ok) {
     constexpr int TP = Cfg<PD>::TP, SPLATS = Cfg<PD>::SPLATS, C = VD - 1, VP = (VD + 3) & ~3;
+    using SF = SplatFast<PD, VD, PRE>;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     float* in_s = reinterpret_cast<float*>(smem_raw);                                       // [TP][C]
-    uint2* sorted_s = reinterpret_cast<uint2*>(smem_raw + SplatFast<PD, VD>::IN_BYTES);     // [SORTED]
-    int* cur_s = reinterpret_cast<int*>(sorted_s + SplatFast<PD, VD>::SORTED);              // [SPLATS]
-    int* prow_s = cur_s + SPLATS;                                                           // [TP]
+    uint2* sorted_s = reinterpret_cast<uint2*>(smem_raw + SF::IN_BYTES);                    // [SORTED]
+    int* prow_s = reinterpret_cast<int*>(sorted_s + SF::SORTED);                            // [TP]
     u32* vid_s = reinterpret_cast<u32*>(prow_s + TP);                                       // [SPLATS] entry -> vertex
+    int* cur_s = reinterpret_cast<int*>(vid_s + SPLATS);                                    // [SPLATS], only without PRE
     __shared__ int wsum_s[32];
     __shared__ __align__(8) u64 bar;
     if (call_failed(hdr)) return;
+    if (PRE && !lattice_is_sorted(hdr)) return;
     const TilePos tpos = this_tile(g);
     const int tid = threadIdx.x, tile = tpos.tile;
     const int2 info = tile_info[tile];
@@ -132,7 +162,7 @@ splat_tiles_fast(Geom g, const float* __restrict__ input, Header* hdr, const int
     const bool valid = tile_point(g, tpos, tid, item, pix);
     prow_s[tid] = valid ? item * g.n + pix : -1;
     for (int i = tid; i < nloc; i += TP) {
-        cur_s[i] = 0;
+        if constexpr (!PRE) cur_s[i] = 0;
         vid_s[i] = list_ref[base + i];
     }
     if (bulk_ok && tid == 0) mbar_init(&bar, 1);
@@ -155,16 +185,21 @@ splat_tiles_fast(Geom g, const float* __restrict__ input, Header* hdr, const int
         }
     }
 
-    float w[PD + 1];
-    int l[PD + 1];
-    const u16* rec_tile = rec + (size_t)tile * SPLATS;
-    const float* recw_tile = rec_w + (size_t)tile * SPLATS;
+    const int total = nvalid * (PD + 1);
+    if constexpr (PRE) {
+        load_sorted_splats<PD, PD + 1>(srec + (size_t)tile * Cfg<PD>::SREC, total, sorted_s);
+    } else {
+        float w[PD + 1];
+        int l[PD + 1];
+        const u16* rec_tile = rec + (size_t)tile * SPLATS;
+        const float* recw_tile = rec_w + (size_t)tile * SPLATS;
 #pragma unroll
-    for (int r = 0; r <= PD; r++) {
-        l[r] = valid ? rec_tile[r * TP + tid] : 0;
-        w[r] = valid ? recw_tile[r * TP + tid] : 0.f;
+        for (int r = 0; r <= PD; r++) {
+            l[r] = valid ? rec_tile[r * TP + tid] : 0;
+            w[r] = valid ? recw_tile[r * TP + tid] : 0.f;
+        }
+        SplatCommon<PD>::template sort_splats<PD + 1>(valid, l, w, nloc, sorted_s, cur_s, nullptr, wsum_s);
     }
-    SplatCommon<PD>::template sort_splats<PD + 1>(valid, l, w, nloc, sorted_s, cur_s, nullptr, wsum_s);
 
     if (bulk_ok) {
         // the outcome of the bounded wait is made uniform over the CTA: either every thread goes on or
@@ -181,7 +216,6 @@ splat_tiles_fast(Geom g, const float* __restrict__ input, Header* hdr, const int
 
     // Every thread sums a window of PD+1 consecutive sorted splats in registers; whenever the entry
     // changes, and at the end of the window, the partial row leaves as vector reductions.
-    const int total = nvalid * (PD + 1);
     const int first = tid * (PD + 1);
     if (first >= total) return;
     float acc[VP];
@@ -215,35 +249,36 @@ splat_tiles_fast(Geom g, const float* __restrict__ input, Header* hdr, const int
 // reads its own row without bank conflicts whatever rows the other quarters read.  Lane h keeps
 // channels 4h .. 4h+3 of the running sum; the row's channel C is staged as 1 (homogeneous), the padding
 // as 0, so the loop has no channel tests.  A flush is one 16-byte vector reduction per lane.
-template <int PD, int VD>
+// PRE: the lattice was built for reuse and holds every tile's splats already sorted, in the windowed form
+// (build_tiles with SORTED = true); the list then arrives by one bulk copy, the kernel needs no sort, no
+// counters, and fits five CTAs on an SM.
+template <int PD, int VD, bool PRE>
 struct SplatRows {
     static constexpr int TP = Cfg<PD>::TP, SPLATS = Cfg<PD>::SPLATS, VP = (VD + 3) & ~3;
     static constexpr int LR = VP / 4;                  // lanes that hold a piece of the row
-    static constexpr int WL = 8 * (PD + 1);            // splats per window: TP / 8 windows
-    static constexpr int SORTED = SPLATS + SPLATS / WL + 1;
-    static constexpr size_t BYTES = sizeof(float) * TP * VP + sizeof(uint2) * SORTED + sizeof(int) * SPLATS +
+    static constexpr int WL = Cfg<PD>::WL;             // splats per window: TP / 8 windows
+    static constexpr int SORTED = Cfg<PD>::SREC;
+    static constexpr size_t BYTES = sizeof(float) * TP * VP + sizeof(uint2) * SORTED + (PRE ? 0 : sizeof(int) * SPLATS) +
                                     sizeof(int) * TP;
 };
 
-#ifndef PL_SPLAT_ROWS_CTAS
-#define PL_SPLAT_ROWS_CTAS 1
-#endif
-template <int PD, int VD>
-__global__ void __launch_bounds__(Cfg<PD>::TP, PL_SPLAT_ROWS_CTAS)
+template <int PD, int VD, bool PRE>
+__global__ void __launch_bounds__(Cfg<PD>::TP, PRE ? 5 : 1)
 splat_tiles_rows(Geom g, const float* __restrict__ input, Header* hdr, const int2* __restrict__ tile_info,
-                 const u16* __restrict__ rec, const float* __restrict__ rec_w,
+                 const u16* __restrict__ rec, const float* __restrict__ rec_w, const uint2* __restrict__ srec,
                  const u32* __restrict__ list_ref, float* __restrict__ v0, int bulk_ok) {
-    using SR = SplatRows<PD, VD>;
+    using SR = SplatRows<PD, VD, PRE>;
     constexpr int TP = SR::TP, SPLATS = SR::SPLATS, C = VD - 1, VP = SR::VP, LR = SR::LR, WL = SR::WL;
     static_assert(LR <= 8, "a row must fit the 8 lanes of a quarter warp");
     extern __shared__ __align__(16) unsigned char smem_raw[];
     float* in_s = reinterpret_cast<float*>(smem_raw);                         // [TP][VP]
     uint2* sorted_s = reinterpret_cast<uint2*>(in_s + TP * VP);               // [SORTED]
-    int* cur_s = reinterpret_cast<int*>(sorted_s + SR::SORTED);               // [SPLATS]
-    int* prow_s = cur_s + SPLATS;                                             // [TP]
+    int* prow_s = reinterpret_cast<int*>(sorted_s + SR::SORTED);              // [TP]
+    int* cur_s = prow_s + TP;                                                 // [SPLATS], only without PRE
     __shared__ int wsum_s[32];
     __shared__ __align__(8) u64 bar;
     if (call_failed(hdr)) return;
+    if (PRE && !lattice_is_sorted(hdr)) return;
     PhaseClock pc(1);
     const TilePos tpos = this_tile(g);
     const int tid = threadIdx.x, tile = tpos.tile, lane = tid & 31, warp = tid >> 5;
@@ -253,21 +288,30 @@ splat_tiles_rows(Geom g, const float* __restrict__ input, Header* hdr, const int
     int item, pix;
     const bool valid = tile_point(g, tpos, tid, item, pix);
     prow_s[tid] = valid ? item * g.n + pix : -1;
-    // the splat records are loaded first: they depend on nothing but the tile number, so their latency
-    // overlaps that of the tile's entry range above
+    // without PRE the splat records are loaded first: they depend on nothing but the tile number, so their
+    // latency overlaps that of the tile's entry range above
     float w[PD + 1];
     int l[PD + 1];
-    const u16* rec_tile = rec + (size_t)tile * SPLATS;
-    const float* recw_tile = rec_w + (size_t)tile * SPLATS;
+    if constexpr (!PRE) {
+        const u16* rec_tile = rec + (size_t)tile * SPLATS;
+        const float* recw_tile = rec_w + (size_t)tile * SPLATS;
 #pragma unroll
-    for (int r = 0; r <= PD; r++) {
-        l[r] = valid ? rec_tile[r * TP + tid] : 0;
-        w[r] = valid ? recw_tile[r * TP + tid] : 0.f;
+        for (int r = 0; r <= PD; r++) {
+            l[r] = valid ? rec_tile[r * TP + tid] : 0;
+            w[r] = valid ? recw_tile[r * TP + tid] : 0.f;
+        }
+        for (int i = tid; i < nloc; i += TP) cur_s[i] = 0;
     }
-    for (int i = tid; i < nloc; i += TP) cur_s[i] = 0;
-    if (bulk_ok && tid == 0) mbar_init(&bar, 1);
+    if ((PRE || bulk_ok) && tid == 0) mbar_init(&bar, 1);
     const int nvalid = __syncthreads_count(valid);
+    const int total = nvalid * (PD + 1);
     pc.mark();
+    // PRE: the tile's sorted splats arrive by one bulk copy, already in the windowed form the loop below reads
+    constexpr unsigned REC_BYTES = PRE ? (unsigned)(sizeof(uint2) * SR::SORTED) : 0u;
+    if ((PRE || bulk_ok) && tid == 0) {
+        mbar_expect_tx(&bar, REC_BYTES + (bulk_ok ? (unsigned)nvalid * C * 4u : 0u));
+        if constexpr (PRE) bulk_load(sorted_s, srec + (size_t)tile * SR::SORTED, REC_BYTES, &bar);
+    }
 
     // Staging.  Bulk form: every tile row's block (TX points x C floats, contiguous in memory) lands
     // by one bulk asynchronous copy at the END of the tile row's padded region; after the sort a warp
@@ -276,7 +320,6 @@ splat_tiles_rows(Geom g, const float* __restrict__ input, Header* hdr, const int
     // the padded positions.
     const int land = g.TX * (VP - C);   // floats between the start of a tile row's region and its landing zone
     if (bulk_ok) {
-        if (tid == 0) mbar_expect_tx(&bar, (unsigned)nvalid * C * 4u);
         if (tid < g.TY) {
             int first, count;
             if (tile_row(g, tpos, tid, first, count))
@@ -304,11 +347,11 @@ splat_tiles_rows(Geom g, const float* __restrict__ input, Header* hdr, const int
         }
     }
 
-    SplatCommon<PD>::template sort_splats<WL>(valid, l, w, nloc, sorted_s, cur_s, nullptr, wsum_s);
+    if constexpr (!PRE) SplatCommon<PD>::template sort_splats<WL>(valid, l, w, nloc, sorted_s, cur_s, nullptr, wsum_s);
     pc.mark();
-    bool arrived = true;   // bulk form: did this thread see the copies complete within the bounded wait
+    // did this thread see the copies complete within the bounded wait
+    const bool arrived = (PRE || bulk_ok) ? mbar_wait(&bar, 0) : true;
     if (bulk_ok) {
-        arrived = mbar_wait(&bar, 0);
         constexpr int MAXE = (16 * C + 31) / 32;   // elements per lane of a tile row (TX <= 16)
         for (int ly = warp; ly < g.TY; ly += TP / 32) {
             // valid points of this tile row: its first point's validity and the row's width
@@ -346,21 +389,19 @@ splat_tiles_rows(Geom g, const float* __restrict__ input, Header* hdr, const int
                 for (int j = C + 1; j < VP; j++) region[lane * VP + j] = 0.f;
             }
         }
-        // this barrier also makes the outcome of the bounded wait uniform over the CTA: either every
-        // thread goes on or every thread leaves (after one more bounded wait, so that no copy lands in
-        // a CTA that is gone)
-        if (!__syncthreads_and(arrived ? 1 : 0)) {
-            if (tid == 0) atomicOr(&hdr->status, 1u << PL_INTERNAL_ERROR);
-            mbar_wait(&bar, 0);
-            return;
-        }
     } else {
         cp_async_wait_all();
-        __syncthreads();
+    }
+    // this barrier also makes the outcome of the bounded wait uniform over the CTA: either every thread
+    // goes on or every thread leaves (after one more bounded wait, so that no copy lands in a CTA that
+    // is gone)
+    if (!__syncthreads_and(arrived ? 1 : 0)) {
+        if (tid == 0) atomicOr(&hdr->status, 1u << PL_INTERNAL_ERROR);
+        mbar_wait(&bar, 0);
+        return;
     }
     pc.mark();
 
-    const int total = nvalid * (PD + 1);
     const int h = tid & 7, wnd = tid >> 3, first = wnd * WL;
     const bool active = (h < LR) && (first < total);
     if (active) {

@@ -307,6 +307,49 @@ def test_lattice_built_once_applied_many_times(gpu, oracle):
     assert err.value.status == 3   # PL_WORKSPACE_TOO_SMALL
 
 
+@pytest.mark.parametrize("shape,r,channels", [
+    ((2, 30, 26), 3, (21, 3, 21)),        # ragged tiles; 21 channels: quarter-warp splat, 3: thread-per-window splat
+    ((1, 64, 48), 3, (21, 1)),
+    ((1, 6, 20, 22), 1, (3, 21)),         # volume
+])
+def test_lattice_reuse_walks_the_sorted_splats(gpu, oracle, shape, r, channels):
+    """A lattice built for reuse keeps every tile's splats sorted by entry; its splat kernels copy that list
+    instead of sorting.  Checked against the oracle in the atomic mode, forward and reverse."""
+    import torch
+    import permutohedral_lattice_b200 as plb
+    rng = np.random.default_rng(47)
+    ref_n = rng.random(shape + (r,), dtype=np.float32)
+    ref = torch.from_numpy(ref_n).cuda()
+    lat = plb.Lattice(ref, bilateral=True, theta_alpha=5.0, theta_beta=0.2, max_channels=max(channels))
+    for k, c in enumerate(channels):
+        reverse = bool(k & 1)
+        x_n = rng.standard_normal(shape + (c,)).astype(np.float32)
+        got = lat.apply(torch.from_numpy(x_n).cuda(), reverse=reverse).cpu().numpy()
+        want = oracle.lattice_filter(x_n, ref_n, True, 5.0, 0.2, 1.0, reverse)
+        gpu.assert_outputs_close(got, want, "apply c=%d reverse=%s" % (c, reverse))
+    assert lat.stats().device_status == 0
+
+
+def test_apply_refuses_a_workspace_no_build_prepared(gpu):
+    """pl_lattice_apply_f32 on the workspace a one-call filter left behind: that lattice has no sorted splats, the
+    splat kernel says so through the device status and the output is NaN (nothing is read out of bounds)."""
+    import torch
+    import permutohedral_lattice_b200 as plb
+    from permutohedral_lattice_b200 import capi
+    rng = np.random.default_rng(48)
+    ref = torch.from_numpy(rng.random((1, 32, 32, 3), dtype=np.float32)).cuda()
+    x = torch.from_numpy(rng.random((1, 32, 32, 21), dtype=np.float32)).cuda()
+    _, ws, call = plb.lattice_filter_raw(x, ref, True, 5.0, 0.2, 1.0, False, max_entries=0)
+    out = torch.zeros_like(x)
+    rc = capi.lib().pl_lattice_apply_f32(
+        out.data_ptr(), x.data_ptr(), 21, 0, capi.PL_MODE_ATOMIC, 1, 32 * 32, call.pd, 2, capi.int_array([32, 32]),
+        ws.data_ptr(), ws.numel(), 0, torch.cuda.current_stream().cuda_stream)
+    assert rc == capi.PL_OK
+    torch.cuda.synchronize()
+    assert plb.lattice_stats(ws).device_status == capi.PL_INVALID_ARGUMENT
+    assert bool(torch.isnan(out).all())
+
+
 def test_autograd_with_lattice_reuse(gpu, oracle):
     import torch
     import permutohedral_lattice_b200 as plb
