@@ -62,6 +62,9 @@ def parse_args():
                     help="accumulation mode of the splat stage (the headline is atomic)")
     ap.add_argument("--dtype", default="f32", choices=["f32", "f64"],
                     help="number type of the call (the headline is f32; f64 is the reference's other registered type)")
+    ap.add_argument("--reuse-lattice", action="store_true",
+                    help="the step builds one lattice and applies it forward and backward (what a training step through "
+                         "lattice_filter(..., reuse_lattice=True) does) instead of two stateless calls; not the headline")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-threads", type=int, default=0)
     ap.add_argument("--batch", type=int, default=0,
@@ -292,9 +295,10 @@ class Arm:
     """One arm of the measurement: a set of device-resident tensors (a rank's slice of the batch, or a whole
     batch) and the forward (+ backward) step over them."""
 
-    def __init__(self, plb, capi, w, lo, hi, dev, mode="atomic", dtype="f32"):
+    def __init__(self, plb, capi, w, lo, hi, dev, mode="atomic", dtype="f32", reuse_lattice=False):
         import torch
         self.plb, self.capi, self.w, self.mode = plb, capi, w, mode
+        self.reuse_lattice = reuse_lattice
         self.b, self.n, self.c = hi - lo, w.pixels_per_item, w.vd - 1
         self.use_positions = w.positions is not None
         tt = torch.float64 if dtype == "f64" else torch.float32
@@ -321,6 +325,17 @@ class Arm:
                                                         w.theta_gamma, reverse, mode=self.mode, out=out)
 
     def step(self, events_f=None, events_b=None):
+        if self.reuse_lattice:
+            if self.b == 0:
+                return
+            w = self.w
+            lat = self.plb.Lattice(self.ref, tuple(self.x.shape[:-1]), w.bilateral, w.theta_alpha, w.theta_beta,
+                                   w.theta_gamma, max_channels=self.c, mode=self.mode)
+            lat.apply(self.x, False, self.mode, out=self.out_f)
+            if w.backward:
+                lat.apply(self.grad, True, self.mode, out=self.out_b)
+            self.ws = lat.workspace
+            return
         self.call(self.x, self.out_f, False, events_f)
         if self.w.backward:
             self.call(self.grad, self.out_b, True, events_b)
@@ -390,9 +405,11 @@ def main():
     B, n, c = full.batch, full.pixels_per_item, full.vd - 1
     sharded = B >= 2
     lo, hi = shard_range(B, world, rank) if sharded else (0, B)
-    arm = Arm(plb, capi, full, lo, hi, dev, args.mode, args.dtype)
+    if args.reuse_lattice and (args.dtype != "f32" or full.positions is not None):
+        raise SystemExit("--reuse-lattice: float calls on a reference image only")
+    arm = Arm(plb, capi, full, lo, hi, dev, args.mode, args.dtype, args.reuse_lattice)
     real_bytes = 8 if args.dtype == "f64" else 4
-    extras = not args.headline_only and args.dtype == "f32" and args.mode == "atomic"
+    extras = not args.headline_only and args.dtype == "f32" and args.mode == "atomic" and not args.reuse_lattice
     calls_per_step = 2 if full.backward else 1
     total_pixels = B * n * (1 if sharded else world)
 
@@ -426,7 +443,7 @@ def main():
     sampler.start()
     launches0 = capi.lib().pl_launch_count()
     sampler.mark_begin()
-    staged = args.dtype == "f32"    # the stage-event hook belongs to the float calls
+    staged = args.dtype == "f32" and not args.reuse_lattice   # the stage-event hook belongs to the one-call float filter
     block_ms = timed_blocks(lambda k: arm.step(), args.steps, args.min_ms,
                             (lambda k: arm.step(ev[k][0], ev[k][1] if full.backward else None)) if staged else None)
     sampler.mark_end()
@@ -461,6 +478,8 @@ def main():
     kernel_names = {"build": "build_tiles", "splat": "splat_tiles", "blur": "blur_axis",
                     "slice": "slice_tiles"}
     call_ms = ms_per_step / calls_per_step
+    if args.reuse_lattice:   # one build serves the step's calls: the features are read once per step
+        call_bytes -= stage_bytes["build"] * (calls_per_step - 1) / calls_per_step
     if staged:
         dominant = max(kernel_names, key=lambda k: stage_ms[k])
         achieved = kernel_bytes[dominant] / max(kernel_ms[dominant] * 1e-3, 1e-12) / 1e9
@@ -648,7 +667,10 @@ def main():
         "config": config_of(full, world),
         "details": {"parallelism": ("one batch of %d items sharded over %d GPU(s), no collective in the data path"
                                     % (B, world)) if sharded else "replicas only (single item), x%d" % world,
-                    "mode": args.mode, "bytes_read_per_call_on_this_rank": (hx.numel() + (
+                    "mode": args.mode,
+                    "lattice": ("built once per step, applied forward and backward" if args.reuse_lattice
+                                else "rebuilt by every call (stateless op)"),
+                    "bytes_read_per_call_on_this_rank": (hx.numel() + (
                         href.numel() if href is not None else 0)) * real_bytes,
                     "num_vertices": num_vertices, "num_entries": num_entries,
                     "timing": "median of %d blocks of %d steps, each block bracketed by barrier + synchronize, "
