@@ -311,6 +311,9 @@ def test_lattice_built_once_applied_many_times(gpu, oracle):
     ((2, 30, 26), 3, (21, 3, 21)),        # ragged tiles; 21 channels: quarter-warp splat, 3: thread-per-window splat
     ((1, 64, 48), 3, (21, 1)),
     ((1, 6, 20, 22), 1, (3, 21)),         # volume
+    ((2, 40, 36), 0, (3, 21)),            # spatial only: one-word keys, vertices found by direct indexing
+    ((1, 24, 20), 14, (3, 21)),           # pd 16: 128-point tiles, five-word keys
+    ((2, 50), 1, (1, 3)),                 # 1-D signal, pd 2
 ])
 def test_lattice_reuse_walks_the_sorted_splats(gpu, oracle, shape, r, channels):
     """A lattice built for reuse keeps every tile's splats sorted by entry; its splat kernels copy that list
@@ -318,14 +321,16 @@ def test_lattice_reuse_walks_the_sorted_splats(gpu, oracle, shape, r, channels):
     import torch
     import permutohedral_lattice_b200 as plb
     rng = np.random.default_rng(47)
-    ref_n = rng.random(shape + (r,), dtype=np.float32)
+    bilateral = r > 0
+    ref_n = rng.random(shape + (max(r, 1),), dtype=np.float32)
     ref = torch.from_numpy(ref_n).cuda()
-    lat = plb.Lattice(ref, bilateral=True, theta_alpha=5.0, theta_beta=0.2, max_channels=max(channels))
+    lat = plb.Lattice(ref if bilateral else None, shape, bilateral, theta_alpha=5.0, theta_beta=0.2, theta_gamma=3.0,
+                      max_channels=max(channels))
     for k, c in enumerate(channels):
         reverse = bool(k & 1)
         x_n = rng.standard_normal(shape + (c,)).astype(np.float32)
         got = lat.apply(torch.from_numpy(x_n).cuda(), reverse=reverse).cpu().numpy()
-        want = oracle.lattice_filter(x_n, ref_n, True, 5.0, 0.2, 1.0, reverse)
+        want = oracle.lattice_filter(x_n, ref_n, bilateral, 5.0, 0.2, 3.0, reverse)
         gpu.assert_outputs_close(got, want, "apply c=%d reverse=%s" % (c, reverse))
     assert lat.stats().device_status == 0
 
