@@ -29,7 +29,6 @@
 #include <mutex>
 #include <stdint.h>
 #include <stdio.h>
-#include <stdlib.h>
 #include <string.h>
 #include <utility>
 
