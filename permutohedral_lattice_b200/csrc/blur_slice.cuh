@@ -16,6 +16,7 @@ __device__ __forceinline__ float mix3(float a, float b, float c) {
 __global__ void __launch_bounds__(256)
 blur_axis(const Header* hdr, const int* __restrict__ nbr_axis, const float* __restrict__ src,
           float* __restrict__ dst, int qpr) {
+    after_previous_kernel();
     if (hdr->status != 0) return;
     const u32 M = hdr->num_vertices;
     const u64 items = (u64)M * qpr;
@@ -65,6 +66,7 @@ __global__ void __launch_bounds__(Cfg<PD>::TP, (Cfg<PD>::TP == 256) ? 5 : 8)
 slice_tiles_fast(Geom g, float* __restrict__ output, const Header* hdr, const int2* __restrict__ tile_info,
                  const u16* __restrict__ rec, const float* __restrict__ rec_w,
                  const u32* __restrict__ list_ref, const float* __restrict__ vsrc, int rows_cap, int bulk_ok) {
+    wait_for_previous_kernel();
     constexpr int TP = Cfg<PD>::TP, SPLATS = Cfg<PD>::SPLATS, C = VD - 1, VP = (VD + 3) & ~3, QPR = VP / 4;
     constexpr int RS = SliceFast<PD, VD>::RS;
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -191,6 +193,7 @@ __global__ void __launch_bounds__(Cfg<PD>::TP)
 slice_tiles_generic(Geom g, float* __restrict__ output, const Header* hdr, const int2* __restrict__ tile_info,
                     const u16* __restrict__ rec, const float* __restrict__ rec_w,
                     const u32* __restrict__ list_ref, const float* __restrict__ vsrc, int vd, int rows_cap) {
+    wait_for_previous_kernel();
     constexpr int TP = Cfg<PD>::TP, SPLATS = Cfg<PD>::SPLATS, PW = SliceCfg<PD>::PW;
     const int C = vd - 1, VP = padded_vd(vd), QPR = VP >> 2;
     extern __shared__ __align__(16) unsigned char smem_raw[];

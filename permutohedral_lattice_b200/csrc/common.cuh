@@ -392,6 +392,26 @@ __device__ __forceinline__ void fence_async_proxy() {
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
 
+// First statement of every kernel of a filter call.  A kernel launched with programmatic stream serialisation
+// may become resident while the kernel before it in the stream is still draining: the first instruction lets
+// the kernel AFTER this one do the same (its CTAs are scheduled once every CTA of this grid has started), the
+// second waits until the kernel BEFORE this one has finished and its writes are visible.  Every kernel waits
+// before it reads anything, so "the kernel before has finished" implies that all earlier ones have.  Both
+// instructions do nothing in a plain launch.
+__device__ __forceinline__ void after_previous_kernel() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+// The two halves for kernels whose grid runs in several waves (the tile kernels): they let the next kernel
+// start only when their own work is nearly done.  Released at their start, the next kernel's CTAs sat on the
+// SMs beside the tile kernel's later waves and slowed them (measured: a call 15 % slower).
+__device__ __forceinline__ void wait_for_previous_kernel() {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+__device__ __forceinline__ void let_next_kernel_start() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
 // Developer aid, compiled only with -DPL_PHASE_CLOCKS: cycles that thread 0 of every CTA spends between
 // marks, summed per kernel and phase (read back with pl_debug_phase_cycles).  Off in the shipped build.
 #ifdef PL_PHASE_CLOCKS

@@ -35,6 +35,7 @@ __device__ __forceinline__ bool direct_slot(const Direct& d, const Key<Cfg<PD>::
 }
 
 __global__ void clear_direct(Header* hdr, u32* __restrict__ table, u64 slots) {
+    after_previous_kernel();
     if (hdr->status != 0) return;
     if (blockIdx.x == 0 && threadIdx.x == 0) {
         u32 lg = 0;
@@ -52,6 +53,7 @@ __global__ void __launch_bounds__(256)
 insert_direct(Header* hdr, Direct d, u32* __restrict__ table, const Key<Cfg<PD>::KW>* __restrict__ list_keys,
               u32* __restrict__ list_ref, u32* __restrict__ vid, Key<Cfg<PD>::KW>* __restrict__ vkeys,
               VertexInit vi) {
+    after_previous_kernel();
     constexpr int KW = Cfg<PD>::KW;
     __shared__ InsertRound rd;
     if (threadIdx.x == 0) rd.count = 0;
@@ -88,6 +90,7 @@ __global__ void __launch_bounds__(256)
 link_neighbours_direct(const Header* hdr, Direct d, const u32* __restrict__ table, u32* __restrict__ list_ref,
                        const u32* __restrict__ vid, const Key<Cfg<PD>::KW>* __restrict__ vkeys,
                        int* __restrict__ nbr, u64 max_entries) {
+    after_previous_kernel();
     constexpr int KW = Cfg<PD>::KW;
     if (hdr->status != 0) return;
     resolve_entries(hdr, list_ref, vid);

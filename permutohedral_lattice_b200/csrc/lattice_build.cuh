@@ -27,6 +27,7 @@ __global__ void __launch_bounds__(Cfg<PD>::TP, (PD <= 5 && !is_double<R>::value)
 build_tiles(Geom g, const R* __restrict__ positions, const R* __restrict__ reference,
             Header* hdr, int2* __restrict__ tile_info, u16* __restrict__ rec, R* __restrict__ rec_w,
             uint2* __restrict__ srec, Key<Cfg<PD>::KW>* __restrict__ list_keys, u32 max_entries) {
+    wait_for_previous_kernel();
     constexpr int KW = Cfg<PD>::KW, TP = Cfg<PD>::TP, SPLATS = Cfg<PD>::SPLATS, LS = Cfg<PD>::LS;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     Key<KW>* keys_s = reinterpret_cast<Key<KW>*>(smem_raw);
@@ -199,6 +200,7 @@ build_tiles(Geom g, const R* __restrict__ positions, const R* __restrict__ refer
     }
     __syncthreads();
     pc.mark();
+    if constexpr (!SORTED) let_next_kernel_start();   // what is left of this tile: its keys
     const int base = base_s;
     if (valid && base >= 0) {
 #pragma unroll
@@ -263,6 +265,7 @@ build_tiles(Geom g, const R* __restrict__ positions, const R* __restrict__ refer
 // clear_table: table capacity = power of two >= 2 * entries (at least 1024), chosen on the device.
 // ---------------------------------------------------------------------------------------------
 __global__ void clear_table(Header* hdr, u64* __restrict__ table, u32 max_log2) {
+    after_previous_kernel();
     if (hdr->status != 0) return;
     u32 need = 2u * hdr->num_entries;
     u32 lg = 10;
@@ -381,6 +384,7 @@ template <int KW>
 __global__ void __launch_bounds__(256)
 insert_entries(Header* hdr, u64* __restrict__ table, const Key<KW>* __restrict__ list_keys,
                u32* __restrict__ list_ref, u32* __restrict__ vid, Key<KW>* __restrict__ vkeys, VertexInit vi) {
+    after_previous_kernel();
     __shared__ InsertRound rd;
     if (threadIdx.x == 0) rd.count = 0;
     if (call_failed(hdr)) return;   // (its barrier also publishes rd.count)
@@ -455,6 +459,7 @@ link_neighbours(const Header* hdr, const u64* __restrict__ table,
                 const Key<Cfg<PD>::KW>* __restrict__ list_keys, u32* __restrict__ list_ref,
                 const u32* __restrict__ vid, const Key<Cfg<PD>::KW>* __restrict__ vkeys, int* __restrict__ nbr,
                 u64 max_entries, void* zero_rows_ptr, u32 zero_row_bytes) {
+    after_previous_kernel();
     constexpr int KW = Cfg<PD>::KW;
     if (hdr->status != 0) return;
     resolve_entries(hdr, list_ref, vid);

@@ -65,19 +65,40 @@ static int cuda_fail(cudaError_t e, const char* where) {
         if (e_ != cudaSuccess) return cuda_fail(e_, #call); \
     } while (0)
 
-// Kernel launch with the error check of every other runtime call.
+// Kernel launch with the error check of every other runtime call.  overlap: with programmatic stream
+// serialisation, i.e. the kernel may become resident while the kernel before it in the stream drains (it waits
+// in after_previous_kernel() until that kernel has finished).
 template <typename... Params, typename... Args>
-static cudaError_t launch_kernel(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
-                                 Args&&... args) {
+static cudaError_t launch_kernel(bool overlap, void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem,
+                                 cudaStream_t st, Args&&... args) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = block;
     cfg.dynamicSmemBytes = smem;
     cfg.stream = st;
+    cudaLaunchAttribute attr = {};
+    if (overlap) {
+        attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr.val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = &attr;
+        cfg.numAttrs = 1;
+    }
     return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
 }
 #define PL_LAUNCH(kernel, grid, block, smem, st, ...) \
-    PL_CUDA(launch_kernel(kernel, dim3(grid), dim3(block), smem, st, __VA_ARGS__))
+    PL_CUDA(launch_kernel(false, kernel, dim3(grid), dim3(block), smem, st, __VA_ARGS__))
+// Which launches overlap the tail of the kernel before them (bits of PL_OVERLAP), each measured on its own
+// (B200, 16 items / 2 items of the dense-CRF workload, ms per forward + backward step, all others as chosen):
+// the blur passes after one another 2.023 -> 2.007 / 0.353 -> 0.342; the slice after the last pass and the
+// splat after link_neighbours -> 2.002 / 0.335; clear_table after build_tiles -> 1.993 / 0.331; insert_entries
+// after clear_table -> 1.992 / 0.328.  Left plain because they measured slower at 16 items: link_neighbours
+// after insert_entries (index stage 0.175 -> 0.181 ms) and the first blur pass after the splat (2.09).
+enum { OV_BLUR = 1, OV_INSERT = 2, OV_SPLAT = 4, OV_BLUR0 = 8, OV_SLICE = 16, OV_CLEAR = 32, OV_LINK = 64 };
+#ifndef PL_OVERLAP
+#define PL_OVERLAP (OV_BLUR | OV_INSERT | OV_SPLAT | OV_SLICE | OV_CLEAR)
+#endif
+#define PL_LAUNCH_AFTER(which, kernel, grid, block, smem, st, ...) \
+    PL_CUDA(launch_kernel((PL_OVERLAP & (which)) != 0, kernel, dim3(grid), dim3(block), smem, st, __VA_ARGS__))
 
 static size_t align_up(size_t x) { return (x + 255) & ~(size_t)255; }
 
@@ -272,18 +293,18 @@ static int launch_splat_as(const Geom& g, const float* input, Header* hdr, const
         PL_TRY((ensure_dynamic_smem<splat_tiles_rows<PD, VD, PRE>>(smem, true)));
         // bulk staging also needs 16-byte aligned landing zones inside the padded tile rows
         const bool bulk = bulk_rows_ok(g, input, VD - 1) && g.TX <= 16 && (g.TX * (SR::VP - (VD - 1))) % 4 == 0;
-        PL_LAUNCH((splat_tiles_rows<PD, VD, PRE>), tile_grid(g), Cfg<PD>::TP, smem, st, g, input, hdr, tile_info, rec, rec_w,
+        PL_LAUNCH_AFTER(OV_SPLAT, (splat_tiles_rows<PD, VD, PRE>), tile_grid(g), Cfg<PD>::TP, smem, st, g, input, hdr, tile_info, rec, rec_w,
                                                                               srec, list_ref, v0, bulk ? 1 : 0);
     } else if constexpr (VD > 0) {
         const size_t smem = SplatFast<PD, VD, PRE>::BYTES;
         PL_TRY((ensure_dynamic_smem<splat_tiles_fast<PD, VD, PRE>>(smem)));
-        PL_LAUNCH((splat_tiles_fast<PD, VD, PRE>), tile_grid(g), Cfg<PD>::TP, smem, st, g, input, hdr, tile_info, rec, rec_w,
+        PL_LAUNCH_AFTER(OV_SPLAT, (splat_tiles_fast<PD, VD, PRE>), tile_grid(g), Cfg<PD>::TP, smem, st, g, input, hdr, tile_info, rec, rec_w,
                                                                               srec, list_ref, v0, bulk_rows_ok(g, input, VD - 1) ? 1 : 0);
     } else {
         const size_t smem = SplatGeneric<PD>::bytes(vd);
         if (smem > 200 * 1024) return PL_UNSUPPORTED_DIMS;
         PL_TRY((ensure_dynamic_smem<splat_tiles_generic<PD>>(smem)));
-        PL_LAUNCH((splat_tiles_generic<PD>), tile_grid(g), Cfg<PD>::TP, smem, st, g, input, hdr, tile_info, rec, rec_w,
+        PL_LAUNCH_AFTER(OV_SPLAT, (splat_tiles_generic<PD>), tile_grid(g), Cfg<PD>::TP, smem, st, g, input, hdr, tile_info, rec, rec_w,
                                                                         list_ref, v0, vd);
     }
     return PL_OK;
@@ -306,14 +327,14 @@ static int launch_slice(const Geom& g, float* output, const Header* hdr, const i
         if (rows_cap > Cfg<PD>::SPLATS) rows_cap = Cfg<PD>::SPLATS;
         const size_t smem = SliceFast<PD, VD>::bytes(rows_cap);
         PL_TRY((ensure_dynamic_smem<slice_tiles_fast<PD, VD>>(smem)));
-        PL_LAUNCH((slice_tiles_fast<PD, VD>), tile_grid(g), Cfg<PD>::TP, smem, st, g, output, hdr, tile_info, rec, rec_w, list_ref, vsrc, rows_cap, bulk_rows_ok(g, output, VD - 1) ? 1 : 0);
+        PL_LAUNCH_AFTER(OV_SLICE, (slice_tiles_fast<PD, VD>), tile_grid(g), Cfg<PD>::TP, smem, st, g, output, hdr, tile_info, rec, rec_w, list_ref, vsrc, rows_cap, bulk_rows_ok(g, output, VD - 1) ? 1 : 0);
     } else {
         const int rows_cap = rows_cap_for(PD, vd);
         const size_t fixed = sizeof(float) * Cfg<PD>::TP * SliceCfg<PD>::PW + sizeof(int) * Cfg<PD>::TP;
         const size_t smem = sizeof(float) * (size_t)rows_cap * padded_vd(vd) + fixed;
         if (smem > 200 * 1024) return PL_UNSUPPORTED_DIMS;
         PL_TRY((ensure_dynamic_smem<slice_tiles_generic<PD>>(smem)));
-        PL_LAUNCH((slice_tiles_generic<PD>), tile_grid(g), Cfg<PD>::TP, smem, st, g, output, hdr, tile_info, rec, rec_w,
+        PL_LAUNCH_AFTER(OV_SLICE, (slice_tiles_generic<PD>), tile_grid(g), Cfg<PD>::TP, smem, st, g, output, hdr, tile_info, rec, rec_w,
                                                                         list_ref, vsrc, vd, rows_cap);
     }
     return PL_OK;
@@ -388,9 +409,9 @@ static int run_filter(const Geom& g, float* output, const float* input, const fl
         if constexpr (PD <= MAX_SDIMS) {
             if (use_direct) {
                 u32* table32 = reinterpret_cast<u32*>(table);
-                PL_LAUNCH((clear_direct), wide, 256, 0, st, hdr, table32, direct.slots);
-                PL_LAUNCH((insert_direct<PD>), wide, 256, 0, st, hdr, direct, table32, list_keys, list_ref, vid, vkeys, vinit);
-                PL_LAUNCH((link_neighbours_direct<PD>), wide, 256, 0, st, hdr, direct, table32, list_ref, vid, vkeys, nbr,
+                PL_LAUNCH_AFTER(OV_CLEAR, (clear_direct), wide, 256, 0, st, hdr, table32, direct.slots);
+                PL_LAUNCH_AFTER(OV_INSERT, (insert_direct<PD>), wide, 256, 0, st, hdr, direct, table32, list_keys, list_ref, vid, vkeys, vinit);
+                PL_LAUNCH_AFTER(OV_LINK, (link_neighbours_direct<PD>), wide, 256, 0, st, hdr, direct, table32, list_ref, vid, vkeys, nbr,
                                                                  L.max_entries);
             }
         }
@@ -398,9 +419,11 @@ static int run_filter(const Geom& g, float* output, const float* input, const fl
             // the value rows are zeroed by the link launch, whose lookups leave the memory system idle
             void* zrows = vinit.rows;
             vinit.rows = nullptr;
-            PL_LAUNCH((clear_table), wide, 256, 0, st, hdr, table, (u32)table_log2);
-            PL_LAUNCH((insert_entries<KW>), wide, 256, 0, st, hdr, table, list_keys, list_ref, vid, vkeys, vinit);
-            PL_LAUNCH((link_neighbours<PD>), wide, 256, 0, st, hdr, table, list_keys, list_ref, vid, vkeys, nbr,
+            // (behind the build that also sorts the splats the overlap measured slower: 1.66 against 1.61 ms for
+            // a build and two applies)
+            PL_LAUNCH_AFTER((phases & PH_APPLY) ? OV_CLEAR : 0, (clear_table), wide, 256, 0, st, hdr, table, (u32)table_log2);
+            PL_LAUNCH_AFTER(OV_INSERT, (insert_entries<KW>), wide, 256, 0, st, hdr, table, list_keys, list_ref, vid, vkeys, vinit);
+            PL_LAUNCH_AFTER(OV_LINK, (link_neighbours<PD>), wide, 256, 0, st, hdr, table, list_keys, list_ref, vid, vkeys, nbr,
                                                       L.max_entries, zrows, vinit.row_bytes);
         }
         if (ev) PL_CUDA(cudaEventRecord(ev[2], st));
@@ -435,7 +458,7 @@ static int run_filter(const Geom& g, float* output, const float* input, const fl
     for (int step = 0; step <= PD; step++) {
         const int axis = reverse ? PD - step : step;
         const int* nb = nbr + (size_t)axis * L.max_entries * 2;
-        PL_LAUNCH((blur_axis), wide, 256, 0, st, hdr, nb, src, dst, qpr);
+        PL_LAUNCH_AFTER(step == 0 ? OV_BLUR0 : OV_BLUR, (blur_axis), wide, 256, 0, st, hdr, nb, src, dst, qpr);
         float* tmp = src; src = dst; dst = tmp;
     }
     PL_COUNT_LAUNCHES(PD + 1);

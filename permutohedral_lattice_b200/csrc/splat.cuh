@@ -141,6 +141,7 @@ __global__ void __launch_bounds__(Cfg<PD>::TP)
 splat_tiles_fast(Geom g, const float* __restrict__ input, Header* hdr, const int2* __restrict__ tile_info,
                  const u16* __restrict__ rec, const float* __restrict__ rec_w, const uint2* __restrict__ srec,
                  const u32* __restrict__ list_ref, float* __restrict__ v0, int bulk_ok) {
+    wait_for_previous_kernel();
     constexpr int TP = Cfg<PD>::TP, SPLATS = Cfg<PD>::SPLATS, C = VD - 1, VP = (VD + 3) & ~3;
     using SF = SplatFast<PD, VD, PRE>;
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -240,6 +241,7 @@ splat_tiles_fast(Geom g, const float* __restrict__ input, Header* hdr, const int
             acc[C] = PL_FADD(acc[C], wt);
         }
     }
+    let_next_kernel_start();   // what is left of this thread's work: its last row
     flush_row<VP>(v0 + (size_t)vid_s[cur] * VP, acc);
 }
 
@@ -269,6 +271,7 @@ __global__ void __launch_bounds__(Cfg<PD>::TP, 5)
 splat_tiles_rows(Geom g, const float* __restrict__ input, Header* hdr, const int2* __restrict__ tile_info,
                  const u16* __restrict__ rec, const float* __restrict__ rec_w, const uint2* __restrict__ srec,
                  const u32* __restrict__ list_ref, float* __restrict__ v0, int bulk_ok) {
+    wait_for_previous_kernel();
     using SR = SplatRows<PD, VD, PRE>;
     constexpr int TP = SR::TP, SPLATS = SR::SPLATS, C = VD - 1, VP = SR::VP, LR = SR::LR, WL = SR::WL;
     static_assert(LR <= 8, "a row must fit the 8 lanes of a quarter warp");
@@ -430,6 +433,7 @@ splat_tiles_rows(Geom g, const float* __restrict__ input, Header* hdr, const int
             acc.z = PL_FMA(wt, x.z, acc.z);
             acc.w = PL_FMA(wt, x.w, acc.w);
         }
+        let_next_kernel_start();   // what is left of this thread's work: its last row
         red_add_v4(v0 + (size_t)vcur * VP + 4 * h, acc);
     }
     pc.mark(true);
@@ -449,6 +453,7 @@ __global__ void __launch_bounds__(Cfg<PD>::TP)
 splat_tiles_generic(Geom g, const float* __restrict__ input, Header* hdr, const int2* __restrict__ tile_info,
                     const u16* __restrict__ rec, const float* __restrict__ rec_w,
                     const u32* __restrict__ list_ref, float* __restrict__ v0, int vd) {
+    wait_for_previous_kernel();
     constexpr int TP = Cfg<PD>::TP, SPLATS = Cfg<PD>::SPLATS, NW = TP / 32;
     const int C = vd - 1, VP = padded_vd(vd), QPR = VP >> 2;
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -520,6 +525,7 @@ splat_tiles_generic(Geom g, const float* __restrict__ input, Header* hdr, const 
 // ---------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256)
 absmax_kernel(const float* __restrict__ input, u64 count, Header* hdr) {
+    after_previous_kernel();
     u32 m = 0;
     for (u64 i = (u64)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += (u64)gridDim.x * blockDim.x)
         m = max(m, __float_as_uint(fabsf(input[i])));
@@ -549,6 +555,7 @@ __global__ void __launch_bounds__(Cfg<PD>::TP)
 splat_tiles_det(Geom g, const float* __restrict__ input, Header* hdr, const int2* __restrict__ tile_info,
                 const u16* __restrict__ rec, const float* __restrict__ rec_w,
                 const u32* __restrict__ list_ref, long long* __restrict__ v64, int vd) {
+    after_previous_kernel();
     constexpr int TP = Cfg<PD>::TP, SPLATS = Cfg<PD>::SPLATS, NW = TP / 32;
     const int C = vd - 1, VP = padded_vd(vd);
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -618,6 +625,7 @@ splat_tiles_det(Geom g, const float* __restrict__ input, Header* hdr, const int2
 // fixed-point sums -> float rows
 __global__ void __launch_bounds__(256)
 convert_fixed(const Header* hdr, const long long* __restrict__ v64, float* __restrict__ v0, int vp) {
+    after_previous_kernel();
     if (hdr->status != 0) return;
     const double inv = 1.0 / fixed_scale(hdr);
     const u64 cells = (u64)hdr->num_vertices * vp;
@@ -628,6 +636,7 @@ convert_fixed(const Header* hdr, const long long* __restrict__ v64, float* __res
 // Start of an apply on an already built lattice: value rows (or fixed-point sums) back to zero.
 __global__ void __launch_bounds__(256)
 zero_rows(Header* hdr, float* __restrict__ v0, long long* __restrict__ v64, int vp) {
+    after_previous_kernel();
     if (hdr->status != 0) return;
     if (blockIdx.x == 0 && threadIdx.x == 0) hdr->absmax_bits = 0;
     const u64 cells = (u64)hdr->num_vertices * vp;
