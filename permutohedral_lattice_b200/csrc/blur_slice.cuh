@@ -16,24 +16,33 @@ __device__ __forceinline__ float mix3(float a, float b, float c) {
 __global__ void __launch_bounds__(256)
 blur_axis(const Header* hdr, const int* __restrict__ nbr_axis, const float* __restrict__ src,
           float* __restrict__ dst, int qpr) {
-    after_previous_kernel();
-    if (hdr->status != 0) return;
+    // Passes after the first overlap the tail of the pass before (see after_previous_kernel).  The vertex count
+    // and the neighbour table are older than any blur pass: a thread's first pair of neighbours is fetched
+    // before the wait, so that one of the two dependent loads of its first row is off the critical path.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const u32 M = hdr->num_vertices;
     const u64 items = (u64)M * qpr;
+    const int2* __restrict__ nb = reinterpret_cast<const int2*>(nbr_axis);
+    u64 e = (u64)blockIdx.x * blockDim.x + threadIdx.x;
+    u32 v = (u32)(e / qpr);
+    int2 n = (e < items) ? __ldg(nb + v) : make_int2(-1, -1);
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (hdr->status != 0) return;
     const float4* __restrict__ s = reinterpret_cast<const float4*>(src);
     float4* __restrict__ d = reinterpret_cast<float4*>(dst);
-    const int2* __restrict__ nb = reinterpret_cast<const int2*>(nbr_axis);
     const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (u64 e = (u64)blockIdx.x * blockDim.x + threadIdx.x; e < items;
-         e += (u64)gridDim.x * blockDim.x) {
-        const u32 v = (u32)(e / qpr);
+    while (e < items) {
         const int j = (int)(e - (u64)v * qpr);
-        const int2 n = __ldg(nb + v);
         const float4 b = s[e];
         const float4 a = (n.x >= 0) ? s[(u64)n.x * qpr + j] : zero;
         const float4 c = (n.y >= 0) ? s[(u64)n.y * qpr + j] : zero;
         d[e] = make_float4(mix3(a.x, b.x, c.x), mix3(a.y, b.y, c.y), mix3(a.z, b.z, c.z),
                            mix3(a.w, b.w, c.w));
+        e += (u64)gridDim.x * blockDim.x;
+        if (e < items) {
+            v = (u32)(e / qpr);
+            n = __ldg(nb + v);
+        }
     }
 }
 
@@ -66,7 +75,8 @@ __global__ void __launch_bounds__(Cfg<PD>::TP, (Cfg<PD>::TP == 256) ? 5 : 8)
 slice_tiles_fast(Geom g, float* __restrict__ output, const Header* hdr, const int2* __restrict__ tile_info,
                  const u16* __restrict__ rec, const float* __restrict__ rec_w,
                  const u32* __restrict__ list_ref, const float* __restrict__ vsrc, int rows_cap, int bulk_ok) {
-    wait_for_previous_kernel();
+    // Launched to overlap the tail of the last blur pass: the status word, the tile's range and the per-point
+    // records are older than any blur pass and are fetched before the wait; the vertex rows after it.
     constexpr int TP = Cfg<PD>::TP, SPLATS = Cfg<PD>::SPLATS, C = VD - 1, VP = (VD + 3) & ~3, QPR = VP / 4;
     constexpr int RS = SliceFast<PD, VD>::RS;
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -75,6 +85,7 @@ slice_tiles_fast(Geom g, float* __restrict__ output, const Header* hdr, const in
     int* prow_s = reinterpret_cast<int*>(smem_raw + SliceFast<PD, VD>::region(rows_cap));       // [TP]
     if (call_failed(hdr)) {
         poison_tile_output(g, output, C);
+        wait_for_previous_kernel();
         return;
     }
     PhaseClock pc(2);
@@ -96,6 +107,7 @@ slice_tiles_fast(Geom g, float* __restrict__ output, const Header* hdr, const in
         l[r] = valid ? rec_tile[r * TP + tid] : 0;
         w[r] = valid ? recw_tile[r * TP + tid] : 0.f;
     }
+    wait_for_previous_kernel();
     // Row staging, CH copies per thread and trip: first the vertex numbers of all CH rows (independent
     // loads, in flight together with the record loads above), then the asynchronous copies that depend on
     // them; interleaving them one by one would put a full memory latency between consecutive copies.

@@ -92,7 +92,8 @@ static cudaError_t launch_kernel(bool overlap, void (*kernel)(Params...), dim3 g
 // the blur passes after one another 2.023 -> 2.007 / 0.353 -> 0.342; the slice after the last pass and the
 // splat after link_neighbours -> 2.002 / 0.335; clear_table after build_tiles -> 1.993 / 0.331; insert_entries
 // after clear_table -> 1.992 / 0.328.  Left plain because they measured slower at 16 items: link_neighbours
-// after insert_entries (index stage 0.175 -> 0.181 ms) and the first blur pass after the splat (2.09).
+// after insert_entries (index stage 0.175 -> 0.181 ms; in small calls it gains or loses 0.5 %) and the first
+// blur pass after the splat (2.09).
 enum { OV_BLUR = 1, OV_INSERT = 2, OV_SPLAT = 4, OV_BLUR0 = 8, OV_SLICE = 16, OV_CLEAR = 32, OV_LINK = 64 };
 #ifndef PL_OVERLAP
 #define PL_OVERLAP (OV_BLUR | OV_INSERT | OV_SPLAT | OV_SLICE | OV_CLEAR)

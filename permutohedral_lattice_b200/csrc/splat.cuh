@@ -271,7 +271,10 @@ __global__ void __launch_bounds__(Cfg<PD>::TP, 5)
 splat_tiles_rows(Geom g, const float* __restrict__ input, Header* hdr, const int2* __restrict__ tile_info,
                  const u16* __restrict__ rec, const float* __restrict__ rec_w, const uint2* __restrict__ srec,
                  const u32* __restrict__ list_ref, float* __restrict__ v0, int bulk_ok) {
-    wait_for_previous_kernel();
+    // Launched to overlap the tail of the kernel before it (link_neighbours, or zero_rows in an apply): all
+    // that the staging and the sort read (the input, the records and tile ranges of build_tiles, whose
+    // failures are final by now) is older than that kernel, so they run before the wait; the window loop,
+    // which reads the entries' vertices and adds to the zeroed rows, runs after it.
     using SR = SplatRows<PD, VD, PRE>;
     constexpr int TP = SR::TP, SPLATS = SR::SPLATS, C = VD - 1, VP = SR::VP, LR = SR::LR, WL = SR::WL;
     static_assert(LR <= 8, "a row must fit the 8 lanes of a quarter warp");
@@ -282,8 +285,10 @@ splat_tiles_rows(Geom g, const float* __restrict__ input, Header* hdr, const int
     int* cur_s = prow_s + TP;                                                 // [SPLATS], only without PRE
     __shared__ int wsum_s[32];
     __shared__ __align__(8) u64 bar;
-    if (call_failed(hdr)) return;
-    if (PRE && !lattice_is_sorted(hdr)) return;
+    if (call_failed(hdr) || (PRE && !lattice_is_sorted(hdr))) {
+        wait_for_previous_kernel();
+        return;
+    }
     PhaseClock pc(1);
     const TilePos tpos = this_tile(g);
     const int tid = threadIdx.x, tile = tpos.tile, lane = tid & 31, warp = tid >> 5;
@@ -403,9 +408,12 @@ splat_tiles_rows(Geom g, const float* __restrict__ input, Header* hdr, const int
     if (!__syncthreads_and(arrived ? 1 : 0)) {
         if (tid == 0) atomicOr(&hdr->status, 1u << PL_INTERNAL_ERROR);
         mbar_wait(&bar, 0);
+        wait_for_previous_kernel();
         return;
     }
     pc.mark();
+    wait_for_previous_kernel();
+    if (call_failed(hdr)) return;   // a failure of the index stage
 
     const int h = tid & 7, wnd = tid >> 3, first = wnd * WL;
     const bool active = (h < LR) && (first < total);
