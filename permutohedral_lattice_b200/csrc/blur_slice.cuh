@@ -19,14 +19,13 @@ blur_axis(const Header* hdr, const int* __restrict__ nbr_axis, const float* __re
     // Passes after the first overlap the tail of the pass before (see after_previous_kernel).  The vertex count
     // and the neighbour table are older than any blur pass: a thread's first pair of neighbours is fetched
     // before the wait, so that one of the two dependent loads of its first row is off the critical path.
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const u32 M = hdr->num_vertices;
     const u64 items = (u64)M * qpr;
     const int2* __restrict__ nb = reinterpret_cast<const int2*>(nbr_axis);
     u64 e = (u64)blockIdx.x * blockDim.x + threadIdx.x;
     u32 v = (u32)(e / qpr);
     int2 n = (e < items) ? __ldg(nb + v) : make_int2(-1, -1);
-    asm volatile("griddepcontrol.wait;" ::: "memory");
+    after_previous_kernel();
     if (hdr->status != 0) return;
     const float4* __restrict__ s = reinterpret_cast<const float4*>(src);
     float4* __restrict__ d = reinterpret_cast<float4*>(dst);

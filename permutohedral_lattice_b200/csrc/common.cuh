@@ -393,14 +393,16 @@ __device__ __forceinline__ void fence_async_proxy() {
 }
 
 // First statement of every kernel of a filter call.  A kernel launched with programmatic stream serialisation
-// may become resident while the kernel before it in the stream is still draining: the first instruction lets
-// the kernel AFTER this one do the same (its CTAs are scheduled once every CTA of this grid has started), the
-// second waits until the kernel BEFORE this one has finished and its writes are visible.  Every kernel waits
-// before it reads anything, so "the kernel before has finished" implies that all earlier ones have.  Both
-// instructions do nothing in a plain launch.
+// may become resident while the kernel before it in the stream is still draining: the first instruction waits
+// until that kernel has finished and its writes are visible, the second lets the kernel AFTER this one become
+// resident in its turn (its CTAs are scheduled once every CTA of this grid has got here).  Every kernel waits
+// before it reads anything, so "the kernel before has finished" implies that all earlier ones have.  The release
+// comes after the wait on purpose: released first, a waiting kernel lets the one after it wait beside it, and
+// two kernels' worth of waiting CTAs on the SMs slowed a long-running tile kernel by a quarter (pd = 16).
+// Both instructions do nothing in a plain launch.
 __device__ __forceinline__ void after_previous_kernel() {
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 }
 // The two halves for kernels whose grid runs in several waves (the tile kernels): they let the next kernel
 // start only when their own work is nearly done.  Released at their start, the next kernel's CTAs sat on the

@@ -91,7 +91,8 @@ static cudaError_t launch_kernel(bool overlap, void (*kernel)(Params...), dim3 g
 // (B200, 16 items / 2 items of the dense-CRF workload, ms per forward + backward step, all others as chosen):
 // the blur passes after one another 2.023 -> 2.007 / 0.353 -> 0.342; the slice after the last pass and the
 // splat after link_neighbours -> 2.002 / 0.335; clear_table after build_tiles -> 1.993 / 0.331; insert_entries
-// after clear_table -> 1.992 / 0.328.  Left plain because they measured slower at 16 items: link_neighbours
+// after clear_table -> 1.992 / 0.328 (small tables only, see run_filter).  Left plain because they measured
+// slower at 16 items: link_neighbours
 // after insert_entries (index stage 0.175 -> 0.181 ms; in small calls it gains or loses 0.5 %) and the first
 // blur pass after the splat (2.09).
 enum { OV_BLUR = 1, OV_INSERT = 2, OV_SPLAT = 4, OV_BLUR0 = 8, OV_SLICE = 16, OV_CLEAR = 32, OV_LINK = 64 };
@@ -384,6 +385,9 @@ static int run_filter(const Geom& g, float* output, const float* input, const fl
     int table_log2 = 0;
     while ((1ull << table_log2) < L.table_slots) table_log2++;
 
+    // insert_entries overlaps clear_table only while the table can stay in L2 (64 MB of slots): behind a
+    // clear_table that itself overlaps build_tiles it cost calls with large tables 4-25 % (pd 16: 30 -> 37 ms)
+    const bool small_table = L.table_slots <= (1ull << 23);
     if (phases & PH_BUILD) {
         // a lattice built to be applied later (no values in this call) also gets its splats sorted
         if (phases & PH_APPLY) {
@@ -411,7 +415,7 @@ static int run_filter(const Geom& g, float* output, const float* input, const fl
             if (use_direct) {
                 u32* table32 = reinterpret_cast<u32*>(table);
                 PL_LAUNCH_AFTER(OV_CLEAR, (clear_direct), wide, 256, 0, st, hdr, table32, direct.slots);
-                PL_LAUNCH_AFTER(OV_INSERT, (insert_direct<PD>), wide, 256, 0, st, hdr, direct, table32, list_keys, list_ref, vid, vkeys, vinit);
+                PL_LAUNCH_AFTER(small_table ? OV_INSERT : 0, (insert_direct<PD>), wide, 256, 0, st, hdr, direct, table32, list_keys, list_ref, vid, vkeys, vinit);
                 PL_LAUNCH_AFTER(OV_LINK, (link_neighbours_direct<PD>), wide, 256, 0, st, hdr, direct, table32, list_ref, vid, vkeys, nbr,
                                                                  L.max_entries);
             }
@@ -423,7 +427,7 @@ static int run_filter(const Geom& g, float* output, const float* input, const fl
             // (behind the build that also sorts the splats the overlap measured slower: 1.66 against 1.61 ms for
             // a build and two applies)
             PL_LAUNCH_AFTER((phases & PH_APPLY) ? OV_CLEAR : 0, (clear_table), wide, 256, 0, st, hdr, table, (u32)table_log2);
-            PL_LAUNCH_AFTER(OV_INSERT, (insert_entries<KW>), wide, 256, 0, st, hdr, table, list_keys, list_ref, vid, vkeys, vinit);
+            PL_LAUNCH_AFTER(small_table ? OV_INSERT : 0, (insert_entries<KW>), wide, 256, 0, st, hdr, table, list_keys, list_ref, vid, vkeys, vinit);
             PL_LAUNCH_AFTER(OV_LINK, (link_neighbours<PD>), wide, 256, 0, st, hdr, table, list_keys, list_ref, vid, vkeys, nbr,
                                                       L.max_entries, zrows, vinit.row_bytes);
         }
