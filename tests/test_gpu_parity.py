@@ -355,6 +355,24 @@ def test_apply_refuses_a_workspace_no_build_prepared(gpu):
     assert bool(torch.isnan(out).all())
 
 
+def test_back_to_back_calls_are_repeatable(gpu):
+    """Several kernels of a call start while the kernel before them drains and wait on the device for it; calls
+    issued back to back on one workspace must still see each other's results in order.  The deterministic mode
+    gives the same bits every time, so any kernel that read too early would show."""
+    import torch
+    import permutohedral_lattice_b200 as plb
+    rng = np.random.default_rng(59)
+    ref = torch.from_numpy(rng.random((3, 96, 80, 3), dtype=np.float32)).cuda()
+    x = torch.from_numpy(rng.standard_normal((3, 96, 80, 21)).astype(np.float32)).cuda()
+    outs = [plb.lattice_filter(x, ref, True, 6.0, 0.15, mode="deterministic") for _ in range(60)]
+    torch.cuda.synchronize()
+    assert all(torch.equal(outs[0], o) for o in outs[1:])
+    lat = plb.Lattice(ref, bilateral=True, theta_alpha=6.0, theta_beta=0.15, max_channels=21, mode="deterministic")
+    outs = [lat.apply(x, reverse=bool(i & 1), mode="deterministic") for i in range(40)]
+    torch.cuda.synchronize()
+    assert all(torch.equal(outs[i & 1], o) for i, o in enumerate(outs))
+
+
 def test_autograd_with_lattice_reuse(gpu, oracle):
     import torch
     import permutohedral_lattice_b200 as plb
